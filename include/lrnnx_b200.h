@@ -1,0 +1,241 @@
+/*
+ * lrnnx_b200.h — C ABI of liblrnnx_b200.so, the sm_100a scan back end for lrnnx.
+ *
+ * Every entry point takes a pointer to a plain-old-data argument block (raw
+ * device pointers, sizes, element strides, flags) plus the CUDA stream to
+ * launch on (a cudaStream_t passed as void*), and returns an int status:
+ *   0            success (kernels enqueued on `stream`; nothing is synchronised)
+ *   negative     argument rejected (B200_ERR_*); b200_last_error() has the text
+ *   positive     CUDA runtime error code from the launch
+ * No entry point allocates device memory unless its comment says so; outputs
+ * and accumulators are caller-allocated.  All strides count ELEMENTS of the
+ * tensor's own dtype (a complex64 element is one element).  The innermost
+ * (sequence) stride of every activation tensor must be 1.
+ *
+ * The "replaces" notes cite the lrnnx source file and lines whose behaviour the
+ * entry point reproduces (paths are relative to the lrnnx repository root).
+ */
+#ifndef LRNNX_B200_H_
+#define LRNNX_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* activation dtypes */
+enum { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2 };
+
+/* discretization methods; same set and meaning as
+ * csrc/selective_scan/selective_scan.h:14-21 (enum DiscretizationMethod) */
+enum {
+  B200_DISC_ZOH = 0,
+  B200_DISC_BILINEAR = 1,
+  B200_DISC_DIRAC = 2,
+  B200_DISC_MAMBA = 3,
+  B200_DISC_RGLRU = 4,
+  B200_DISC_S7 = 5
+};
+
+/* status codes */
+enum {
+  B200_OK = 0,
+  B200_ERR_NULL = -1,      /* required pointer is null */
+  B200_ERR_SHAPE = -2,     /* size out of range (e.g. dstate > 256) */
+  B200_ERR_DTYPE = -3,     /* unknown dtype / discretization / combination */
+  B200_ERR_ALIGN = -4,     /* pointer alignment */
+  B200_ERR_UNSUPPORTED = -5,
+  B200_ERR_TOO_LARGE = -6  /* exceeds a fixed capacity of a no-allocation entry point */
+};
+
+const char *b200_last_error(void);   /* thread-local text of the last negative status */
+int b200_abi_version(void);          /* bumped when any struct below changes */
+int b200_sizeof(const char *struct_name);   /* sizeof() of a named argument block, -1 if unknown */
+
+/* ------------------------------------------------------------------------
+ * Selective scan forward.
+ * Replaces selective_scan_fwd (csrc/selective_scan/selective_scan_cpu.cpp:263-421)
+ * and the kernel it launches (csrc/selective_scan/selective_scan.cuh:73-382).
+ *   u, delta, z, deltaA, out, out_z : (batch, dim, seqlen) activations dtype
+ *   A : (dim, dstate) float32 or complex64
+ *   B, C : constant (dim, dstate) in A's dtype, or variable
+ *          (batch, n_groups, dstate, seqlen) activations dtype
+ *          (last dim 2*seqlen interleaved re/im when A is complex)
+ *   D, delta_bias : (dim) float32, nullable
+ *   x : (batch, dim, n_chunks, 2*dstate) in A's dtype, n_chunks = ceil(seqlen/2048);
+ *       x[b,d,c,2n] = running product of the discrete A from t=0 to the end of
+ *       chunk c, x[b,d,c,2n+1] = state at the end of chunk c.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_selscan_fwd_args {
+  int32_t batch, dim, seqlen, dstate, n_groups;
+  int32_t dtype;            /* B200_F32 / F16 / BF16: u, delta, z, deltaA, variable B/C, out */
+  int32_t is_complex;       /* A (and constant B/C, x) are complex64 */
+  int32_t var_B, var_C;
+  int32_t delta_softplus;
+  int32_t method;           /* B200_DISC_* */
+  int32_t reserved0;
+  const void *u, *delta, *A, *B, *C;
+  const void *D, *z, *delta_bias, *deltaA;      /* nullable */
+  void *out;                                    /* (batch, dim, seqlen) */
+  void *out_z;                                  /* required iff z != NULL */
+  void *x;                                      /* required */
+  int64_t u_bs, u_ds;
+  int64_t delta_bs, delta_ds;
+  int64_t z_bs, z_ds;
+  int64_t deltaA_bs, deltaA_ds;
+  int64_t out_bs, out_ds;
+  int64_t out_z_bs, out_z_ds;
+  int64_t A_ds, A_ns;
+  int64_t B_bs, B_gs, B_ns;   /* variable: batch/group/state strides; constant: B_gs = dim stride */
+  int64_t C_bs, C_gs, C_ns;
+} b200_selscan_fwd_args;
+
+int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Selective scan backward (reverse scan with recomputation of the states).
+ * Replaces selective_scan_bwd (csrc/selective_scan/selective_scan_cpu.cpp:423-632)
+ * and its kernel (csrc/selective_scan/selective_scan_backward.cuh:86-845).
+ * The caller zero-fills dA, dB, dC, dD, ddelta_bias before the call; the kernel
+ * accumulates into them with atomics.  dB/dC are float32 accumulators when the
+ * matching input is variable ((batch, n_groups, dstate, seqlen[*2]) float32),
+ * otherwise (dim, dstate) in A's dtype.
+ *   x   : forward checkpoints; may be NULL only when seqlen <= 2048
+ *   out : forward output before gating; required iff z != NULL
+ *   dz  : required iff z != NULL;  out_z : optional recomputed gated output
+ * ------------------------------------------------------------------------ */
+typedef struct b200_selscan_bwd_args {
+  b200_selscan_fwd_args f;   /* f.out = saved forward `out` (or NULL), f.out_z = optional recompute target */
+  const void *dout;          /* (batch, dim, seqlen) activations dtype */
+  void *du, *ddelta;         /* (batch, dim, seqlen) activations dtype */
+  void *ddeltaA;             /* required iff f.deltaA != NULL */
+  void *dz;                  /* required iff f.z != NULL */
+  void *dA;                  /* (dim, dstate) A dtype, zero-filled */
+  void *dB, *dC;             /* see above, zero-filled */
+  void *dD, *ddelta_bias;    /* (dim) float32 zero-filled; required iff D / delta_bias given */
+  int64_t dout_bs, dout_ds;
+  int64_t du_bs, du_ds;
+  int64_t ddelta_bs, ddelta_ds;
+  int64_t ddeltaA_bs, ddeltaA_ds;
+  int64_t dz_bs, dz_ds;
+  int64_t dA_ds, dA_ns;
+  int64_t dB_bs, dB_gs, dB_ns;
+  int64_t dC_bs, dC_gs, dC_ns;
+} b200_selscan_bwd_args;
+
+int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Sequence-parallel helpers for the selective scan (no counterpart in lrnnx,
+ * which is single-GPU; they implement the chunk-summary exchange that
+ * BASELINE's long-sequence configuration asks for).
+ * b200_selscan_fixup adds the contribution of an incoming state h_in
+ * (batch, dim, dstate) float32 to an already computed zero-state output:
+ *   out[b,d,t] += sum_n C[t,n] * (prod_{k<=t} a_k[n]) * h_in[b,d,n]
+ * and rewrites out_z, the checkpoints x (product entries are multiplied by
+ * p_in, state entries corrected) accordingly.  Real A, variable B/C only.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_selscan_fixup_args {
+  b200_selscan_fwd_args f;      /* same tensors as the forward call on this rank's slice */
+  const void *h_in;             /* (batch, dim, dstate) float32: state entering this slice */
+  const void *p_in;             /* (batch, dim, dstate) float32: product of a over all earlier slices */
+} b200_selscan_fixup_args;
+
+int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Simplified (diagonal, complex-input) scan used by LTV-S5.
+ * Replaces simplified_scan_fwd/bwd (csrc/simplified_scan/simplified_scan_cpu.cpp:160-331)
+ * and kernels (csrc/simplified_scan/simplified_scan.cuh:85-262,
+ * csrc/simplified_scan/simplified_scan_backward.cuh:91-420).
+ *   u, out, dout, du : (batch, dim, seqlen) complex64
+ *   delta, deltaA, ddelta, ddeltaA : (batch, dim, seqlen) float32
+ *   A, B, C, dA, dB, dC : (dim, dstate) complex64  (dA/dB/dC zero-filled by caller)
+ *   x : (batch, dim, n_chunks, 2*dstate) complex64
+ *   method : ZOH, BILINEAR or DIRAC
+ * ------------------------------------------------------------------------ */
+typedef struct b200_simpscan_args {
+  int32_t batch, dim, seqlen, dstate;
+  int32_t method;
+  int32_t reserved0;
+  const void *u, *delta, *A, *B, *C;
+  const void *deltaA;              /* nullable */
+  void *out;                       /* fwd: output; bwd: unused */
+  void *x;                         /* fwd: written; bwd: read (may be NULL when seqlen <= 2048) */
+  int64_t u_bs, u_ds, delta_bs, delta_ds, deltaA_bs, deltaA_ds, out_bs, out_ds;
+  int64_t A_ds, A_ns, B_ds, B_ns, C_ds, C_ns;
+  /* backward only */
+  const void *dout;
+  void *du, *ddelta, *ddeltaA;
+  void *dA, *dB, *dC;
+  int64_t dout_bs, dout_ds, du_bs, du_ds, ddelta_bs, ddelta_ds, ddeltaA_bs, ddeltaA_ds;
+} b200_simpscan_args;
+
+int b200_simpscan_fwd(const b200_simpscan_args *args, void *stream);
+int b200_simpscan_bwd(const b200_simpscan_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * One-token state update used in decoding.
+ * Replaces selective_state_update and its Triton kernel
+ * (lrnnx/ops/triton/selective_state_update.py:300-476, 17-297).
+ * All tensors are described in the 4-D "heads" form; strides may be 0 for
+ * broadcast dimensions.  `state` is updated in place.
+ *   state (batch|*, nheads, dim, dstate) state_dtype
+ *   x, dt, z, deltaA, out (batch, nheads, dim) act dtype
+ *   A (nheads, dim, dstate) f32 ; B, C (batch, ngroups, dstate) bc dtype
+ *   D, dt_bias (nheads, dim) ; state_batch_indices (batch) int32, nullable
+ * ------------------------------------------------------------------------ */
+typedef struct b200_ssu_args {
+  int32_t batch, nheads, dim, dstate, ngroups;
+  int32_t state_dtype, x_dtype, dt_dtype, A_dtype, bc_dtype, D_dtype, z_dtype, dt_bias_dtype, deltaA_dtype;
+  int32_t dt_softplus;
+  int32_t method;
+  int32_t reserved0;
+  void *state;
+  const void *x, *dt, *A, *B, *C;
+  const void *D, *z, *dt_bias, *deltaA;         /* nullable */
+  const int32_t *state_batch_indices;           /* nullable */
+  void *out;                                    /* x dtype */
+  int64_t state_bs, state_hs, state_ds, state_ns;
+  int64_t x_bs, x_hs, x_ds;
+  int64_t dt_bs, dt_hs, dt_ds;
+  int64_t A_hs, A_ds, A_ns;
+  int64_t B_bs, B_gs, B_ns;
+  int64_t C_bs, C_gs, C_ns;
+  int64_t D_hs, D_ds;
+  int64_t z_bs, z_hs, z_ds;
+  int64_t dt_bias_hs, dt_bias_ds;
+  int64_t deltaA_bs, deltaA_hs, deltaA_ds;
+  int64_t out_bs, out_hs, out_ds;
+} b200_ssu_args;
+
+int b200_ssu_step(const b200_ssu_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * S4 structured kernels (contiguous tensors).
+ * Replace cauchy_mult_sym_fwd/bwd and vand_log_mult_sym_fwd/bwd
+ * (csrc/s4/cauchy.cpp:20-102, csrc/s4/cauchy_cuda.cu:34-368).
+ *   Cauchy: v, w (batch, n) complex64 (n = half size, power of two in [1,1024]),
+ *           z (seqlen) complex64, out/dout (batch, seqlen) complex64,
+ *           dv, dw (batch, n) complex64 written (not accumulated).
+ *   Vandermonde: v, x (batch, n) complex64, out/dout (batch, seqlen) float32,
+ *           dv, dx (batch, n) complex64 written.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_s4_args {
+  int32_t batch, n, seqlen, reserved0;
+  const void *v, *z, *w;        /* Vandermonde: w is the exponent tensor x, z unused */
+  void *out;
+  const void *dout;
+  void *dv, *dw;
+} b200_s4_args;
+
+int b200_cauchy_fwd(const b200_s4_args *args, void *stream);
+int b200_cauchy_bwd(const b200_s4_args *args, void *stream);
+int b200_vand_fwd(const b200_s4_args *args, void *stream);
+int b200_vand_bwd(const b200_s4_args *args, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LRNNX_B200_H_ */

@@ -1,0 +1,18 @@
+// Internal (C++) entry points behind the extern "C" layer in api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include "../../include/lrnnx_b200.h"
+
+namespace b200 {
+
+// coverage kernels: every variant (selscan_generic.cu)
+int selscan_fwd_generic(const b200_selscan_fwd_args &a, cudaStream_t st);
+int selscan_bwd_generic(const b200_selscan_bwd_args &a, cudaStream_t st);
+
+// throughput kernels for the hot S6 shape class (selscan_fast.cu)
+bool selscan_fwd_fast_supported(const b200_selscan_fwd_args &a);
+bool selscan_bwd_fast_supported(const b200_selscan_bwd_args &a);
+int selscan_fwd_fast(const b200_selscan_fwd_args &a, cudaStream_t st);
+int selscan_bwd_fast(const b200_selscan_bwd_args &a, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,694 @@
+// Generic selective scan (forward and backward) for sm_100a.
+//
+// Coverage kernel: every discretization, real or complex A, constant or
+// variable B/C, any dstate <= 256, any activation dtype, any sequence length.
+// One warp owns one (batch, channel) row and walks it in stages of 256
+// timesteps (8 consecutive timesteps per lane).  Inside a stage the recurrence
+//   h_t = a_t * h_{t-1} + b_t
+// is evaluated as a thread-serial scan over the lane's 8 items followed by a
+// warp-shuffle scan of the per-lane aggregates; the carry between stages lives
+// in shared memory.  The backward pass walks each 2048-step checkpoint chunk
+// twice: a forward sweep that rebuilds the state at every stage boundary from
+// the checkpoint tensor x, then a reverse sweep that recomputes the states of
+// one stage, runs the adjoint recurrence g_t = conj(a_{t+1}) g_{t+1} + seed_t
+// as a reverse warp scan and emits all gradients.
+//
+// Behaviour follows csrc/selective_scan/selective_scan.cuh:73-382 and
+// csrc/selective_scan/selective_scan_backward.cuh:86-845 of lrnnx (math
+// restated in include/lrnnx_b200.h and DESIGN.md, not the code structure).
+#include "common.cuh"
+#include <type_traits>
+
+namespace b200 {
+namespace {
+
+constexpr int GI = 8;               // timesteps per lane per stage
+constexpr int GSTAGE = 32 * GI;     // 256 timesteps per warp stage
+constexpr int GWARPS = 4;           // rows per CTA
+constexpr int SCR = 2 * GSTAGE + (2 * GSTAGE) / 32;   // transposition scratch (floats) per warp
+constexpr int STAGES_PER_CHUNK = kChunk / GSTAGE;      // 8
+
+__device__ __forceinline__ int padi(int i) { return i + (i >> 5); }
+
+// Coalesced (lane-striped) global read of I*32 consecutive scalars starting at
+// element `off + t0`, returned lane-blocked (lane holds I consecutive scalars).
+template <int I>
+__device__ __forceinline__ void load_blocked(const void *base, int dtype, int64_t off, int t0, int tend,
+                                             float *scr, float (&dst)[I], int lane) {
+#pragma unroll
+  for (int j = 0; j < I; ++j) {
+    int idx = j * 32 + lane;
+    int t = t0 + idx;
+    scr[padi(idx)] = t < tend ? ld_act(base, dtype, off + t) : 0.f;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < I; ++i) dst[i] = scr[padi(lane * I + i)];
+  __syncwarp();
+}
+
+template <int I>
+__device__ __forceinline__ void store_blocked(void *base, int dtype, int64_t off, int t0, int tend, float *scr,
+                                              const float (&src)[I], int lane) {
+#pragma unroll
+  for (int i = 0; i < I; ++i) scr[padi(lane * I + i)] = src[i];
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < I; ++j) {
+    int idx = j * 32 + lane;
+    int t = t0 + idx;
+    if (t < tend) st_act(base, dtype, off + t, scr[padi(idx)]);
+  }
+  __syncwarp();
+}
+
+// lane-blocked values -> coalesced float atomics (used for variable dB / dC)
+template <int I>
+__device__ __forceinline__ void atomic_add_blocked(float *base, int64_t off, int t0, int tend, float *scr,
+                                                   const float (&src)[I], int lane) {
+#pragma unroll
+  for (int i = 0; i < I; ++i) scr[padi(lane * I + i)] = src[i];
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < I; ++j) {
+    int idx = j * 32 + lane;
+    int t = t0 + idx;
+    if (t < tend) atomicAdd(base + off + t, scr[padi(idx)]);
+  }
+  __syncwarp();
+}
+
+// variable B / C of one state for one stage, as V per timestep
+template <typename V>
+__device__ __forceinline__ void load_bc(const void *base, int dtype, int64_t off, int t0, int L, float *scr,
+                                        V (&dst)[GI], int lane) {
+  if constexpr (std::is_same<V, float>::value) {
+    load_blocked<GI>(base, dtype, off, t0, L, scr, dst, lane);
+  } else {
+    float tmp[2 * GI];
+    load_blocked<2 * GI>(base, dtype, off, 2 * t0, 2 * L, scr, tmp, lane);
+#pragma unroll
+    for (int i = 0; i < GI; ++i) dst[i] = cf(tmp[2 * i], tmp[2 * i + 1]);
+  }
+}
+
+__device__ __forceinline__ float rmulc(float g, float x) { return g * x; }                  // Re(g*conj(x))
+__device__ __forceinline__ float rmulc(cf g, cf x) { return g.re * x.re + g.im * x.im; }
+__device__ __forceinline__ float cmulc(float g, float x) { return g * x; }                  // g*conj(x)
+__device__ __forceinline__ cf cmulc(cf g, cf x) { return g * conj(x); }
+__device__ __forceinline__ float vmul(float a, float b) { return a * b; }
+__device__ __forceinline__ cf vmul(cf a, cf b) { return a * b; }
+__device__ __forceinline__ cf vmul(cf a, float b) { return a * b; }
+__device__ __forceinline__ cf vmul(float a, cf b) { return a * b; }
+__device__ __forceinline__ float vexp(float x) { return expf(x); }
+__device__ __forceinline__ cf vexp(cf x) { return cexp(x); }
+__device__ __forceinline__ float vinv(float x) { return 1.f / x; }
+__device__ __forceinline__ cf vinv(cf x) { return cf(1.f, 0.f) / x; }
+__device__ __forceinline__ float vexpm1_over(float x, float A) { return expm1f(x) / A; }    // (exp(x)-1)/A
+__device__ __forceinline__ cf vexpm1_over(cf x, cf A) { return (cexp(x) - cf(1.f, 0.f)) / A; }
+__device__ __forceinline__ void atomic_add_v(float *p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add_v(cf *p, cf v) {
+  atomicAdd(&p->re, v.re);
+  atomicAdd(&p->im, v.im);
+}
+
+// Discrete transition a_t and input coefficient k_t (b_t = k_t * u_t * B_t) of
+// one (timestep, state) pair; csrc/selective_scan/selective_scan.cuh:231-302.
+template <int DM, typename V>
+__device__ __forceinline__ void disc_coef(V A, float logA, float d, float dA, V &a, V &k) {
+  if constexpr (DM == B200_DISC_MAMBA) {
+    a = vexp(vmul(A, dA));
+    k = V(d);
+  } else if constexpr (DM == B200_DISC_DIRAC) {
+    a = vexp(vmul(A, dA));
+    k = V(1.f);
+  } else if constexpr (DM == B200_DISC_ZOH) {
+    a = vexp(vmul(A, dA));
+    k = vexpm1_over(vmul(A, d), A);
+  } else if constexpr (DM == B200_DISC_BILINEAR) {
+    V vA = vmul(A, 0.5f * dA);
+    a = (V(1.f) + vA) * vinv(V(1.f) - vA);
+    k = vmul(vinv(V(1.f) - vmul(A, 0.5f * d)), d);
+  } else if constexpr (DM == B200_DISC_S7) {
+    a = V(1.f - 1.f / (d * d + 0.5f));
+    k = V(1.f);
+  } else {   // RGLRU: a = A^d, k = sqrt(1 - a^2) (B ignored by the caller)
+    float ar = expf(d * logA);
+    a = V(ar);
+    k = V(sqrtf(1.f - ar * ar));
+  }
+}
+
+template <typename V> struct RowCtx {
+  int b, d, g, lane;
+  int64_t row;
+};
+
+// ---------------------------------------------------------------- forward
+template <int DM, bool CPLX>
+__global__ void __launch_bounds__(GWARPS * 32) selscan_fwd_generic_kernel(const b200_selscan_fwd_args p) {
+  using V = typename std::conditional<CPLX, cf, float>::type;
+  extern __shared__ __align__(16) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * GWARPS + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int g = d / (p.dim / p.n_groups);
+  const int N = p.dstate, L = p.seqlen, dt = p.dtype;
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  const int per_warp = SCR + 2 * N * (CPLX ? 2 : 1);
+  float *scr = smem + warp * per_warp;
+  V *carryP = reinterpret_cast<V *>(scr + SCR);
+  V *carryH = carryP + N;
+
+  const int64_t u_off = (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+  const int64_t dl_off = (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const int64_t dA_off = (int64_t)b * p.deltaA_bs + (int64_t)d * p.deltaA_ds;
+  const int64_t z_off = (int64_t)b * p.z_bs + (int64_t)d * p.z_ds;
+  const int64_t o_off = (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const int64_t oz_off = (int64_t)b * p.out_z_bs + (int64_t)d * p.out_z_ds;
+  const V *Ap = reinterpret_cast<const V *>(p.A) + (int64_t)d * p.A_ds;
+  const V *Bc = reinterpret_cast<const V *>(p.B) + (int64_t)d * p.B_gs;
+  const V *Cc = reinterpret_cast<const V *>(p.C) + (int64_t)d * p.C_gs;
+  const int64_t Bv_off = (int64_t)b * p.B_bs + (int64_t)g * p.B_gs;
+  const int64_t Cv_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  V *xrow = reinterpret_cast<V *>(p.x) + row * n_chunks * 2 * N;
+  const float Dval = p.D ? reinterpret_cast<const float *>(p.D)[d] : 0.f;
+  const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
+  const bool varB = p.var_B && DM != B200_DISC_RGLRU;   // RGLRU ignores B in the recurrence
+  const bool constB = !p.var_B;
+
+  const int nstages = (L + GSTAGE - 1) / GSTAGE;
+  for (int s = 0; s < nstages; ++s) {
+    const int t0 = s * GSTAGE;
+    float u[GI], dl[GI], dAv[GI], y[GI];
+    load_blocked<GI>(p.u, dt, u_off, t0, L, scr, u, lane);
+    load_blocked<GI>(p.delta, dt, dl_off, t0, L, scr, dl, lane);
+    if (p.deltaA) load_blocked<GI>(p.deltaA, dt, dA_off, t0, L, scr, dAv, lane);
+#pragma unroll
+    for (int i = 0; i < GI; ++i) {
+      dl[i] += bias;
+      if (p.delta_softplus) dl[i] = softplus20(dl[i]);
+      if (!p.deltaA) dAv[i] = dl[i];
+      y[i] = Dval * u[i];
+    }
+    for (int n = 0; n < N; ++n) {
+      const V An = Ap[(int64_t)n * p.A_ns];
+      float logA = 0.f;
+      if constexpr (DM == B200_DISC_RGLRU) logA = logf(realpart(An));
+      V Bv[GI], Cv[GI];
+      // C factor applied to the state: C (variable or constant) times constant B when B is constant
+      V cfix = V(1.f);
+      if (constB) cfix = Bc[(int64_t)n * p.B_ns];
+      if (!p.var_C) cfix = cfix * Cc[(int64_t)n * p.C_ns];
+      if (varB) load_bc<V>(p.B, dt, Bv_off + (int64_t)n * p.B_ns, t0, L, scr, Bv, lane);
+      if (p.var_C) {
+        load_bc<V>(p.C, dt, Cv_off + (int64_t)n * p.C_ns, t0, L, scr, Cv, lane);
+#pragma unroll
+        for (int i = 0; i < GI; ++i) Cv[i] = Cv[i] * cfix;
+      } else {
+#pragma unroll
+        for (int i = 0; i < GI; ++i) Cv[i] = cfix;
+      }
+      V a[GI], h[GI];
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        V k;
+        disc_coef<DM, V>(An, logA, dl[i], dAv[i], a[i], k);
+        h[i] = vmul(k, u[i]);
+        if (varB) h[i] = h[i] * Bv[i];
+        if (t0 + lane * GI + i >= L) { a[i] = V(1.f); h[i] = V(0.f); }
+      }
+      // thread-serial inclusive scan; a[] becomes the running product
+      V P = a[0], hh = h[0];
+#pragma unroll
+      for (int i = 1; i < GI; ++i) {
+        hh = a[i] * hh + h[i];
+        P = P * a[i];
+        h[i] = hh;
+        a[i] = P;
+      }
+      // warp inclusive scan of the per-lane aggregates
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        V Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+        if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+      }
+      V Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
+      if (lane == 0) { Pex = V(1.f); hex = V(0.f); }
+      V Pc = V(1.f), hc = V(0.f);
+      if (s > 0) { Pc = carryP[n]; hc = carryH[n]; }
+      const V hin = Pex * hc + hex;   // state entering this lane's first item
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        V hv = a[i] * hin + h[i];
+        if constexpr (CPLX) y[i] += 2.f * (hv * Cv[i]).re;
+        else y[i] += hv * Cv[i];
+      }
+      const V Ptot = shfl_idx(P, 31), htot = shfl_idx(hh, 31);
+      const V Pn = Pc * Ptot, hn = Ptot * hc + htot;
+      __syncwarp();
+      if (lane == 0) {
+        carryP[n] = Pn;
+        carryH[n] = hn;
+        if (((t0 + GSTAGE) % kChunk) == 0 || s == nstages - 1) {
+          V *xr = xrow + (int64_t)(t0 / kChunk) * 2 * N;
+          xr[2 * n] = Pn;
+          xr[2 * n + 1] = hn;
+        }
+      }
+      __syncwarp();
+    }
+    store_blocked<GI>(p.out, dt, o_off, t0, L, scr, y, lane);
+    if (p.z) {
+      float zz[GI];
+      load_blocked<GI>(p.z, dt, z_off, t0, L, scr, zz, lane);
+#pragma unroll
+      for (int i = 0; i < GI; ++i) y[i] *= zz[i] * sigmoidf_(zz[i]);
+      store_blocked<GI>(p.out_z, dt, oz_off, t0, L, scr, y, lane);
+    }
+  }
+}
+
+// --------------------------------------------------------------- backward
+template <int DM, bool CPLX>
+__global__ void __launch_bounds__(GWARPS * 32) selscan_bwd_generic_kernel(const b200_selscan_bwd_args q) {
+  using V = typename std::conditional<CPLX, cf, float>::type;
+  constexpr int VF = CPLX ? 2 : 1;
+  const b200_selscan_fwd_args &p = q.f;
+  extern __shared__ __align__(16) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * GWARPS + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int g = d / (p.dim / p.n_groups);
+  const int N = p.dstate, L = p.seqlen, dt = p.dtype;
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  // per-warp shared memory: scratch | hb[N][8] | anext[N] | gcar[N] | accA[N] | accBC[N]
+  const int per_warp = SCR + N * VF * (STAGES_PER_CHUNK + 4);
+  float *scr = smem + warp * per_warp;
+  V *hb = reinterpret_cast<V *>(scr + SCR);
+  V *anext = hb + N * STAGES_PER_CHUNK;
+  V *gcar = anext + N;
+  V *accA = gcar + N;
+  V *accBC = accA + N;
+
+  const int64_t u_off = (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+  const int64_t dl_off = (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const int64_t dA_off = (int64_t)b * p.deltaA_bs + (int64_t)d * p.deltaA_ds;
+  const int64_t z_off = (int64_t)b * p.z_bs + (int64_t)d * p.z_ds;
+  const int64_t o_off = (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const int64_t oz_off = (int64_t)b * p.out_z_bs + (int64_t)d * p.out_z_ds;
+  const int64_t do_off = (int64_t)b * q.dout_bs + (int64_t)d * q.dout_ds;
+  const int64_t du_off = (int64_t)b * q.du_bs + (int64_t)d * q.du_ds;
+  const int64_t dd_off = (int64_t)b * q.ddelta_bs + (int64_t)d * q.ddelta_ds;
+  const int64_t ddA_off = (int64_t)b * q.ddeltaA_bs + (int64_t)d * q.ddeltaA_ds;
+  const int64_t dz_off = (int64_t)b * q.dz_bs + (int64_t)d * q.dz_ds;
+  const V *Ap = reinterpret_cast<const V *>(p.A) + (int64_t)d * p.A_ds;
+  const V *Bc = reinterpret_cast<const V *>(p.B) + (int64_t)d * p.B_gs;
+  const V *Cc = reinterpret_cast<const V *>(p.C) + (int64_t)d * p.C_gs;
+  const int64_t Bv_off = (int64_t)b * p.B_bs + (int64_t)g * p.B_gs;
+  const int64_t Cv_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  const int64_t dBv_off = (int64_t)b * q.dB_bs + (int64_t)g * q.dB_gs;
+  const int64_t dCv_off = (int64_t)b * q.dC_bs + (int64_t)g * q.dC_gs;
+  const V *xrow = p.x ? reinterpret_cast<const V *>(p.x) + row * n_chunks * 2 * N : nullptr;
+  const float Dval = p.D ? reinterpret_cast<const float *>(p.D)[d] : 0.f;
+  const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
+  const bool varB = p.var_B && DM != B200_DISC_RGLRU;
+  const bool constB = !p.var_B;
+  const bool has_dA_in = p.deltaA != nullptr;
+
+  for (int n = lane; n < N; n += 32) { accA[n] = V(0.f); accBC[n] = V(0.f); gcar[n] = V(0.f); anext[n] = V(1.f); }
+  __syncwarp();
+  float dD_acc = 0.f, dbias_acc = 0.f;
+
+  for (int c = n_chunks - 1; c >= 0; --c) {
+    const int cbase = c * kChunk;
+    const int clen = min(kChunk, L - cbase);
+    const int nst = (clen + GSTAGE - 1) / GSTAGE;
+    // ---- sweep 1: states at the stage boundaries of this chunk
+    for (int n = lane; n < N; n += 32) hb[n * STAGES_PER_CHUNK] = (c > 0) ? xrow[(int64_t)(c - 1) * 2 * N + 2 * n + 1] : V(0.f);
+    __syncwarp();
+    for (int s = 0; s + 1 < nst; ++s) {
+      const int t0 = cbase + s * GSTAGE;
+      float u[GI], dl[GI], dAv[GI];
+      load_blocked<GI>(p.u, dt, u_off, t0, L, scr, u, lane);
+      load_blocked<GI>(p.delta, dt, dl_off, t0, L, scr, dl, lane);
+      if (has_dA_in) load_blocked<GI>(p.deltaA, dt, dA_off, t0, L, scr, dAv, lane);
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        dl[i] += bias;
+        if (p.delta_softplus) dl[i] = softplus20(dl[i]);
+        if (!has_dA_in) dAv[i] = dl[i];
+      }
+      for (int n = 0; n < N; ++n) {
+        const V An = Ap[(int64_t)n * p.A_ns];
+        float logA = 0.f;
+        if constexpr (DM == B200_DISC_RGLRU) logA = logf(realpart(An));
+        V Bv[GI];
+        if (varB) load_bc<V>(p.B, dt, Bv_off + (int64_t)n * p.B_ns, t0, L, scr, Bv, lane);
+        V P = V(1.f), hh = V(0.f);
+#pragma unroll
+        for (int i = 0; i < GI; ++i) {
+          V a, k;
+          disc_coef<DM, V>(An, logA, dl[i], dAv[i], a, k);
+          V bb = vmul(k, u[i]);
+          if (varB) bb = bb * Bv[i];
+          if (t0 + lane * GI + i >= L) { a = V(1.f); bb = V(0.f); }
+          hh = a * hh + bb;
+          P = P * a;
+        }
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          V Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+          if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+        }
+        if (lane == 31) hb[n * STAGES_PER_CHUNK + s + 1] = P * hb[n * STAGES_PER_CHUNK + s] + hh;
+        __syncwarp();
+      }
+    }
+    // ---- sweep 2: reverse over the stages, gradients
+    for (int s = nst - 1; s >= 0; --s) {
+      const int t0 = cbase + s * GSTAGE;
+      float u[GI], dl[GI], dAv[GI], dy[GI], du[GI], ddl[GI], ddA[GI];
+      load_blocked<GI>(p.u, dt, u_off, t0, L, scr, u, lane);
+      load_blocked<GI>(p.delta, dt, dl_off, t0, L, scr, dl, lane);
+      if (has_dA_in) load_blocked<GI>(p.deltaA, dt, dA_off, t0, L, scr, dAv, lane);
+      load_blocked<GI>(q.dout, dt, do_off, t0, L, scr, dy, lane);
+      float sig[GI];   // d softplus / d raw
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        float raw = dl[i] + bias;
+        sig[i] = 1.f;
+        if (p.delta_softplus) {
+          dl[i] = softplus20(raw);
+          sig[i] = raw <= 20.f ? sigmoidf_(raw) : 1.f;
+        } else {
+          dl[i] = raw;
+        }
+        if (!has_dA_in) dAv[i] = dl[i];
+        ddl[i] = 0.f;
+        ddA[i] = 0.f;
+      }
+      if (p.z) {
+        float zz[GI], oo[GI], dzv[GI];
+        load_blocked<GI>(p.z, dt, z_off, t0, L, scr, zz, lane);
+        load_blocked<GI>(p.out, dt, o_off, t0, L, scr, oo, lane);
+#pragma unroll
+        for (int i = 0; i < GI; ++i) {
+          float sg = sigmoidf_(zz[i]);
+          float silu = zz[i] * sg;
+          dzv[i] = dy[i] * oo[i] * sg * (1.f + zz[i] * (1.f - sg));
+          dy[i] *= silu;
+          oo[i] *= silu;
+        }
+        store_blocked<GI>(q.dz, dt, dz_off, t0, L, scr, dzv, lane);
+        if (p.out_z) store_blocked<GI>(p.out_z, dt, oz_off, t0, L, scr, oo, lane);
+      }
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        du[i] = Dval * dy[i];
+        dD_acc += dy[i] * u[i];
+      }
+      for (int n = 0; n < N; ++n) {
+        const V An = Ap[(int64_t)n * p.A_ns];
+        float logA = 0.f;
+        if constexpr (DM == B200_DISC_RGLRU) logA = logf(realpart(An));
+        V Bcn = V(1.f), Ccn = V(1.f);
+        if (constB) Bcn = Bc[(int64_t)n * p.B_ns];
+        if (!p.var_C) Ccn = Cc[(int64_t)n * p.C_ns];
+        V Bv[GI], Cv[GI];
+        if (varB) load_bc<V>(p.B, dt, Bv_off + (int64_t)n * p.B_ns, t0, L, scr, Bv, lane);
+        else {
+#pragma unroll
+          for (int i = 0; i < GI; ++i) Bv[i] = V(1.f);
+        }
+        if (p.var_C) load_bc<V>(p.C, dt, Cv_off + (int64_t)n * p.C_ns, t0, L, scr, Cv, lane);
+        else {
+#pragma unroll
+          for (int i = 0; i < GI; ++i) Cv[i] = V(1.f);
+        }
+        const V cfix = (constB ? Bcn : V(1.f)) * (p.var_C ? V(1.f) : Ccn);
+        // forward recompute
+        V a[GI], kk[GI], h[GI], cp[GI];   // a: transition, kk: input coef, h: state, cp: running product
+#pragma unroll
+        for (int i = 0; i < GI; ++i) {
+          disc_coef<DM, V>(An, logA, dl[i], dAv[i], a[i], kk[i]);
+          if (t0 + lane * GI + i >= L) { a[i] = V(1.f); kk[i] = V(0.f); }
+        }
+        V P = V(1.f), hh = V(0.f);
+#pragma unroll
+        for (int i = 0; i < GI; ++i) {
+          V bb = vmul(kk[i], u[i]) * Bv[i];
+          hh = a[i] * hh + bb;
+          P = P * a[i];
+          h[i] = hh;
+          cp[i] = P;
+        }
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          V Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+          if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+        }
+        V Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
+        if (lane == 0) { Pex = V(1.f); hex = V(0.f); }
+        const V hstart = hb[n * STAGES_PER_CHUNK + s];
+        const V hin = Pex * hstart + hex;
+#pragma unroll
+        for (int i = 0; i < GI; ++i) h[i] = cp[i] * hin + h[i];
+        // adjoint: reverse scan. an[i] = conj(a_{t+1})
+        V a_first_next = shfl_down(a[0], 1);
+        const V an_stage = anext[n];
+        if (lane == 31) a_first_next = an_stage;
+        V gl[GI], qs[GI];
+        {
+          V gg = V(0.f), Q = V(1.f);
+#pragma unroll
+          for (int i = GI - 1; i >= 0; --i) {
+            const V an = conj(i == GI - 1 ? a_first_next : a[i + 1]);
+            V seed;
+            if constexpr (CPLX) seed = (2.f * dy[i]) * conj(Cv[i] * cfix);
+            else seed = dy[i] * (Cv[i] * cfix);
+            gg = an * gg + seed;
+            Q = Q * an;
+            gl[i] = gg;
+            qs[i] = Q;
+          }
+          // reverse warp scan of (Q, gg): gg = adjoint at the lane's first item
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            V Qr = shfl_down(Q, off), gr = shfl_down(gg, off);
+            if (lane + off < 32) { gg = gg + Q * gr; Q = Q * Qr; }
+          }
+          const V gc = gcar[n];
+          V g_right = shfl_down(gg, 1), Q_right = shfl_down(Q, 1);
+          V gin = g_right + Q_right * gc;    // adjoint at the first item of the next lane
+          if (lane == 31) gin = gc;
+          const V g0 = shfl_idx(gg, 0) + shfl_idx(Q, 0) * gc;
+          const V a0 = shfl_idx(a[0], 0);
+          __syncwarp();
+          if (lane == 0) { gcar[n] = g0; anext[n] = a0; }
+#pragma unroll
+          for (int i = 0; i < GI; ++i) gl[i] = gl[i] + qs[i] * gin;
+        }
+        // gradients
+        V dA_l = V(0.f), dBC_l = V(0.f);
+        V dBv[GI], dCv[GI];
+#pragma unroll
+        for (int i = 0; i < GI; ++i) {
+          const V G = gl[i];
+          const V hprev = (i == 0) ? hin : h[i - 1];
+          const V beta = vmul(kk[i], u[i]) * Bv[i];
+          const float dv = dl[i], dav = dAv[i], uv = u[i];
+          float d_dl = 0.f, d_dA = 0.f;
+          V dBvi = V(0.f);
+          if constexpr (DM == B200_DISC_MAMBA) {
+            const float gb = rmulc(G, Bv[i]);
+            du[i] += gb * dv;
+            d_dl = gb * uv;
+            const V ah = h[i] - beta;
+            d_dA = rmulc(G, An * ah);
+            dA_l = dA_l + cmulc(G, vmul(ah, dav));
+            dBvi = vmul(G, dv * uv);
+          } else if constexpr (DM == B200_DISC_DIRAC) {
+            du[i] += rmulc(G, Bv[i]);
+            const V ah = h[i] - beta;
+            d_dA = rmulc(G, An * ah);
+            dA_l = dA_l + cmulc(G, vmul(ah, dav));
+            dBvi = vmul(G, uv);
+          } else if constexpr (DM == B200_DISC_ZOH) {
+            const V E = vexp(vmul(An, dv));
+            const V K = kk[i];
+            du[i] += rmulc(G, K * Bv[i]);
+            d_dl = rmulc(G, vmul(E * Bv[i], uv));
+            const V ah = h[i] - beta;
+            d_dA = rmulc(G, An * ah);
+            dA_l = dA_l + cmulc(G, vmul(ah, dav)) + cmulc(G, vmul(Bv[i], uv) * ((vmul(E, dv) - K) * vinv(An)));
+            dBvi = cmulc(G, vmul(K, uv));
+          } else if constexpr (DM == B200_DISC_BILINEAR) {
+            const V r = vinv(V(1.f) - vmul(An, 0.5f * dv));
+            const V rA = vinv(V(1.f) - vmul(An, 0.5f * dav));
+            const V r2 = r * r, rA2 = rA * rA;
+            du[i] += rmulc(G, kk[i] * Bv[i]);
+            d_dl = rmulc(G, vmul(r2 * Bv[i], uv));
+            d_dA = rmulc(G, hprev * An * rA2);
+            dA_l = dA_l + cmulc(G, vmul(hprev * rA2, dav) + vmul(Bv[i] * r2, uv * 0.5f * dv * dv));
+            dBvi = cmulc(G, vmul(kk[i], uv));
+          } else if constexpr (DM == B200_DISC_S7) {
+            du[i] += rmulc(G, Bv[i]);
+            const float sq = dv * dv + 0.5f;
+            d_dl = realpart(G) * realpart(hprev) * (2.f * dv / (sq * sq));
+            dBvi = vmul(G, uv);
+          } else {   // RGLRU
+            const float ar = realpart(a[i]), sr = realpart(kk[i]);
+            du[i] += realpart(G) * sr;
+            if (dv > 0.f && t0 + lane * GI + i < L) {
+              const float Ga = realpart(G) * (realpart(hprev) - ar * uv / sr);
+              d_dl = Ga * ar * logA;
+              dA_l = dA_l + V(Ga * dv * ar / realpart(An));
+            }
+          }
+          if (DM == B200_DISC_S7 || DM == B200_DISC_RGLRU || !has_dA_in) ddl[i] += d_dl + d_dA;
+          else { ddl[i] += d_dl; ddA[i] += d_dA; }
+          dBv[i] = dBvi;
+          // C-side gradients
+          V hs = h[i];
+          if constexpr (CPLX) {
+            const V t = (2.f * dy[i]) * conj(hs);
+            dCv[i] = constB ? t * conj(Bcn) : t;
+            if (constB) dBC_l = dBC_l + (p.var_C ? t * conj(Cv[i]) : t);
+            else if (!p.var_C) dBC_l = dBC_l + t;
+          } else {
+            const float t = dy[i] * hs;
+            dCv[i] = constB ? t * Bcn : t;
+            if (constB) dBC_l = dBC_l + (p.var_C ? t * Cv[i] : t);
+            else if (!p.var_C) dBC_l = dBC_l + t;
+          }
+        }
+        if (p.var_B && DM != B200_DISC_RGLRU) {
+          float *dBp = reinterpret_cast<float *>(q.dB);
+          if constexpr (CPLX) {
+            float tmp[2 * GI];
+#pragma unroll
+            for (int i = 0; i < GI; ++i) { tmp[2 * i] = dBv[i].re; tmp[2 * i + 1] = dBv[i].im; }
+            atomic_add_blocked<2 * GI>(dBp, dBv_off + (int64_t)n * q.dB_ns, 2 * t0, 2 * L, scr, tmp, lane);
+          } else {
+            atomic_add_blocked<GI>(dBp, dBv_off + (int64_t)n * q.dB_ns, t0, L, scr, dBv, lane);
+          }
+        }
+        if (p.var_C) {
+          float *dCp = reinterpret_cast<float *>(q.dC);
+          if constexpr (CPLX) {
+            float tmp[2 * GI];
+#pragma unroll
+            for (int i = 0; i < GI; ++i) { tmp[2 * i] = dCv[i].re; tmp[2 * i + 1] = dCv[i].im; }
+            atomic_add_blocked<2 * GI>(dCp, dCv_off + (int64_t)n * q.dC_ns, 2 * t0, 2 * L, scr, tmp, lane);
+          } else {
+            atomic_add_blocked<GI>(dCp, dCv_off + (int64_t)n * q.dC_ns, t0, L, scr, dCv, lane);
+          }
+        }
+        dA_l = warp_sum(dA_l);
+        dBC_l = warp_sum(dBC_l);
+        if (lane == 0) {
+          accA[n] = accA[n] + dA_l;
+          accBC[n] = accBC[n] + dBC_l;
+        }
+        __syncwarp();
+      }
+      // chain through softplus, write per-timestep gradients
+#pragma unroll
+      for (int i = 0; i < GI; ++i) {
+        ddl[i] *= sig[i];
+        if (t0 + lane * GI + i < L) dbias_acc += ddl[i];
+      }
+      store_blocked<GI>(q.du, dt, du_off, t0, L, scr, du, lane);
+      store_blocked<GI>(q.ddelta, dt, dd_off, t0, L, scr, ddl, lane);
+      if (has_dA_in) store_blocked<GI>(q.ddeltaA, dt, ddA_off, t0, L, scr, ddA, lane);
+    }
+  }
+  // row-level reductions
+  dD_acc = warp_sum(dD_acc);
+  dbias_acc = warp_sum(dbias_acc);
+  if (lane == 0) {
+    if (q.dD) atomicAdd(reinterpret_cast<float *>(q.dD) + d, dD_acc);
+    if (q.ddelta_bias) atomicAdd(reinterpret_cast<float *>(q.ddelta_bias) + d, dbias_acc);
+  }
+  __syncwarp();
+  V *dAp = reinterpret_cast<V *>(q.dA) + (int64_t)d * q.dA_ds;
+  for (int n = lane; n < N; n += 32) {
+    atomic_add_v(dAp + (int64_t)n * q.dA_ns, accA[n]);
+    const V bc = accBC[n];
+    if (constB) {
+      V *dBp = reinterpret_cast<V *>(q.dB) + (int64_t)d * q.dB_gs + (int64_t)n * q.dB_ns;
+      atomic_add_v(dBp, p.var_C ? bc : bc * conj(Cc[(int64_t)n * p.C_ns]));
+    }
+    if (!p.var_C) {
+      V *dCp = reinterpret_cast<V *>(q.dC) + (int64_t)d * q.dC_gs + (int64_t)n * q.dC_ns;
+      atomic_add_v(dCp, constB ? bc * conj(Bc[(int64_t)n * p.B_ns]) : bc);
+    }
+  }
+}
+
+template <typename K> int set_smem(K kernel, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  }
+  return 0;
+}
+
+template <int DM, bool CPLX> int launch_fwd(const b200_selscan_fwd_args &a, cudaStream_t st) {
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = (size_t)GWARPS * (SCR + 2 * a.dstate * (CPLX ? 2 : 1)) * sizeof(float);
+  auto k = selscan_fwd_generic_kernel<DM, CPLX>;
+  if (int e = set_smem(k, smem)) return e;
+  k<<<(unsigned)((rows + GWARPS - 1) / GWARPS), GWARPS * 32, smem, st>>>(a);
+  return launch_status();
+}
+template <int DM, bool CPLX> int launch_bwd(const b200_selscan_bwd_args &a, cudaStream_t st) {
+  const int64_t rows = (int64_t)a.f.batch * a.f.dim;
+  const size_t smem =
+      (size_t)GWARPS * (SCR + a.f.dstate * (CPLX ? 2 : 1) * (STAGES_PER_CHUNK + 4)) * sizeof(float);
+  auto k = selscan_bwd_generic_kernel<DM, CPLX>;
+  if (int e = set_smem(k, smem)) return e;
+  k<<<(unsigned)((rows + GWARPS - 1) / GWARPS), GWARPS * 32, smem, st>>>(a);
+  return launch_status();
+}
+
+}  // namespace
+
+int selscan_fwd_generic(const b200_selscan_fwd_args &a, cudaStream_t st) {
+#define B200_CASE(DM)                                                  \
+  case DM:                                                             \
+    return a.is_complex ? launch_fwd<DM, true>(a, st) : launch_fwd<DM, false>(a, st);
+  switch (a.method) {
+    B200_CASE(B200_DISC_ZOH)
+    B200_CASE(B200_DISC_BILINEAR)
+    B200_CASE(B200_DISC_DIRAC)
+    B200_CASE(B200_DISC_MAMBA)
+    case B200_DISC_RGLRU: return launch_fwd<B200_DISC_RGLRU, false>(a, st);
+    case B200_DISC_S7: return launch_fwd<B200_DISC_S7, false>(a, st);
+  }
+#undef B200_CASE
+  set_error("unknown discretization %d", a.method);
+  return B200_ERR_DTYPE;
+}
+
+int selscan_bwd_generic(const b200_selscan_bwd_args &a, cudaStream_t st) {
+#define B200_CASE(DM)                                                  \
+  case DM:                                                             \
+    return a.f.is_complex ? launch_bwd<DM, true>(a, st) : launch_bwd<DM, false>(a, st);
+  switch (a.f.method) {
+    B200_CASE(B200_DISC_ZOH)
+    B200_CASE(B200_DISC_BILINEAR)
+    B200_CASE(B200_DISC_DIRAC)
+    B200_CASE(B200_DISC_MAMBA)
+    case B200_DISC_RGLRU: return launch_bwd<B200_DISC_RGLRU, false>(a, st);
+    case B200_DISC_S7: return launch_bwd<B200_DISC_S7, false>(a, st);
+  }
+#undef B200_CASE
+  set_error("unknown discretization %d", a.f.method);
+  return B200_ERR_DTYPE;
+}
+
+}  // namespace b200
