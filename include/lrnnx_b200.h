@@ -175,6 +175,10 @@ typedef struct b200_simpscan_args {
 int b200_simpscan_fwd(const b200_simpscan_args *args, void *stream);
 int b200_simpscan_bwd(const b200_simpscan_args *args, void *stream);
 
+/* Diagnostic: non-zero after a kernel abandoned a bounded wait on a shared-memory
+ * barrier (its outputs are then invalid).  Synchronises the device. */
+int b200_device_status(void);
+
 /* ------------------------------------------------------------------------
  * One-token state update used in decoding.
  * Replaces selective_state_update and its Triton kernel
@@ -216,20 +220,29 @@ int b200_ssu_step(const b200_ssu_args *args, void *stream);
  * S4 structured kernels (contiguous tensors).
  * Replace cauchy_mult_sym_fwd/bwd and vand_log_mult_sym_fwd/bwd
  * (csrc/s4/cauchy.cpp:20-102, csrc/s4/cauchy_cuda.cu:34-368).
- *   Cauchy: v, w (batch, n) complex64 (n = half size, power of two in [1,1024]),
- *           z (seqlen) complex64, out/dout (batch, seqlen) complex64,
- *           dv, dw (batch, n) complex64 written (not accumulated).
- *   Vandermonde: v, x (batch, n) complex64, out/dout (batch, seqlen) float32,
- *           dv, dx (batch, n) complex64 written.
+ *   Cauchy: v, w (batch, n) complex64 (n = half size: one member of each
+ *           conjugate pair; any n >= 1), z (seqlen) complex64,
+ *           out/dout (batch, seqlen) complex64, dv, dw (batch, n) complex64.
+ *   Vandermonde: v, x (batch, n) complex64 (x passed in the `w` field),
+ *           out/dout (batch, seqlen) float32, dv, dx (batch, n) complex64
+ *           (dx returned in the `dw` field).
+ * The backward entry points reduce over the sequence in two passes: per-chunk
+ * partial sums go to `scratch` (caller-allocated device memory of at least
+ * b200_s4_bwd_scratch_bytes(batch, n, seqlen) bytes, 16-byte aligned; contents
+ * on entry are ignored), then a second kernel folds them into dv / dw in a fixed
+ * order, so results are deterministic.  dv / dw are overwritten.
  * ------------------------------------------------------------------------ */
 typedef struct b200_s4_args {
   int32_t batch, n, seqlen, reserved0;
-  const void *v, *z, *w;        /* Vandermonde: w is the exponent tensor x, z unused */
+  const void *v, *z, *w;
   void *out;
   const void *dout;
   void *dv, *dw;
+  void *scratch;
+  int64_t scratch_bytes;
 } b200_s4_args;
 
+int64_t b200_s4_bwd_scratch_bytes(int32_t batch, int32_t n, int32_t seqlen);
 int b200_cauchy_fwd(const b200_s4_args *args, void *stream);
 int b200_cauchy_bwd(const b200_s4_args *args, void *stream);
 int b200_vand_fwd(const b200_s4_args *args, void *stream);

@@ -19,7 +19,7 @@ HEADER = _PKG.parent / "include" / "lrnnx_b200.h"
 LIB_PATH = _PKG / "lib" / "liblrnnx_b200.so"
 
 ENTRY_POINTS = (
-    "b200_last_error", "b200_abi_version", "b200_sizeof",
+    "b200_last_error", "b200_abi_version", "b200_sizeof", "b200_device_status", "b200_s4_bwd_scratch_bytes",
     "b200_selscan_fwd", "b200_selscan_bwd", "b200_selscan_fixup",
     "b200_simpscan_fwd", "b200_simpscan_bwd",
     "b200_ssu_step",
@@ -76,7 +76,7 @@ def parse_header() -> tuple[dict, dict, list]:
                     raise ValueError(f"cannot parse field '{decl}' of {name}")
                 fields.append((var, ctype))
         structs[name] = type(name, (ctypes.Structure,), {"_fields_": fields})
-    functions = re.findall(r"^\s*(?:const\s+char\s*\*|int)\s*(b200_\w+)\s*\(", text, flags=re.M)
+    functions = re.findall(r"^\s*(?:const\s+char\s*\*|int|int64_t)\s*(b200_\w+)\s*\(", text, flags=re.M)
     return structs, enums, functions
 
 
@@ -107,7 +107,11 @@ def lib() -> ctypes.CDLL:
     handle.b200_abi_version.restype = ctypes.c_int
     handle.b200_sizeof.restype = ctypes.c_int
     handle.b200_sizeof.argtypes = [ctypes.c_char_p]
-    for fn in ENTRY_POINTS[3:]:
+    handle.b200_device_status.restype = ctypes.c_int
+    handle.b200_device_status.argtypes = []
+    handle.b200_s4_bwd_scratch_bytes.restype = ctypes.c_int64
+    handle.b200_s4_bwd_scratch_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    for fn in ENTRY_POINTS[5:]:
         f = getattr(handle, fn)
         f.restype = ctypes.c_int
         f.argtypes = [ctypes.c_void_p, ctypes.c_void_p]

@@ -53,9 +53,28 @@ __device__ __forceinline__ cf operator/(cf a, cf b) {
   float inv = 1.f / (b.re * b.re + b.im * b.im);
   return cf((a.re * b.re + a.im * b.im) * inv, (a.im * b.re - a.re * b.im) * inv);
 }
+// sin and cos to about 1 ulp for |x| up to ~1e5: three-constant Cody-Waite reduction by
+// pi/2 and the classic single-precision minimax polynomials on [-pi/4, pi/4].  The
+// recurrences multiply thousands of these factors, so the SFU approximations
+// (abs. error 2^-21) are not accurate enough for the phase.
+__device__ __forceinline__ void sincos_cw(float x, float &sn, float &cs) {
+  const float q = rintf(x * 0.6366197723675814f);
+  const int qi = (int)q;
+  float r = fmaf(-q, 1.5707962513e+0f, x);
+  r = fmaf(-q, 7.5497894159e-8f, r);
+  r = fmaf(-q, 5.3903029534e-15f, r);
+  const float r2 = r * r;
+  const float ps = fmaf(fmaf(fmaf(-1.9515295891e-4f, r2, 8.3321608736e-3f), r2, -1.6666654611e-1f), r2 * r, r);
+  const float pc = fmaf(fmaf(fmaf(2.443315711809948e-5f, r2, -1.388731625493765e-3f), r2, 4.166664568298827e-2f),
+                        r2 * r2, fmaf(-0.5f, r2, 1.f));
+  const float s0 = (qi & 1) ? pc : ps;
+  const float c0 = (qi & 1) ? ps : pc;
+  sn = (qi & 2) ? -s0 : s0;
+  cs = ((qi + 1) & 2) ? -c0 : c0;
+}
 __device__ __forceinline__ cf cexp(cf z) {
   float e = expf(z.re), s, c;
-  sincosf(z.im, &s, &c);
+  sincos_cw(z.im, s, c);
   return cf(e * c, e * s);
 }
 __device__ __forceinline__ float realpart(float a) { return a; }

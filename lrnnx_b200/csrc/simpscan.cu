@@ -1,0 +1,659 @@
+// Simplified (diagonal, complex-input) scan for sm_100a — forward and backward.
+//
+// Math (csrc/simplified_scan/simplified_scan.cuh:85-262 and
+// simplified_scan_backward.cuh:91-420 of lrnnx): per row (batch b, state p) and
+// state slot s,  h_t = a_t h_{t-1} + k_t u_t  with complex u and
+//   ZOH      a = exp(A dA_t),            k = (exp(A d_t) - 1) / A
+//   BILINEAR a = (1+A dA_t/2)/(1-A dA_t/2), k = d_t / (1 - A d_t/2)
+//   DIRAC    a = exp(A dA_t),            k = 1
+// (dA_t = deltaA_t when given, else d_t = delta_t), out_t = sum_s h_t B_s C_s.
+//
+// Forward: one warp per row, 10 consecutive timesteps per lane (320 per
+// stage).  Each warp runs its own 3-slot pipeline: lane 0 issues 1-D bulk
+// asynchronous copies (cp.async.bulk, the TMA engine) of the stage's u / delta
+// (/ deltaA) row segments into the warp's shared-memory slots and the warp
+// waits on the slot's mbarrier; the 80-byte per-lane stride makes the
+// lane-blocked 128-bit shared loads bank-conflict free.  The result is written
+// over the u slot and leaves through a bulk shared->global copy.  Rows whose
+// addresses are not 16-byte aligned, and the ragged last stage, use plain
+// loads/stores on the same layout.
+//
+// Backward: one 256-thread CTA per row walks the 2048-step checkpoint chunks
+// in reverse with 8 timesteps per thread, so a whole chunk is resident in
+// registers: states are recomputed from the chunk's checkpoint with a block
+// scan, the adjoint g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C) runs as a
+// reverse block scan, and du / ddelta / ddeltaA / dA / dB / dC follow.  Chunk
+// inputs are double-buffered in shared memory by bulk copies (a buffer is
+// refilled as soon as its chunk sits in registers); du and ddelta are staged in
+// a separate shared-memory area and leave through bulk stores.
+#include "common.cuh"
+#include "dispatch.h"
+
+namespace b200 {
+
+__device__ int g_simpscan_status = 0;   // set to non-zero when a bounded barrier wait expires
+
+namespace {
+
+template <int DM>
+__device__ __forceinline__ void s5_coef(cf A, float d, float dA, cf &a, cf &k) {
+  if constexpr (DM == B200_DISC_ZOH) {
+    a = cexp(A * dA);
+    k = (cexp(A * d) - cf(1.f, 0.f)) / A;
+  } else if constexpr (DM == B200_DISC_BILINEAR) {
+    const cf vA = A * (0.5f * dA);
+    a = (cf(1.f, 0.f) + vA) / (cf(1.f, 0.f) - vA);
+    k = (cf(1.f, 0.f) / (cf(1.f, 0.f) - A * (0.5f * d))) * d;
+  } else {
+    a = cexp(A * dA);
+    k = cf(1.f, 0.f);
+  }
+}
+
+// ------------------------------------------------------------------ forward
+constexpr int FI = 10;               // timesteps per lane
+constexpr int FSTAGE = 32 * FI;      // 320
+constexpr int FWARPS = 2;            // rows per CTA
+constexpr int FNS = 3;               // pipeline slots per warp
+constexpr int F_U_BYTES = FSTAGE * 8;
+constexpr int F_D_BYTES = FSTAGE * 4;
+
+template <int DM, bool HAS_DA>
+__global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200_simpscan_args p) {
+  constexpr int SLOT_BYTES = F_U_BYTES + F_D_BYTES * (HAS_DA ? 2 : 1);
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * FWARPS + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int L = p.seqlen, S = p.dstate;
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  // shared memory: [FWARPS][FNS] slots | [FWARPS][FNS] mbarriers | [FWARPS][2*S] carry
+  unsigned char *wbase = smem_raw + (size_t)warp * FNS * SLOT_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)FWARPS * FNS * SLOT_BYTES) + warp * FNS;
+  cf *carry = reinterpret_cast<cf *>(smem_raw + (size_t)FWARPS * FNS * SLOT_BYTES + FWARPS * FNS * 8) +
+              (size_t)warp * 2 * S;
+
+  const cf *u_row = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+  const float *d_row = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const float *dA_row = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs +
+                                     (int64_t)d * p.deltaA_ds
+                               : nullptr;
+  cf *o_row = reinterpret_cast<cf *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const cf *Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
+  const cf *Bp = reinterpret_cast<const cf *>(p.B) + (int64_t)d * p.B_ds;
+  const cf *Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
+  cf *xrow = reinterpret_cast<cf *>(p.x) + row * n_chunks * 2 * S;
+
+  bool tma_ok = ((reinterpret_cast<uintptr_t>(u_row) | reinterpret_cast<uintptr_t>(d_row) |
+                  reinterpret_cast<uintptr_t>(o_row)) & 15) == 0;
+  if (HAS_DA) tma_ok = tma_ok && ((reinterpret_cast<uintptr_t>(dA_row) & 15) == 0);
+
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < FNS; ++k) mbar_init(&bars[k], 1);
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  __syncwarp();
+
+  const int nst = (L + FSTAGE - 1) / FSTAGE;
+  auto slot_u = [&](int k) { return reinterpret_cast<cf *>(wbase + (size_t)k * SLOT_BYTES); };
+  auto slot_d = [&](int k) { return reinterpret_cast<float *>(wbase + (size_t)k * SLOT_BYTES + F_U_BYTES); };
+  auto slot_dA = [&](int k) {
+    return reinterpret_cast<float *>(wbase + (size_t)k * SLOT_BYTES + F_U_BYTES + F_D_BYTES);
+  };
+  auto is_async = [&](int s) { return tma_ok && (s + 1) * FSTAGE <= L; };
+  auto issue = [&](int s) {   // lane 0 only
+    if (s >= nst || !is_async(s)) return;
+    const int k = s % FNS;
+    const int64_t t0 = (int64_t)s * FSTAGE;
+    mbar_expect_tx(&bars[k], SLOT_BYTES);
+    bulk_g2s(slot_u(k), u_row + t0, F_U_BYTES, &bars[k]);
+    bulk_g2s(slot_d(k), d_row + t0, F_D_BYTES, &bars[k]);
+    if (HAS_DA) bulk_g2s(slot_dA(k), dA_row + t0, F_D_BYTES, &bars[k]);
+  };
+  if (lane == 0) { issue(0); issue(1); }
+
+  bool failed = false;
+  for (int s = 0; s < nst; ++s) {
+    const int k = s % FNS;
+    const int t0 = s * FSTAGE;
+    cf *su = slot_u(k);
+    float *sd = slot_d(k), *sdA = slot_dA(k);
+    if (is_async(s)) {
+      if (!mbar_wait(&bars[k], (uint32_t)((s / FNS) & 1))) { failed = true; break; }
+    } else {
+      // ragged or unaligned stage: coalesced plain loads into the same layout (after any bulk
+      // store that still reads this slot)
+      if (tma_ok) {
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+      }
+      for (int i = lane; i < FSTAGE; i += 32) {
+        const int t = t0 + i;
+        su[i] = t < L ? u_row[t] : cf(0.f, 0.f);
+        sd[i] = t < L ? d_row[t] : 0.f;
+        if (HAS_DA) sdA[i] = t < L ? dA_row[t] : 0.f;
+      }
+      __syncwarp();
+    }
+    cf u[FI];
+    float dl[FI], dAv[FI];
+    {
+      const float4 *s4 = reinterpret_cast<const float4 *>(su + lane * FI);
+#pragma unroll
+      for (int j = 0; j < FI / 2; ++j) {
+        const float4 v = s4[j];
+        u[2 * j] = cf(v.x, v.y);
+        u[2 * j + 1] = cf(v.z, v.w);
+      }
+      const float2 *d2 = reinterpret_cast<const float2 *>(sd + lane * FI);
+      const float2 *dA2 = reinterpret_cast<const float2 *>(sdA + lane * FI);
+#pragma unroll
+      for (int j = 0; j < FI / 2; ++j) {
+        const float2 v = d2[j];
+        dl[2 * j] = v.x;
+        dl[2 * j + 1] = v.y;
+        if (HAS_DA) {
+          const float2 w = dA2[j];
+          dAv[2 * j] = w.x;
+          dAv[2 * j + 1] = w.y;
+        } else {
+          dAv[2 * j] = v.x;
+          dAv[2 * j + 1] = v.y;
+        }
+      }
+    }
+    cf out[FI];
+#pragma unroll
+    for (int i = 0; i < FI; ++i) out[i] = cf(0.f, 0.f);
+    // a stage can hold both a chunk boundary and the row end (L % 2048 < 320); handle the second below
+    const int tend = min(L, t0 + FSTAGE);
+    const int boundary = (tend / kChunk) * kChunk;
+    const int ck_a = (boundary > t0) ? boundary - 1 - t0 : -1;           // chunk boundary inside the stage
+    const int ck_b = (tend == L && (L % kChunk) != 0) ? L - 1 - t0 : -1;  // row end (when not itself a boundary)
+    for (int si = 0; si < S; ++si) {
+      const cf An = Ap[(int64_t)si * p.A_ns];
+      const cf BC = Bp[(int64_t)si * p.B_ns] * Cp[(int64_t)si * p.C_ns];
+      cf a[FI], h[FI];
+#pragma unroll
+      for (int i = 0; i < FI; ++i) {
+        cf kk;
+        s5_coef<DM>(An, dl[i], dAv[i], a[i], kk);
+        h[i] = kk * u[i];
+        if (t0 + lane * FI + i >= L) { a[i] = cf(1.f, 0.f); h[i] = cf(0.f, 0.f); }
+      }
+      cf P = a[0], hh = h[0];
+#pragma unroll
+      for (int i = 1; i < FI; ++i) {
+        hh = a[i] * hh + h[i];
+        P = P * a[i];
+        h[i] = hh;
+        a[i] = P;
+      }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        cf Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+        if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+      }
+      cf Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
+      if (lane == 0) { Pex = cf(1.f, 0.f); hex = cf(0.f, 0.f); }
+      cf Pc = cf(1.f, 0.f), hc = cf(0.f, 0.f);
+      if (s > 0) { Pc = carry[2 * si]; hc = carry[2 * si + 1]; }
+      const cf hin = Pex * hc + hex;
+      const cf Pin = Pex * Pc;
+#pragma unroll
+      for (int i = 0; i < FI; ++i) {
+        const cf hv = a[i] * hin + h[i];
+        out[i] = out[i] + hv * BC;
+        const int pos = lane * FI + i;
+        if (pos == ck_a || pos == ck_b) {
+          cf *xr = xrow + (int64_t)((t0 + pos) / kChunk) * 2 * S;
+          xr[2 * si] = a[i] * Pin;
+          xr[2 * si + 1] = hv;
+        }
+      }
+      const cf Ptot = shfl_idx(P, 31), htot = shfl_idx(hh, 31);
+      __syncwarp();
+      if (lane == 0) {
+        carry[2 * si] = Pc * Ptot;
+        carry[2 * si + 1] = Ptot * hc + htot;
+      }
+      __syncwarp();
+    }
+    // prefetch stage s+2 into the slot used by stage s-1 (its bulk store must have finished reading)
+    if (lane == 0 && s + 2 < nst && is_async(s + 2)) {
+      bulk_wait_read<0>();
+      issue(s + 2);
+    }
+    if (is_async(s)) {
+      float4 *s4 = reinterpret_cast<float4 *>(su + lane * FI);
+#pragma unroll
+      for (int j = 0; j < FI / 2; ++j) s4[j] = make_float4(out[2 * j].re, out[2 * j].im, out[2 * j + 1].re, out[2 * j + 1].im);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        bulk_s2g(o_row + t0, su, F_U_BYTES);
+        bulk_commit();
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < FI; ++i) {
+        const int t = t0 + lane * FI + i;
+        if (t < L) o_row[t] = out[i];
+      }
+    }
+  }
+  if (lane == 0) bulk_wait<0>();
+  if (failed && lane == 0) atomicExch(&g_simpscan_status, 1);
+}
+
+// ----------------------------------------------------------------- backward
+constexpr int BT = 256;               // threads per CTA
+constexpr int BI = 8;                 // timesteps per thread (BT*BI = 2048 = one checkpoint chunk)
+constexpr int BWARPS = BT / 32;
+constexpr int B_U_BYTES = kChunk * 8;
+constexpr int B_D_BYTES = kChunk * 4;
+
+struct __align__(16) BwdShared {
+  cf wtot_a[2][BWARPS];     // per-warp aggregates of the forward scan (double-buffered by parity)
+  cf wtot_h[2][BWARPS];
+  cf rtot_q[2][BWARPS];     // per-warp aggregates of the reverse scan
+  cf rtot_g[2][BWARPS];
+  cf afirst[BWARPS];        // first transition of each warp (needed by the previous warp's last lane)
+  cf red[3][BWARPS];        // block reduction scratch for dA, dB, dC
+  uint64_t bar[2];
+};
+
+template <int DM, bool HAS_DA, bool S1>
+__global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan_args p) {
+  constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);   // u, dout, delta (, deltaA)
+  constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);       // du, ddelta (, ddeltaA)
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // layout: buf[2] | out staging | BwdShared | per-state: gcar, anext, accA, accB, accC (cf each)
+  unsigned char *out_stage = smem_raw + 2 * (size_t)BUF_BYTES;
+  BwdShared &sh = *reinterpret_cast<BwdShared *>(out_stage + OUT_BYTES);
+  cf *st_arr = reinterpret_cast<cf *>(out_stage + OUT_BYTES + sizeof(BwdShared));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t row = blockIdx.x;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int L = p.seqlen, S = S1 ? 1 : p.dstate;
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  cf *gcar = st_arr, *anext = st_arr + S, *accA = st_arr + 2 * S, *accB = st_arr + 3 * S, *accC = st_arr + 4 * S;
+
+  const cf *u_row = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+  const cf *do_row = reinterpret_cast<const cf *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
+  const float *d_row = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const float *dA_row = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs +
+                                     (int64_t)d * p.deltaA_ds
+                               : nullptr;
+  cf *du_row = reinterpret_cast<cf *>(p.du) + (int64_t)b * p.du_bs + (int64_t)d * p.du_ds;
+  float *dd_row = reinterpret_cast<float *>(p.ddelta) + (int64_t)b * p.ddelta_bs + (int64_t)d * p.ddelta_ds;
+  float *ddA_row = HAS_DA ? reinterpret_cast<float *>(p.ddeltaA) + (int64_t)b * p.ddeltaA_bs +
+                                (int64_t)d * p.ddeltaA_ds
+                          : nullptr;
+  const cf *Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
+  const cf *Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
+  const cf *xrow = p.x ? reinterpret_cast<const cf *>(p.x) + row * n_chunks * 2 * S : nullptr;
+
+  bool tma_ok = ((reinterpret_cast<uintptr_t>(u_row) | reinterpret_cast<uintptr_t>(do_row) |
+                  reinterpret_cast<uintptr_t>(d_row) | reinterpret_cast<uintptr_t>(du_row) |
+                  reinterpret_cast<uintptr_t>(dd_row)) & 15) == 0;
+  if (HAS_DA) tma_ok = tma_ok && (((reinterpret_cast<uintptr_t>(dA_row) | reinterpret_cast<uintptr_t>(ddA_row)) & 15) == 0);
+
+  auto buf_u = [&](int k) { return reinterpret_cast<cf *>(smem_raw + (size_t)k * BUF_BYTES); };
+  auto buf_do = [&](int k) { return reinterpret_cast<cf *>(smem_raw + (size_t)k * BUF_BYTES + B_U_BYTES); };
+  auto buf_d = [&](int k) { return reinterpret_cast<float *>(smem_raw + (size_t)k * BUF_BYTES + 2 * B_U_BYTES); };
+  auto buf_dA = [&](int k) {
+    return reinterpret_cast<float *>(smem_raw + (size_t)k * BUF_BYTES + 2 * B_U_BYTES + B_D_BYTES);
+  };
+  auto is_async = [&](int c) { return tma_ok && (c + 1) * kChunk <= L; };
+  auto issue = [&](int c, int k) {   // one thread
+    if (c < 0 || !is_async(c)) return;
+    const int64_t t0 = (int64_t)c * kChunk;
+    mbar_expect_tx(&sh.bar[k], BUF_BYTES);
+    bulk_g2s(buf_u(k), u_row + t0, B_U_BYTES, &sh.bar[k]);
+    bulk_g2s(buf_do(k), do_row + t0, B_U_BYTES, &sh.bar[k]);
+    bulk_g2s(buf_d(k), d_row + t0, B_D_BYTES, &sh.bar[k]);
+    if (HAS_DA) bulk_g2s(buf_dA(k), dA_row + t0, B_D_BYTES, &sh.bar[k]);
+  };
+
+  if (tid == 0) {
+    mbar_init(&sh.bar[0], 1);
+    mbar_init(&sh.bar[1], 1);
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  for (int i = tid; i < S; i += BT) {
+    gcar[i] = cf(0.f, 0.f);
+    anext[i] = cf(1.f, 0.f);
+    accA[i] = accB[i] = accC[i] = cf(0.f, 0.f);
+  }
+  __syncthreads();
+  // chunk n_chunks-1-j uses buffer j&1
+  if (tid == 0) { issue(n_chunks - 1, 0); issue(n_chunks - 2, 1); }
+
+  bool failed = false;
+  int used0 = 0, used1 = 0;   // completed async fills of buffer 0 / 1 (barrier phase)
+  bool stores_pending = false;
+  for (int j = 0; j < n_chunks; ++j) {
+    const int c = n_chunks - 1 - j;
+    const int k = j & 1;
+    const int t0 = c * kChunk;
+    cf *su = buf_u(k), *sdo = buf_do(k);
+    float *sd = buf_d(k), *sdA = buf_dA(k);
+    if (is_async(c)) {
+      const int used = k ? used1 : used0;
+      if (!mbar_wait(&sh.bar[k], (uint32_t)(used & 1))) failed = true;
+      if (k) ++used1; else ++used0;
+    } else {
+      for (int i = tid; i < kChunk; i += BT) {
+        const int t = t0 + i;
+        su[i] = t < L ? u_row[t] : cf(0.f, 0.f);
+        sdo[i] = t < L ? do_row[t] : cf(0.f, 0.f);
+        sd[i] = t < L ? d_row[t] : 0.f;
+        if (HAS_DA) sdA[i] = t < L ? dA_row[t] : 0.f;
+      }
+    }
+    if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
+
+    cf u[BI], dy[BI];
+    float dl[BI], dAv[BI];
+    {
+      const float4 *s4 = reinterpret_cast<const float4 *>(su + tid * BI);
+      const float4 *o4 = reinterpret_cast<const float4 *>(sdo + tid * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 2; ++q) {
+        const float4 v = s4[q], w = o4[q];
+        u[2 * q] = cf(v.x, v.y);
+        u[2 * q + 1] = cf(v.z, v.w);
+        dy[2 * q] = cf(w.x, w.y);
+        dy[2 * q + 1] = cf(w.z, w.w);
+      }
+      const float4 *d4 = reinterpret_cast<const float4 *>(sd + tid * BI);
+      const float4 *dA4 = reinterpret_cast<const float4 *>(sdA + tid * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 4; ++q) {
+        const float4 v = d4[q];
+        dl[4 * q] = v.x; dl[4 * q + 1] = v.y; dl[4 * q + 2] = v.z; dl[4 * q + 3] = v.w;
+        if (HAS_DA) {
+          const float4 w = dA4[q];
+          dAv[4 * q] = w.x; dAv[4 * q + 1] = w.y; dAv[4 * q + 2] = w.z; dAv[4 * q + 3] = w.w;
+        }
+      }
+      if (!HAS_DA) {
+#pragma unroll
+        for (int i = 0; i < BI; ++i) dAv[i] = dl[i];
+      }
+    }
+    // the chunk now lives in registers: refill this buffer with the chunk two steps ahead
+    __syncthreads();
+    if (tid == 0) issue(c - 2, k);
+    cf du[BI];
+    float ddl[BI], ddA[BI];
+#pragma unroll
+    for (int i = 0; i < BI; ++i) { du[i] = cf(0.f, 0.f); ddl[i] = 0.f; ddA[i] = 0.f; }
+
+    for (int si = 0; si < S; ++si) {
+      const int par = si & 1;
+      const cf An = Ap[(int64_t)si * p.A_ns];
+      const cf Cn = Cp[(int64_t)si * p.C_ns];
+      cf a[BI], kk[BI], h[BI];
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        s5_coef<DM>(An, dl[i], dAv[i], a[i], kk[i]);
+        if (t0 + tid * BI + i >= L) { a[i] = cf(1.f, 0.f); kk[i] = cf(0.f, 0.f); }
+      }
+      // forward, pass 1: per-thread aggregate, warp scan, cross-warp prefix
+      cf P = cf(1.f, 0.f), hh = cf(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        hh = a[i] * hh + kk[i] * u[i];
+        P = P * a[i];
+      }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        cf Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+        if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+      }
+      if (lane == 31) { sh.wtot_a[par][warp] = P; sh.wtot_h[par][warp] = hh; }
+      if (lane == 0) sh.afirst[warp] = a[0];
+      cf a_next_lane = shfl_down(a[0], 1);   // a_{t+1} for this thread's last item
+      __syncthreads();
+      cf hpre = (c > 0) ? xrow[(int64_t)(c - 1) * 2 * S + 2 * si + 1] : cf(0.f, 0.f);
+      for (int w = 0; w < warp; ++w) hpre = sh.wtot_a[par][w] * hpre + sh.wtot_h[par][w];
+      cf Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
+      if (lane == 0) { Pex = cf(1.f, 0.f); hex = cf(0.f, 0.f); }
+      const cf hin = Pex * hpre + hex;       // state entering this thread's first item
+      // forward, pass 2: the states
+      {
+        cf hc = hin;
+#pragma unroll
+        for (int i = 0; i < BI; ++i) {
+          hc = a[i] * hc + kk[i] * u[i];
+          h[i] = hc;
+        }
+      }
+      if (lane == 31) a_next_lane = (warp == BWARPS - 1) ? anext[si] : sh.afirst[warp + 1];
+      // reverse, pass 1: aggregate of g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C)
+      const cf Cc = conj(Cn);
+      cf gg = cf(0.f, 0.f), Q = cf(1.f, 0.f);
+#pragma unroll
+      for (int i = BI - 1; i >= 0; --i) {
+        const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
+        gg = an * gg + dy[i] * Cc;
+        Q = Q * an;
+      }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        cf Qr = shfl_down(Q, off), gr = shfl_down(gg, off);
+        if (lane + off < 32) { gg = gg + Q * gr; Q = Q * Qr; }
+      }
+      if (lane == 0) { sh.rtot_q[par][warp] = Q; sh.rtot_g[par][warp] = gg; }
+      const cf gc_chunk = gcar[si];
+      __syncthreads();
+      cf gpost = gc_chunk;                   // adjoint entering this warp from the later warps / chunk
+      for (int w = BWARPS - 1; w > warp; --w) gpost = sh.rtot_g[par][w] + sh.rtot_q[par][w] * gpost;
+      cf g_right = shfl_down(gg, 1), Q_right = shfl_down(Q, 1);
+      cf gin = g_right + Q_right * gpost;    // adjoint at the first item of the next thread
+      if (lane == 31) gin = gpost;
+      if (tid == 0) {
+        gcar[si] = gg + Q * gpost;           // adjoint at the first step of this chunk
+        anext[si] = a[0];
+      }
+      // reverse, pass 2: adjoints and gradients
+      cf dA_l = cf(0.f, 0.f), dB_l = cf(0.f, 0.f), dC_l = cf(0.f, 0.f);
+      cf G = gin;
+#pragma unroll
+      for (int i = BI - 1; i >= 0; --i) {
+        const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
+        G = an * G + dy[i] * Cc;
+        const cf hprev = (i == 0) ? hin : h[i - 1];
+        const float dv = dl[i], dav = dAv[i];
+        du[i] = du[i] + G * conj(kk[i]);
+        dB_l = dB_l + G * conj(kk[i] * u[i]);
+        dC_l = dC_l + dy[i] * conj(h[i]);
+        float d_dl = 0.f, d_dA = 0.f;
+        if constexpr (DM == B200_DISC_ZOH) {
+          const cf E = cexp(An * dv);
+          const cf ah = a[i] * hprev;
+          d_dA = (G * conj(An * ah)).re;
+          d_dl = (G * conj(E * u[i])).re;
+          dA_l = dA_l + G * conj(ah * dav + u[i] * ((E * dv - kk[i]) / An));
+        } else if constexpr (DM == B200_DISC_BILINEAR) {
+          const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dv));
+          const cf rA = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dav));
+          const cf r2 = r * r, rA2 = rA * rA;
+          d_dA = (G * conj(hprev * An * rA2)).re;
+          d_dl = (G * conj(r2 * u[i])).re;
+          dA_l = dA_l + G * conj(hprev * rA2 * dav + r2 * u[i] * (0.5f * dv * dv));
+        } else {
+          const cf ah = a[i] * hprev;
+          d_dA = (G * conj(An * ah)).re;
+          dA_l = dA_l + G * conj(ah * dav);
+        }
+        if (t0 + tid * BI + i >= L) { d_dl = 0.f; d_dA = 0.f; }
+        if (HAS_DA) { ddl[i] += d_dl; ddA[i] += d_dA; }
+        else ddl[i] += d_dl + d_dA;
+      }
+      dA_l = warp_sum(dA_l);
+      dB_l = warp_sum(dB_l);
+      dC_l = warp_sum(dC_l);
+      if (lane == 0) { sh.red[0][warp] = dA_l; sh.red[1][warp] = dB_l; sh.red[2][warp] = dC_l; }
+      __syncthreads();
+      if (tid < 3) {
+        cf acc = cf(0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < BWARPS; ++w) acc = acc + sh.red[tid][w];
+        cf *dst = tid == 0 ? accA : (tid == 1 ? accB : accC);
+        dst[si] = dst[si] + acc;
+      }
+    }
+    // ---- write du / ddelta (/ ddeltaA) through the staging area
+    const bool bulk_out = tma_ok && (c + 1) * kChunk <= L;
+    if (bulk_out) {
+      if (tid == 0 && stores_pending) bulk_wait_read<0>();   // previous chunk's stores have left the staging area
+      __syncthreads();
+      cf *so = reinterpret_cast<cf *>(out_stage);
+      float *sod = reinterpret_cast<float *>(out_stage + B_U_BYTES);
+      float *sodA = reinterpret_cast<float *>(out_stage + B_U_BYTES + B_D_BYTES);
+      float4 *s4 = reinterpret_cast<float4 *>(so + tid * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 2; ++q) s4[q] = make_float4(du[2 * q].re, du[2 * q].im, du[2 * q + 1].re, du[2 * q + 1].im);
+      float4 *d4 = reinterpret_cast<float4 *>(sod + tid * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 4; ++q) d4[q] = make_float4(ddl[4 * q], ddl[4 * q + 1], ddl[4 * q + 2], ddl[4 * q + 3]);
+      if (HAS_DA) {
+        float4 *dA4 = reinterpret_cast<float4 *>(sodA + tid * BI);
+#pragma unroll
+        for (int q = 0; q < BI / 4; ++q) dA4[q] = make_float4(ddA[4 * q], ddA[4 * q + 1], ddA[4 * q + 2], ddA[4 * q + 3]);
+      }
+      fence_proxy_async();
+      __syncthreads();
+      if (tid == 0) {
+        bulk_s2g(du_row + t0, so, B_U_BYTES);
+        bulk_s2g(dd_row + t0, sod, B_D_BYTES);
+        if (HAS_DA) bulk_s2g(ddA_row + t0, sodA, B_D_BYTES);
+        bulk_commit();
+      }
+      stores_pending = true;
+    } else {
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        const int t = t0 + tid * BI + i;
+        if (t < L) {
+          du_row[t] = du[i];
+          dd_row[t] = ddl[i];
+          if (HAS_DA) ddA_row[t] = ddA[i];
+        }
+      }
+    }
+  }
+  if (tid == 0) bulk_wait<0>();
+  __syncthreads();
+  if (failed) {
+    if (tid == 0) atomicExch(&g_simpscan_status, 2);
+    return;
+  }
+  cf *dAp = reinterpret_cast<cf *>(p.dA) + (int64_t)d * p.A_ds;
+  cf *dBp = reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds;
+  cf *dCp = reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds;
+  for (int i = tid; i < S; i += BT) {
+    atomicAdd(&dAp[(int64_t)i * p.A_ns].re, accA[i].re);
+    atomicAdd(&dAp[(int64_t)i * p.A_ns].im, accA[i].im);
+    atomicAdd(&dBp[(int64_t)i * p.B_ns].re, accB[i].re);
+    atomicAdd(&dBp[(int64_t)i * p.B_ns].im, accB[i].im);
+    atomicAdd(&dCp[(int64_t)i * p.C_ns].re, accC[i].re);
+    atomicAdd(&dCp[(int64_t)i * p.C_ns].im, accC[i].im);
+  }
+}
+
+template <typename K> int set_smem(K kernel, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  }
+  return 0;
+}
+
+template <int DM, bool HAS_DA> int launch_fwd(const b200_simpscan_args &a, cudaStream_t st) {
+  constexpr int SLOT_BYTES = F_U_BYTES + F_D_BYTES * (HAS_DA ? 2 : 1);
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = (size_t)FWARPS * FNS * SLOT_BYTES + FWARPS * FNS * 8 + (size_t)FWARPS * 2 * a.dstate * sizeof(cf);
+  auto k = simpscan_fwd_kernel<DM, HAS_DA>;
+  if (int e = set_smem(k, smem)) return e;
+  k<<<(unsigned)((rows + FWARPS - 1) / FWARPS), FWARPS * 32, smem, st>>>(a);
+  return launch_status();
+}
+template <int DM, bool HAS_DA, bool S1> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
+  constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
+  constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = 2 * (size_t)BUF_BYTES + OUT_BYTES + sizeof(BwdShared) + (size_t)5 * a.dstate * sizeof(cf);
+  auto k = simpscan_bwd_kernel<DM, HAS_DA, S1>;
+  if (int e = set_smem(k, smem)) return e;
+  k<<<(unsigned)rows, BT, smem, st>>>(a);
+  return launch_status();
+}
+template <int DM, bool HAS_DA> int launch_bwd(const b200_simpscan_args &a, cudaStream_t st) {
+  return a.dstate == 1 ? launch_bwd_s<DM, HAS_DA, true>(a, st) : launch_bwd_s<DM, HAS_DA, false>(a, st);
+}
+
+int check(const b200_simpscan_args &a, bool bwd) {
+  B200_REQUIRE(a.u && a.delta && a.A && a.B && a.C, B200_ERR_NULL, "simpscan: u, delta, A, B, C must be non-null");
+  B200_REQUIRE(a.batch > 0 && a.dim > 0 && a.seqlen > 0 && a.dstate > 0, B200_ERR_SHAPE,
+               "simpscan: batch, dim, seqlen, dstate must be positive");
+  B200_REQUIRE(a.dstate <= kMaxDState, B200_ERR_SHAPE, "simplified_scan only supports state dimension <= 256");
+  B200_REQUIRE(a.method == B200_DISC_ZOH || a.method == B200_DISC_BILINEAR || a.method == B200_DISC_DIRAC,
+               B200_ERR_DTYPE, "simplified_scan supports the zoh, bilinear and dirac discretizations");
+  if (!bwd) {
+    B200_REQUIRE(a.out && a.x, B200_ERR_NULL, "simpscan_fwd: out and x must be non-null");
+  } else {
+    B200_REQUIRE(a.dout && a.du && a.ddelta && a.dA && a.dB && a.dC, B200_ERR_NULL,
+                 "simpscan_bwd: dout, du, ddelta, dA, dB, dC must be non-null");
+    B200_REQUIRE(a.x || a.seqlen <= kChunk, B200_ERR_NULL, "simpscan_bwd: x is required when seqlen > 2048");
+    B200_REQUIRE(!a.deltaA || a.ddeltaA, B200_ERR_NULL, "simpscan_bwd: ddeltaA is required when deltaA is given");
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_simpscan_fwd(const b200_simpscan_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "simpscan_fwd: null argument block");
+  if (int e = check(*args, false)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool dA = args->deltaA != nullptr;
+  switch (args->method) {
+    case B200_DISC_ZOH: return dA ? launch_fwd<B200_DISC_ZOH, true>(*args, st) : launch_fwd<B200_DISC_ZOH, false>(*args, st);
+    case B200_DISC_BILINEAR: return dA ? launch_fwd<B200_DISC_BILINEAR, true>(*args, st) : launch_fwd<B200_DISC_BILINEAR, false>(*args, st);
+    default: return dA ? launch_fwd<B200_DISC_DIRAC, true>(*args, st) : launch_fwd<B200_DISC_DIRAC, false>(*args, st);
+  }
+}
+
+int b200_simpscan_bwd(const b200_simpscan_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "simpscan_bwd: null argument block");
+  if (int e = check(*args, true)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool dA = args->deltaA != nullptr;
+  switch (args->method) {
+    case B200_DISC_ZOH: return dA ? launch_bwd<B200_DISC_ZOH, true>(*args, st) : launch_bwd<B200_DISC_ZOH, false>(*args, st);
+    case B200_DISC_BILINEAR: return dA ? launch_bwd<B200_DISC_BILINEAR, true>(*args, st) : launch_bwd<B200_DISC_BILINEAR, false>(*args, st);
+    default: return dA ? launch_bwd<B200_DISC_DIRAC, true>(*args, st) : launch_bwd<B200_DISC_DIRAC, false>(*args, st);
+  }
+}
+
+// Non-zero after a kernel gave up on a bounded barrier wait (diagnostic; synchronises the device).
+int b200_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_simpscan_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // extern "C"
