@@ -1,0 +1,447 @@
+#!/usr/bin/env python
+"""Benchmark of the lrnnx scan hot path on B200 (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Default workload (BASELINE.json configs[1]): the diagonal complex simplified scan used by
+S5, complex64, B=8, P=256 states, H=512 channels, L=4096, forward + backward, recurrence
+x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
+
+  value      tokens/s of the scan hot path (forward + backward kernels through the C ABI,
+             operands resident in HBM); a token is one (batch, timestep) pair.  With N > 1
+             every rank runs the full workload on its own batch shard (weak scaling) and the
+             parameter gradients dA/dB/dC are all-reduced over NCCL inside the step.
+  e2e        the same metric through the public op ``lrnnx_b200.ops.simplified_scan_fn``
+             starting from pinned HOST tensors: host->device copies of u and delta, the
+             complex projections (cuBLAS), both scan kernels, and a device->host read of the
+             loss every step.
+  roofline   algorithmic HBM bytes of the dominant kernel / its mean launch time (CUDA
+             events on the launching stream) against the measured copy bandwidth in
+             MEASURED_PEAKS.json.
+  cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch scan) timed on the
+             host cores on a bounded sample of the same workload.
+
+``--impl reference`` times that CPU implementation alone (rank 0 only).
+Other workloads (``--workload``): s6_cfg0, s6_layer, s6_long, ssu_step, cauchy.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+# --------------------------------------------------------------------------- helpers
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            self.path = tempfile.NamedTemporaryFile(delete=False, suffix=".csv").name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in Path(self.path).read_text().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        # samples under load: the upper half of the clock samples (idle samples sit at low clocks)
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cn(g, *shape):
+    return torch.complex(torch.randn(*shape, generator=g), torch.randn(*shape, generator=g)) / math.sqrt(2)
+
+
+# --------------------------------------------------------------------------- workloads
+class S5Scan:
+    """BASELINE config 1."""
+    name = "s5_scan_cfg1"
+    dtype = "c64"
+    metric, unit = "scan tokens/s (simplified scan fwd+bwd)", "tokens/s"
+
+    def __init__(self, batch=8, P=256, H=512, L=4096):
+        self.batch, self.P, self.H, self.L = batch, P, H, L
+        self.tokens = batch * L
+        self.fwd_bytes = 20 * batch * P * L          # u 8 + delta 4 read, out 8 written per (b,p,l)
+        self.bwd_bytes = 32 * batch * P * L          # u 8, delta 4, dout 8 read; du 8, ddelta 4 written
+        self.describe = {"workload": f"{self.name}: B={batch} P={P} H={H} L={L} complex64 dirac fwd+bwd",
+                         "global_batch": batch, "seq_len": L, "states": P, "channels": H,
+                         "l2": "operands of every kernel exceed the 126 MB L2 (fwd 168 MB, bwd 268 MB)"}
+
+    def host_inputs(self, seed=0, batch=None, L=None):
+        g = torch.Generator().manual_seed(seed)
+        batch, L = batch or self.batch, L or self.L
+        lam = torch.polar(0.9 + 0.099 * torch.rand(self.P, generator=g), math.pi / 10 * torch.rand(self.P, generator=g))
+        A = torch.log(lam)
+        B = cn(g, self.P, self.H) / math.sqrt(self.H)
+        C = cn(g, self.H, self.P) / math.sqrt(self.P)
+        u = torch.randn(batch, L, self.H, generator=g).transpose(1, 2).to(torch.complex64).contiguous()
+        delta = torch.ones(batch, self.P, L)
+        gout = cn(g, batch, self.H, L)
+        return dict(u=u, delta=delta, A=A, B=B, C=C, gout=gout)
+
+    def setup(self, dev, pg):
+        from lrnnx_b200 import simplified_scan_cuda
+        from lrnnx_b200.ops import simplified_scan_fn
+        self.dev, self.pg = dev, pg
+        h = self.host_inputs()
+        self.h_u, self.h_delta, self.h_gout = h["u"].pin_memory(), h["delta"].pin_memory(), h["gout"].pin_memory()
+        self.A, self.B, self.C = (h[k].to(dev) for k in ("A", "B", "C"))
+        self.u, self.delta, self.gout = self.h_u.to(dev), self.h_delta.to(dev), self.h_gout.to(dev)
+        # kernel-level operands (what SimplifiedScanFn hands to the extension)
+        self.Bu = torch.einsum("ph,bhl->bpl", self.B, self.u).contiguous()
+        self.dBu_in = torch.einsum("hp,bhl->bpl", self.C.conj(), self.gout).contiguous()
+        self.A_k = self.A.unsqueeze(-1).contiguous()
+        self.one = torch.ones(self.P, 1, dtype=torch.complex64, device=dev)
+        self.ext, self.op = simplified_scan_cuda, simplified_scan_fn
+        self.d_u = torch.empty_like(self.u)
+        self.d_delta = torch.empty_like(self.delta)
+        self.ev = []
+
+    def step(self, record=False):
+        """forward + backward scan kernels through the extension entry points."""
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            e[0].record()
+        out, x = self.ext.fwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, "dirac")
+        if record:
+            e[1].record()
+        res = self.ext.bwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, self.dBu_in, x, "dirac")
+        if record:
+            e[2].record()
+            self.ev.append(e)
+        if self.pg is not None:
+            torch.distributed.all_reduce(torch.view_as_real(res[2]), group=self.pg)
+        return res
+
+    launches_per_step = 2
+
+    def e2e_step(self):
+        u = self.d_u.copy_(self.h_u, non_blocking=True).requires_grad_(True)
+        delta = self.d_delta.copy_(self.h_delta, non_blocking=True).requires_grad_(True)
+        A, B, C = (t.detach().requires_grad_(True) for t in (self.A, self.B, self.C))
+        y = self.op(u, delta, A, B, C, discretization="dirac")
+        loss = (y * self.gout.conj()).real.sum()
+        loss.backward()
+        if self.pg is not None:
+            for t in (A, B, C):
+                torch.distributed.all_reduce(torch.view_as_real(t.grad), group=self.pg)
+        val = float(loss.item())
+        self.d_u, self.d_delta = u.detach(), delta.detach()
+        return val
+
+    def e2e_bytes(self):
+        return self.h_u.numel() * 8 + self.h_delta.numel() * 4, 4
+
+    def kernel_rooflines(self):
+        f = [a[0].elapsed_time(a[1]) for a in self.ev]
+        b = [a[1].elapsed_time(a[2]) for a in self.ev]
+        return {"simpscan_fwd_kernel": (self.fwd_bytes, statistics.mean(f)),
+                "simpscan_bwd_kernel": (self.bwd_bytes, statistics.mean(b))}
+
+    # CPU arm: batch 1, first 1024 steps, same P and H (per-token work unchanged)
+    cpu_sample = "batch 1 of 8, first 1024 of 4096 timesteps, P=256, H=512 (same work per token)"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            self._cpu = self.host_inputs(batch=1, L=1024)
+        h = self._cpu
+        leaves = [h[k].clone().requires_grad_(True) for k in ("u", "delta", "A", "B", "C")]
+        y = O.simplified_scan_oracle(*leaves, discretization="dirac")
+        torch.autograd.grad(y, leaves, h["gout"])
+        return 1 * 1024
+
+
+class S6Scan:
+    """Selective scan (S6/Mamba) forward(+backward); shapes of BASELINE configs 0, 2 (one layer) and 3."""
+    metric, unit = "scan tokens/s (selective scan)", "tokens/s"
+
+    def __init__(self, name, batch, dim, L, N, dtype, backward=True):
+        self.name, self.batch, self.dim, self.L, self.N, self.tdtype, self.backward = name, batch, dim, L, N, dtype, backward
+        self.dtype = "f32" if dtype == torch.float32 else "bf16 i/o, f32 state"
+        s = 4 if dtype == torch.float32 else 2
+        bdl, bnl = batch * dim * L, batch * N * L
+        self.tokens = batch * L
+        self.fwd_bytes = 5 * s * bdl + 2 * s * bnl
+        self.bwd_bytes = 8 * s * bdl + (2 * s + 8) * bnl
+        self.describe = {"workload": f"{name}: B={batch} D={dim} L={L} N={N} {self.dtype} "
+                                     f"{'fwd+bwd' if backward else 'fwd'} mamba, z, D, delta_bias, softplus",
+                         "global_batch": batch, "seq_len": L,
+                         "l2": "L2 flushed by a 256 MB write between timed iterations" if self.fwd_bytes < 2.6e8
+                         else "operands exceed the 126 MB L2"}
+        self.flush = self.fwd_bytes < 2.6e8
+        self.launches_per_step = 2 if backward else 1
+
+    def host_inputs(self, seed=0, dim=None, L=None):
+        g = torch.Generator().manual_seed(seed)
+        batch, dim, L, N = self.batch, dim or self.dim, L or self.L, self.N
+        dt = torch.exp(torch.rand(dim, generator=g) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+        return dict(u=torch.randn(batch, dim, L, generator=g).to(self.tdtype),
+                    delta=torch.randn(batch, dim, L, generator=g).to(self.tdtype),
+                    A=-torch.arange(1, N + 1, dtype=torch.float32).repeat(dim, 1),
+                    B=torch.randn(batch, 1, N, L, generator=g).to(self.tdtype),
+                    C=torch.randn(batch, 1, N, L, generator=g).to(self.tdtype),
+                    D=torch.ones(dim), z=torch.randn(batch, dim, L, generator=g).to(self.tdtype),
+                    delta_bias=dt + torch.log(-torch.expm1(-dt)),
+                    gout=torch.randn(batch, dim, L, generator=g).to(self.tdtype))
+
+    def setup(self, dev, pg):
+        from lrnnx_b200 import selective_scan_cuda
+        from lrnnx_b200.ops import selective_scan_fn
+        self.dev, self.pg, self.ext, self.op = dev, pg, selective_scan_cuda, selective_scan_fn
+        h = self.host_inputs()
+        self.h = {k: v.pin_memory() for k, v in h.items()}
+        self.t = {k: v.to(dev) for k, v in h.items()}
+        self.ev = []
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
+
+    def step(self, record=False):
+        t = self.t
+        if self.flush_buf is not None:
+            self.flush_buf.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            e[0].record()
+        out, x, out_z = self.ext.fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"],
+                                     None, True, "mamba")
+        if record:
+            e[1].record()
+        res = None
+        if self.backward:
+            res = self.ext.bwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"], None,
+                               t["gout"], x, out, None, True, False, "mamba")
+        if record:
+            e[2].record()
+            self.ev.append(e)
+        if self.pg is not None and res is not None:
+            torch.distributed.all_reduce(res[2], group=self.pg)
+        return res
+
+    def e2e_step(self):
+        t = {k: (self.t[k].copy_(self.h[k], non_blocking=True)) for k in ("u", "delta", "B", "C", "z")}
+        leaves = {k: v.detach().requires_grad_(self.backward) for k, v in t.items()}
+        A, D, bias = (self.t[k].detach().requires_grad_(self.backward) for k in ("A", "D", "delta_bias"))
+        y = self.op(leaves["u"], leaves["delta"], A, leaves["B"], leaves["C"], D, leaves["z"], bias,
+                    delta_softplus=True, discretization="mamba")
+        loss = (y.float() * self.t["gout"].float()).sum()
+        if self.backward:
+            loss.backward()
+        return float(loss.item())
+
+    def e2e_bytes(self):
+        return sum(self.h[k].numel() * self.h[k].element_size() for k in ("u", "delta", "B", "C", "z")), 4
+
+    def kernel_rooflines(self):
+        f = [a[0].elapsed_time(a[1]) for a in self.ev]
+        r = {"selscan_fwd": (self.fwd_bytes, statistics.mean(f))}
+        if self.backward:
+            b = [a[1].elapsed_time(a[2]) for a in self.ev]
+            r["selscan_bwd"] = (self.bwd_bytes, statistics.mean(b))
+        return r
+
+    @property
+    def cpu_sample(self):
+        return f"{self._cpu_dim} of {self.dim} channels, first {self._cpu_L} of {self.L} timesteps, all batches"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        self._cpu_dim, self._cpu_L = min(self.dim, 64), min(self.L, 1024)
+        if not hasattr(self, "_cpu"):
+            self._cpu = self.host_inputs(dim=self._cpu_dim, L=self._cpu_L)
+        h = self._cpu
+        names = ("u", "delta", "A", "B", "C", "D", "z", "delta_bias")
+        leaves = {k: h[k].clone().requires_grad_(self.backward) for k in names}
+        y = O.selective_scan_oracle(**leaves, delta_softplus=True, discretization="mamba")
+        if self.backward:
+            torch.autograd.grad(y, list(leaves.values()), h["gout"])
+        # tokens of the sample scaled by the channel fraction (channels are independent rows)
+        return self.batch * self._cpu_L * self._cpu_dim / self.dim
+
+
+def make_workload(name):
+    if name in ("s5_scan", "s5_scan_cfg1", "default"):
+        return S5Scan()
+    if name == "s6_cfg0":
+        return S6Scan("s6_cfg0", 2, 256, 512, 16, torch.float32)
+    if name == "s6_layer":
+        return S6Scan("s6_layer_cfg2", 8, 1536, 2048, 16, torch.bfloat16)
+    if name == "s6_layer_f32":
+        return S6Scan("s6_layer_f32", 8, 1536, 2048, 16, torch.float32)
+    if name == "s6_long":
+        return S6Scan("s6_long_cfg3", 1, 5120, 131072, 16, torch.bfloat16, backward=False)
+    raise SystemExit(f"unknown workload {name}")
+
+
+# --------------------------------------------------------------------------- arms
+def time_cpu(wl, steps, warmup):
+    torch.set_num_threads(os.cpu_count() or 1)
+    for _ in range(warmup):
+        wl.cpu_step()
+    t0 = time.perf_counter()
+    toks = 0.0
+    for _ in range(steps):
+        toks += wl.cpu_step()
+    dt = time.perf_counter() - t0
+    return toks / dt, dt / steps
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
+    tps, sec = time_cpu(wl, steps, warmup)
+    line = {"impl": "reference", "metric": wl.metric, "value": tps, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)", "config": wl.describe,
+            "cpu_baseline": {"value": tps, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": wl.cpu_sample},
+            "e2e": {"value": tps, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def run_ours(args, wl):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    pg = None
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+        pg = torch.distributed.group.WORLD
+    wl.setup(dev, pg)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, record=False):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn(record=True) if record else fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_step = timed(wl.step, args.steps, args.warmup, record=True)
+    # separate pass without per-kernel events inside the loop is not needed: events cost ~1 us
+    clocks = sampler.stop() if sampler else None
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = timed(wl.e2e_step, e2e_steps, 3)
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        roofs = {}
+        for kname, (nbytes, ms) in wl.kernel_rooflines().items():
+            ach = nbytes / (ms * 1e-3) / 1e9
+            roofs[kname] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                            "traffic": None, "algorithmic_bytes": nbytes, "ms_per_launch": ms,
+                            "peak_source": peak_kind}
+        dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
+        cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
+        h2d, d2h = wl.e2e_bytes()
+        line = {"metric": wl.metric, "value": world * wl.tokens / (ms_step * 1e-3), "unit": wl.unit,
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+                "data": "synthetic (seeded CPU generator, copied to the GPU)", "config": wl.describe,
+                "clocks": clocks,
+                "e2e": {"value": world * wl.tokens / (ms_e2e * 1e-3), "unit": wl.unit, "ms_per_step": ms_e2e,
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                "gpu_launches": wl.launches_per_step * args.steps,
+                "roofline": dict(roofs[dominant], kernel=dominant),
+                "kernels": roofs,
+                "cpu_baseline": {"value": cpu_tps, "unit": wl.unit, "cores": torch.get_num_threads(),
+                                 "kind": "port", "sample": wl.cpu_sample, "seconds": cpu_sec}}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="s5_scan_cfg1")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = make_workload(args.workload)
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()
