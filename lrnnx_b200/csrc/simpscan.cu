@@ -58,36 +58,43 @@ constexpr int FNS = 3;               // pipeline slots per warp
 constexpr int F_U_BYTES = FSTAGE * 8;
 constexpr int F_D_BYTES = FSTAGE * 4;
 
-template <int DM, bool HAS_DA>
+// Operands past the end of the row are zero-filled, which makes them neutral without any
+// masking: delta = 0 gives a = 1 for all three methods and u = 0 gives a zero input term.
+template <int DM, bool HAS_DA, bool S1>
 __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200_simpscan_args p) {
   constexpr int SLOT_BYTES = F_U_BYTES + F_D_BYTES * (HAS_DA ? 2 : 1);
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * FWARPS + warp;
-  if (row >= (int64_t)p.batch * p.dim) return;
-  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
-  const int L = p.seqlen, S = p.dstate;
+  const int L = p.seqlen, S = S1 ? 1 : p.dstate;
   const int n_chunks = (L + kChunk - 1) / kChunk;
+  const int nst = (L + FSTAGE - 1) / FSTAGE;
+  // persistent warps: warp gw owns rows gw, gw + W, gw + 2W, ...; the stages of all its rows form
+  // one stream that the 3-slot pipeline runs through without draining between rows
+  const int64_t nrows = (int64_t)p.batch * p.dim;
+  const int64_t W = (int64_t)gridDim.x * FWARPS;
+  const int64_t gw = (int64_t)blockIdx.x * FWARPS + warp;
+  if (gw >= nrows) return;
+  const int my_rows = (int)((nrows - gw + W - 1) / W);
+  const int total = my_rows * nst;
   // shared memory: [FWARPS][FNS] slots | [FWARPS][FNS] mbarriers | [FWARPS][2*S] carry
   unsigned char *wbase = smem_raw + (size_t)warp * FNS * SLOT_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)FWARPS * FNS * SLOT_BYTES) + warp * FNS;
   cf *carry = reinterpret_cast<cf *>(smem_raw + (size_t)FWARPS * FNS * SLOT_BYTES + FWARPS * FNS * 8) +
               (size_t)warp * 2 * S;
 
-  const cf *u_row = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
-  const float *d_row = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
-  const float *dA_row = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs +
-                                     (int64_t)d * p.deltaA_ds
-                               : nullptr;
-  cf *o_row = reinterpret_cast<cf *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
-  const cf *Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
-  const cf *Bp = reinterpret_cast<const cf *>(p.B) + (int64_t)d * p.B_ds;
-  const cf *Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
-  cf *xrow = reinterpret_cast<cf *>(p.x) + row * n_chunks * 2 * S;
-
-  bool tma_ok = ((reinterpret_cast<uintptr_t>(u_row) | reinterpret_cast<uintptr_t>(d_row) |
-                  reinterpret_cast<uintptr_t>(o_row)) & 15) == 0;
-  if (HAS_DA) tma_ok = tma_ok && ((reinterpret_cast<uintptr_t>(dA_row) & 15) == 0);
+  struct RowPtrs { const cf *u; const float *d; const float *dA; cf *o; bool tma; };
+  auto row_ptrs = [&](int64_t row) {
+    const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+    RowPtrs r;
+    r.u = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+    r.d = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+    r.dA = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs + (int64_t)d * p.deltaA_ds
+                  : nullptr;
+    r.o = reinterpret_cast<cf *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+    r.tma = ((reinterpret_cast<uintptr_t>(r.u) | reinterpret_cast<uintptr_t>(r.d) | reinterpret_cast<uintptr_t>(r.o)) & 15) == 0;
+    if (HAS_DA) r.tma = r.tma && ((reinterpret_cast<uintptr_t>(r.dA) & 15) == 0);
+    return r;
+  };
 
   if (lane == 0) {
 #pragma unroll
@@ -97,44 +104,69 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
   }
   __syncwarp();
 
-  const int nst = (L + FSTAGE - 1) / FSTAGE;
   auto slot_u = [&](int k) { return reinterpret_cast<cf *>(wbase + (size_t)k * SLOT_BYTES); };
   auto slot_d = [&](int k) { return reinterpret_cast<float *>(wbase + (size_t)k * SLOT_BYTES + F_U_BYTES); };
   auto slot_dA = [&](int k) {
     return reinterpret_cast<float *>(wbase + (size_t)k * SLOT_BYTES + F_U_BYTES + F_D_BYTES);
   };
-  auto is_async = [&](int s) { return tma_ok && (s + 1) * FSTAGE <= L; };
-  auto issue = [&](int s) {   // lane 0 only
-    if (s >= nst || !is_async(s)) return;
-    const int k = s % FNS;
+  // stage f of the stream: bulk (TMA) copies when the row is 16-byte aligned and the stage is full
+  auto issue = [&](int f) {   // lane 0 only
+    if (f >= total) return;
+    const int s = f % nst;
+    if ((s + 1) * FSTAGE > L) return;
+    const RowPtrs r = row_ptrs(gw + (int64_t)(f / nst) * W);
+    if (!r.tma) return;
+    const int k = f % FNS;
     const int64_t t0 = (int64_t)s * FSTAGE;
     mbar_expect_tx(&bars[k], SLOT_BYTES);
-    bulk_g2s(slot_u(k), u_row + t0, F_U_BYTES, &bars[k]);
-    bulk_g2s(slot_d(k), d_row + t0, F_D_BYTES, &bars[k]);
-    if (HAS_DA) bulk_g2s(slot_dA(k), dA_row + t0, F_D_BYTES, &bars[k]);
+    bulk_g2s(slot_u(k), r.u + t0, F_U_BYTES, &bars[k]);
+    bulk_g2s(slot_d(k), r.d + t0, F_D_BYTES, &bars[k]);
+    if (HAS_DA) bulk_g2s(slot_dA(k), r.dA + t0, F_D_BYTES, &bars[k]);
   };
   if (lane == 0) { issue(0); issue(1); }
 
+  uint32_t phase_bits = 0;   // bit k: parity the next wait on slot k expects
   bool failed = false;
-  for (int s = 0; s < nst; ++s) {
-    const int k = s % FNS;
+  RowPtrs rp = row_ptrs(gw);
+  int64_t row = gw;
+  cf A0, BC0, Pc0, hc0;
+  bool bc_one = false;
+  const cf *Ap = nullptr, *Bp = nullptr, *Cp = nullptr;
+  cf *xrow = nullptr;
+  for (int f = 0; f < total; ++f) {
+    const int s = f % nst;
+    if (s == 0) {   // new row
+      row = gw + (int64_t)(f / nst) * W;
+      rp = row_ptrs(row);
+      const int d = (int)(row % p.dim);
+      Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
+      Bp = reinterpret_cast<const cf *>(p.B) + (int64_t)d * p.B_ds;
+      Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
+      xrow = reinterpret_cast<cf *>(p.x) + row * n_chunks * 2 * S;
+      A0 = Ap[0];
+      BC0 = Bp[0] * Cp[0];
+      bc_one = S1 && BC0.re == 1.f && BC0.im == 0.f;
+      Pc0 = cf(1.f, 0.f);
+      hc0 = cf(0.f, 0.f);
+    }
+    const int k = f % FNS;
     const int t0 = s * FSTAGE;
+    const bool async_stage = rp.tma && (s + 1) * FSTAGE <= L;
     cf *su = slot_u(k);
     float *sd = slot_d(k), *sdA = slot_dA(k);
-    if (is_async(s)) {
-      if (!mbar_wait(&bars[k], (uint32_t)((s / FNS) & 1))) { failed = true; break; }
+    if (async_stage) {
+      if (!mbar_wait(&bars[k], (phase_bits >> k) & 1u)) { failed = true; break; }
+      phase_bits ^= (1u << k);
     } else {
       // ragged or unaligned stage: coalesced plain loads into the same layout (after any bulk
-      // store that still reads this slot)
-      if (tma_ok) {
-        if (lane == 0) bulk_wait_read<0>();
-        __syncwarp();
-      }
+      // store that still reads this slot), zero-filled past the end of the row
+      if (lane == 0) bulk_wait_read<0>();
+      __syncwarp();
       for (int i = lane; i < FSTAGE; i += 32) {
         const int t = t0 + i;
-        su[i] = t < L ? u_row[t] : cf(0.f, 0.f);
-        sd[i] = t < L ? d_row[t] : 0.f;
-        if (HAS_DA) sdA[i] = t < L ? dA_row[t] : 0.f;
+        su[i] = t < L ? rp.u[t] : cf(0.f, 0.f);
+        sd[i] = t < L ? rp.d[t] : 0.f;
+        if (HAS_DA) sdA[i] = t < L ? rp.dA[t] : 0.f;
       }
       __syncwarp();
     }
@@ -166,23 +198,30 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
       }
     }
     cf out[FI];
+    if (!S1) {
 #pragma unroll
-    for (int i = 0; i < FI; ++i) out[i] = cf(0.f, 0.f);
-    // a stage can hold both a chunk boundary and the row end (L % 2048 < 320); handle the second below
+      for (int i = 0; i < FI; ++i) out[i] = cf(0.f, 0.f);
+    }
+    // positions of this stage whose state is a checkpoint: the end of a 2048-step chunk and/or
+    // the end of the row (a 320-step stage holds at most one of each)
     const int tend = min(L, t0 + FSTAGE);
     const int boundary = (tend / kChunk) * kChunk;
-    const int ck_a = (boundary > t0) ? boundary - 1 - t0 : -1;           // chunk boundary inside the stage
-    const int ck_b = (tend == L && (L % kChunk) != 0) ? L - 1 - t0 : -1;  // row end (when not itself a boundary)
+    const int ck_a = (boundary > t0) ? boundary - 1 - t0 : -1;
+    const int ck_b = (tend == L && (L % kChunk) != 0) ? L - 1 - t0 : -1;
     for (int si = 0; si < S; ++si) {
-      const cf An = Ap[(int64_t)si * p.A_ns];
-      const cf BC = Bp[(int64_t)si * p.B_ns] * Cp[(int64_t)si * p.C_ns];
+      const cf An = S1 ? A0 : Ap[(int64_t)si * p.A_ns];
+      const cf BC = S1 ? BC0 : Bp[(int64_t)si * p.B_ns] * Cp[(int64_t)si * p.C_ns];
       cf a[FI], h[FI];
 #pragma unroll
       for (int i = 0; i < FI; ++i) {
-        cf kk;
-        s5_coef<DM>(An, dl[i], dAv[i], a[i], kk);
-        h[i] = kk * u[i];
-        if (t0 + lane * FI + i >= L) { a[i] = cf(1.f, 0.f); h[i] = cf(0.f, 0.f); }
+        if constexpr (DM == B200_DISC_DIRAC) {
+          a[i] = cexp(An * dAv[i]);
+          h[i] = u[i];
+        } else {
+          cf kk;
+          s5_coef<DM>(An, dl[i], dAv[i], a[i], kk);
+          h[i] = kk * u[i];
+        }
       }
       cf P = a[0], hh = h[0];
 #pragma unroll
@@ -199,50 +238,65 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
       }
       cf Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
       if (lane == 0) { Pex = cf(1.f, 0.f); hex = cf(0.f, 0.f); }
-      cf Pc = cf(1.f, 0.f), hc = cf(0.f, 0.f);
-      if (s > 0) { Pc = carry[2 * si]; hc = carry[2 * si + 1]; }
+      cf Pc = Pc0, hc = hc0;
+      if (!S1) {
+        if (s > 0) { Pc = carry[2 * si]; hc = carry[2 * si + 1]; }
+        else { Pc = cf(1.f, 0.f); hc = cf(0.f, 0.f); }
+      }
       const cf hin = Pex * hc + hex;
-      const cf Pin = Pex * Pc;
 #pragma unroll
       for (int i = 0; i < FI; ++i) {
-        const cf hv = a[i] * hin + h[i];
-        out[i] = out[i] + hv * BC;
-        const int pos = lane * FI + i;
-        if (pos == ck_a || pos == ck_b) {
-          cf *xr = xrow + (int64_t)((t0 + pos) / kChunk) * 2 * S;
-          xr[2 * si] = a[i] * Pin;
-          xr[2 * si + 1] = hv;
+        h[i] = a[i] * hin + h[i];
+        if (S1) out[i] = bc_one ? h[i] : h[i] * BC;
+        else out[i] = out[i] + h[i] * BC;
+      }
+      if (ck_a >= 0 || ck_b >= 0) {
+        const cf Pin = Pex * Pc;
+#pragma unroll
+        for (int i = 0; i < FI; ++i) {
+          const int pos = lane * FI + i;
+          if (pos == ck_a || pos == ck_b) {
+            cf *xr = xrow + (int64_t)((t0 + pos) / kChunk) * 2 * S;
+            xr[2 * si] = a[i] * Pin;
+            xr[2 * si + 1] = h[i];
+          }
         }
       }
       const cf Ptot = shfl_idx(P, 31), htot = shfl_idx(hh, 31);
-      __syncwarp();
-      if (lane == 0) {
-        carry[2 * si] = Pc * Ptot;
-        carry[2 * si + 1] = Ptot * hc + htot;
+      if (S1) {
+        hc0 = Ptot * hc + htot;
+        Pc0 = Pc * Ptot;
+      } else {
+        __syncwarp();
+        if (lane == 0) {
+          carry[2 * si] = Pc * Ptot;
+          carry[2 * si + 1] = Ptot * hc + htot;
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
-    // prefetch stage s+2 into the slot used by stage s-1 (its bulk store must have finished reading)
-    if (lane == 0 && s + 2 < nst && is_async(s + 2)) {
+    // prefetch stage f+2 into the slot used by stage f-1 (its bulk store must have finished reading)
+    if (lane == 0 && f + 2 < total) {
       bulk_wait_read<0>();
-      issue(s + 2);
+      issue(f + 2);
     }
-    if (is_async(s)) {
+    if (async_stage) {
       float4 *s4 = reinterpret_cast<float4 *>(su + lane * FI);
 #pragma unroll
       for (int j = 0; j < FI / 2; ++j) s4[j] = make_float4(out[2 * j].re, out[2 * j].im, out[2 * j + 1].re, out[2 * j + 1].im);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        bulk_s2g(o_row + t0, su, F_U_BYTES);
+        bulk_s2g(rp.o + t0, su, F_U_BYTES);
         bulk_commit();
       }
     } else {
 #pragma unroll
       for (int i = 0; i < FI; ++i) {
         const int t = t0 + lane * FI + i;
-        if (t < L) o_row[t] = out[i];
+        if (t < L) rp.o[t] = out[i];
       }
+      __syncwarp();   // the slot may be refilled by plain loads of the next stage
     }
   }
   if (lane == 0) bulk_wait<0>();
@@ -276,47 +330,53 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
   BwdShared &sh = *reinterpret_cast<BwdShared *>(out_stage + OUT_BYTES);
   cf *st_arr = reinterpret_cast<cf *>(out_stage + OUT_BYTES + sizeof(BwdShared));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t row = blockIdx.x;
-  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
   const int L = p.seqlen, S = S1 ? 1 : p.dstate;
   const int n_chunks = (L + kChunk - 1) / kChunk;
   cf *gcar = st_arr, *anext = st_arr + S, *accA = st_arr + 2 * S, *accB = st_arr + 3 * S, *accC = st_arr + 4 * S;
+  // persistent CTAs: CTA g owns rows g, g + G, ...; the chunks of all its rows (each row walked
+  // from its last chunk to its first) form one stream for the two-buffer pipeline
+  const int64_t nrows = (int64_t)p.batch * p.dim;
+  const int my_rows = (int)((nrows - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  const int total = my_rows * n_chunks;
 
-  const cf *u_row = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
-  const cf *do_row = reinterpret_cast<const cf *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
-  const float *d_row = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
-  const float *dA_row = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs +
-                                     (int64_t)d * p.deltaA_ds
-                               : nullptr;
-  cf *du_row = reinterpret_cast<cf *>(p.du) + (int64_t)b * p.du_bs + (int64_t)d * p.du_ds;
-  float *dd_row = reinterpret_cast<float *>(p.ddelta) + (int64_t)b * p.ddelta_bs + (int64_t)d * p.ddelta_ds;
-  float *ddA_row = HAS_DA ? reinterpret_cast<float *>(p.ddeltaA) + (int64_t)b * p.ddeltaA_bs +
-                                (int64_t)d * p.ddeltaA_ds
-                          : nullptr;
-  const cf *Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
-  const cf *Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
-  const cf *xrow = p.x ? reinterpret_cast<const cf *>(p.x) + row * n_chunks * 2 * S : nullptr;
-
-  bool tma_ok = ((reinterpret_cast<uintptr_t>(u_row) | reinterpret_cast<uintptr_t>(do_row) |
-                  reinterpret_cast<uintptr_t>(d_row) | reinterpret_cast<uintptr_t>(du_row) |
-                  reinterpret_cast<uintptr_t>(dd_row)) & 15) == 0;
-  if (HAS_DA) tma_ok = tma_ok && (((reinterpret_cast<uintptr_t>(dA_row) | reinterpret_cast<uintptr_t>(ddA_row)) & 15) == 0);
-
+  struct RowPtrs { const cf *u, *dout; const float *d, *dA; cf *du; float *dd, *ddA; bool tma; };
+  auto row_ptrs = [&](int64_t row) {
+    const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+    RowPtrs r;
+    r.u = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+    r.dout = reinterpret_cast<const cf *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
+    r.d = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+    r.dA = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs + (int64_t)d * p.deltaA_ds
+                  : nullptr;
+    r.du = reinterpret_cast<cf *>(p.du) + (int64_t)b * p.du_bs + (int64_t)d * p.du_ds;
+    r.dd = reinterpret_cast<float *>(p.ddelta) + (int64_t)b * p.ddelta_bs + (int64_t)d * p.ddelta_ds;
+    r.ddA = HAS_DA ? reinterpret_cast<float *>(p.ddeltaA) + (int64_t)b * p.ddeltaA_bs + (int64_t)d * p.ddeltaA_ds
+                   : nullptr;
+    r.tma = ((reinterpret_cast<uintptr_t>(r.u) | reinterpret_cast<uintptr_t>(r.dout) | reinterpret_cast<uintptr_t>(r.d) |
+              reinterpret_cast<uintptr_t>(r.du) | reinterpret_cast<uintptr_t>(r.dd)) & 15) == 0;
+    if (HAS_DA) r.tma = r.tma && (((reinterpret_cast<uintptr_t>(r.dA) | reinterpret_cast<uintptr_t>(r.ddA)) & 15) == 0);
+    return r;
+  };
   auto buf_u = [&](int k) { return reinterpret_cast<cf *>(smem_raw + (size_t)k * BUF_BYTES); };
   auto buf_do = [&](int k) { return reinterpret_cast<cf *>(smem_raw + (size_t)k * BUF_BYTES + B_U_BYTES); };
   auto buf_d = [&](int k) { return reinterpret_cast<float *>(smem_raw + (size_t)k * BUF_BYTES + 2 * B_U_BYTES); };
   auto buf_dA = [&](int k) {
     return reinterpret_cast<float *>(smem_raw + (size_t)k * BUF_BYTES + 2 * B_U_BYTES + B_D_BYTES);
   };
-  auto is_async = [&](int c) { return tma_ok && (c + 1) * kChunk <= L; };
-  auto issue = [&](int c, int k) {   // one thread
-    if (c < 0 || !is_async(c)) return;
+  // stream item f: row blockIdx.x + (f / n_chunks) * gridDim.x, chunk n_chunks - 1 - f % n_chunks
+  auto issue = [&](int f) {   // one thread
+    if (f >= total) return;
+    const int c = n_chunks - 1 - f % n_chunks;
+    if ((c + 1) * kChunk > L) return;
+    const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x);
+    if (!r.tma) return;
+    const int k = f & 1;
     const int64_t t0 = (int64_t)c * kChunk;
     mbar_expect_tx(&sh.bar[k], BUF_BYTES);
-    bulk_g2s(buf_u(k), u_row + t0, B_U_BYTES, &sh.bar[k]);
-    bulk_g2s(buf_do(k), do_row + t0, B_U_BYTES, &sh.bar[k]);
-    bulk_g2s(buf_d(k), d_row + t0, B_D_BYTES, &sh.bar[k]);
-    if (HAS_DA) bulk_g2s(buf_dA(k), dA_row + t0, B_D_BYTES, &sh.bar[k]);
+    bulk_g2s(buf_u(k), r.u + t0, B_U_BYTES, &sh.bar[k]);
+    bulk_g2s(buf_do(k), r.dout + t0, B_U_BYTES, &sh.bar[k]);
+    bulk_g2s(buf_d(k), r.d + t0, B_D_BYTES, &sh.bar[k]);
+    if (HAS_DA) bulk_g2s(buf_dA(k), r.dA + t0, B_D_BYTES, &sh.bar[k]);
   };
 
   if (tid == 0) {
@@ -325,35 +385,54 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     mbar_fence_init();
     fence_proxy_async();
   }
-  for (int i = tid; i < S; i += BT) {
-    gcar[i] = cf(0.f, 0.f);
-    anext[i] = cf(1.f, 0.f);
-    accA[i] = accB[i] = accC[i] = cf(0.f, 0.f);
-  }
   __syncthreads();
-  // chunk n_chunks-1-j uses buffer j&1
-  if (tid == 0) { issue(n_chunks - 1, 0); issue(n_chunks - 2, 1); }
+  if (tid == 0) { issue(0); issue(1); }
 
   bool failed = false;
-  int used0 = 0, used1 = 0;   // completed async fills of buffer 0 / 1 (barrier phase)
+  uint32_t phase_bits = 0;
   bool stores_pending = false;
-  for (int j = 0; j < n_chunks; ++j) {
+  RowPtrs rp = row_ptrs(blockIdx.x);
+  int64_t row = blockIdx.x;
+  const cf *Ap = nullptr, *Cp = nullptr, *xrow = nullptr;
+  cf A0, C0;
+  bool c_one = false;
+  cf dA_acc, dB_acc, dC_acc;   // per-thread partial sums over the row (single-state rows)
+  for (int f = 0; f < total; ++f) {
+    const int j = f % n_chunks;
     const int c = n_chunks - 1 - j;
-    const int k = j & 1;
+    if (j == 0) {   // new row
+      row = blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x;
+      rp = row_ptrs(row);
+      const int d = (int)(row % p.dim);
+      Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
+      Cp = reinterpret_cast<const cf *>(p.C) + (int64_t)d * p.C_ds;
+      xrow = p.x ? reinterpret_cast<const cf *>(p.x) + row * n_chunks * 2 * S : nullptr;
+      A0 = Ap[0];
+      C0 = Cp[0];
+      c_one = S1 && C0.re == 1.f && C0.im == 0.f;
+      dA_acc = dB_acc = dC_acc = cf(0.f, 0.f);
+      __syncthreads();   // the previous row's tail has consumed gcar / anext / acc*
+      for (int i = tid; i < S; i += BT) {
+        gcar[i] = cf(0.f, 0.f);
+        anext[i] = cf(1.f, 0.f);
+        accA[i] = accB[i] = accC[i] = cf(0.f, 0.f);
+      }
+    }
+    const int k = f & 1;
     const int t0 = c * kChunk;
+    const bool async_chunk = rp.tma && (c + 1) * kChunk <= L;
     cf *su = buf_u(k), *sdo = buf_do(k);
     float *sd = buf_d(k), *sdA = buf_dA(k);
-    if (is_async(c)) {
-      const int used = k ? used1 : used0;
-      if (!mbar_wait(&sh.bar[k], (uint32_t)(used & 1))) failed = true;
-      if (k) ++used1; else ++used0;
+    if (async_chunk) {
+      if (!mbar_wait(&sh.bar[k], (phase_bits >> k) & 1u)) failed = true;
+      phase_bits ^= (1u << k);
     } else {
       for (int i = tid; i < kChunk; i += BT) {
         const int t = t0 + i;
-        su[i] = t < L ? u_row[t] : cf(0.f, 0.f);
-        sdo[i] = t < L ? do_row[t] : cf(0.f, 0.f);
-        sd[i] = t < L ? d_row[t] : 0.f;
-        if (HAS_DA) sdA[i] = t < L ? dA_row[t] : 0.f;
+        su[i] = t < L ? rp.u[t] : cf(0.f, 0.f);
+        sdo[i] = t < L ? rp.dout[t] : cf(0.f, 0.f);
+        sd[i] = t < L ? rp.d[t] : 0.f;
+        if (HAS_DA) sdA[i] = t < L ? rp.dA[t] : 0.f;
       }
     }
     if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
@@ -387,29 +466,36 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         for (int i = 0; i < BI; ++i) dAv[i] = dl[i];
       }
     }
-    // the chunk now lives in registers: refill this buffer with the chunk two steps ahead
+    // the chunk now lives in registers: refill this buffer with the stream item two steps ahead
     __syncthreads();
-    if (tid == 0) issue(c - 2, k);
+    if (tid == 0) issue(f + 2);
     cf du[BI];
     float ddl[BI], ddA[BI];
+    if (!S1) {
 #pragma unroll
-    for (int i = 0; i < BI; ++i) { du[i] = cf(0.f, 0.f); ddl[i] = 0.f; ddA[i] = 0.f; }
+      for (int i = 0; i < BI; ++i) { du[i] = cf(0.f, 0.f); ddl[i] = 0.f; ddA[i] = 0.f; }
+    }
 
     for (int si = 0; si < S; ++si) {
       const int par = si & 1;
-      const cf An = Ap[(int64_t)si * p.A_ns];
-      const cf Cn = Cp[(int64_t)si * p.C_ns];
-      cf a[BI], kk[BI], h[BI];
+      const cf An = S1 ? A0 : Ap[(int64_t)si * p.A_ns];
+      const cf Cc = conj(S1 ? C0 : Cp[(int64_t)si * p.C_ns]);
+      // checkpoint of the previous chunk: issued early so the load overlaps the local scans
+      cf hpre = cf(0.f, 0.f);
+      if (c > 0) hpre = xrow[(int64_t)(c - 1) * 2 * S + 2 * si + 1];
+      constexpr bool kUnitK = (DM == B200_DISC_DIRAC);   // k_t = 1: the input term is u_t itself
+      cf a[BI], kk[kUnitK ? 1 : BI], h[BI];
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
-        s5_coef<DM>(An, dl[i], dAv[i], a[i], kk[i]);
-        if (t0 + tid * BI + i >= L) { a[i] = cf(1.f, 0.f); kk[i] = cf(0.f, 0.f); }
+        if constexpr (kUnitK) a[i] = cexp(An * dAv[i]);
+        else s5_coef<DM>(An, dl[i], dAv[i], a[i], kk[i]);
       }
+      auto beta = [&](int i) { return kUnitK ? u[i] : kk[kUnitK ? 0 : i] * u[i]; };
       // forward, pass 1: per-thread aggregate, warp scan, cross-warp prefix
       cf P = cf(1.f, 0.f), hh = cf(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
-        hh = a[i] * hh + kk[i] * u[i];
+        hh = a[i] * hh + beta(i);
         P = P * a[i];
       }
 #pragma unroll
@@ -421,7 +507,6 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
       if (lane == 0) sh.afirst[warp] = a[0];
       cf a_next_lane = shfl_down(a[0], 1);   // a_{t+1} for this thread's last item
       __syncthreads();
-      cf hpre = (c > 0) ? xrow[(int64_t)(c - 1) * 2 * S + 2 * si + 1] : cf(0.f, 0.f);
       for (int w = 0; w < warp; ++w) hpre = sh.wtot_a[par][w] * hpre + sh.wtot_h[par][w];
       cf Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
       if (lane == 0) { Pex = cf(1.f, 0.f); hex = cf(0.f, 0.f); }
@@ -431,18 +516,17 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         cf hc = hin;
 #pragma unroll
         for (int i = 0; i < BI; ++i) {
-          hc = a[i] * hc + kk[i] * u[i];
+          hc = a[i] * hc + beta(i);
           h[i] = hc;
         }
       }
       if (lane == 31) a_next_lane = (warp == BWARPS - 1) ? anext[si] : sh.afirst[warp + 1];
       // reverse, pass 1: aggregate of g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C)
-      const cf Cc = conj(Cn);
       cf gg = cf(0.f, 0.f), Q = cf(1.f, 0.f);
 #pragma unroll
       for (int i = BI - 1; i >= 0; --i) {
         const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
-        gg = an * gg + dy[i] * Cc;
+        gg = an * gg + (c_one ? dy[i] : dy[i] * Cc);
         Q = Q * an;
       }
 #pragma unroll
@@ -468,11 +552,16 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
 #pragma unroll
       for (int i = BI - 1; i >= 0; --i) {
         const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
-        G = an * G + dy[i] * Cc;
+        G = an * G + (c_one ? dy[i] : dy[i] * Cc);
         const cf hprev = (i == 0) ? hin : h[i - 1];
         const float dv = dl[i], dav = dAv[i];
-        du[i] = du[i] + G * conj(kk[i]);
-        dB_l = dB_l + G * conj(kk[i] * u[i]);
+        if constexpr (kUnitK) {
+          du[i] = S1 ? G : du[i] + G;
+          dB_l = dB_l + G * conj(u[i]);
+        } else {
+          du[i] = S1 ? G * conj(kk[kUnitK ? 0 : i]) : du[i] + G * conj(kk[kUnitK ? 0 : i]);
+          dB_l = dB_l + G * conj(beta(i));
+        }
         dC_l = dC_l + dy[i] * conj(h[i]);
         float d_dl = 0.f, d_dA = 0.f;
         if constexpr (DM == B200_DISC_ZOH) {
@@ -480,7 +569,7 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
           const cf ah = a[i] * hprev;
           d_dA = (G * conj(An * ah)).re;
           d_dl = (G * conj(E * u[i])).re;
-          dA_l = dA_l + G * conj(ah * dav + u[i] * ((E * dv - kk[i]) / An));
+          dA_l = dA_l + G * conj(ah * dav + u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / An));
         } else if constexpr (DM == B200_DISC_BILINEAR) {
           const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dv));
           const cf rA = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dav));
@@ -489,31 +578,41 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
           d_dl = (G * conj(r2 * u[i])).re;
           dA_l = dA_l + G * conj(hprev * rA2 * dav + r2 * u[i] * (0.5f * dv * dv));
         } else {
-          const cf ah = a[i] * hprev;
-          d_dA = (G * conj(An * ah)).re;
-          dA_l = dA_l + G * conj(ah * dav);
+          // G conj(A a h_prev) and G conj(dA a h_prev) share t = G conj(a h_prev)
+          const cf t = G * conj(a[i] * hprev);
+          d_dA = (t * conj(An)).re;
+          dA_l = dA_l + t * dav;
         }
-        if (t0 + tid * BI + i >= L) { d_dl = 0.f; d_dA = 0.f; }
-        if (HAS_DA) { ddl[i] += d_dl; ddA[i] += d_dA; }
-        else ddl[i] += d_dl + d_dA;
+        if (S1) {
+          if (HAS_DA) { ddl[i] = d_dl; ddA[i] = d_dA; }
+          else ddl[i] = d_dl + d_dA;
+        } else {
+          if (HAS_DA) { ddl[i] += d_dl; ddA[i] += d_dA; }
+          else ddl[i] += d_dl + d_dA;
+        }
       }
-      dA_l = warp_sum(dA_l);
-      dB_l = warp_sum(dB_l);
-      dC_l = warp_sum(dC_l);
-      if (lane == 0) { sh.red[0][warp] = dA_l; sh.red[1][warp] = dB_l; sh.red[2][warp] = dC_l; }
-      __syncthreads();
-      if (tid < 3) {
-        cf acc = cf(0.f, 0.f);
+      if (S1) {
+        dA_acc = dA_acc + dA_l;
+        dB_acc = dB_acc + dB_l;
+        dC_acc = dC_acc + dC_l;
+      } else {
+        dA_l = warp_sum(dA_l);
+        dB_l = warp_sum(dB_l);
+        dC_l = warp_sum(dC_l);
+        if (lane == 0) { sh.red[0][warp] = dA_l; sh.red[1][warp] = dB_l; sh.red[2][warp] = dC_l; }
+        __syncthreads();
+        if (tid < 3) {
+          cf acc = cf(0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < BWARPS; ++w) acc = acc + sh.red[tid][w];
-        cf *dst = tid == 0 ? accA : (tid == 1 ? accB : accC);
-        dst[si] = dst[si] + acc;
+          for (int w = 0; w < BWARPS; ++w) acc = acc + sh.red[tid][w];
+          cf *dst = tid == 0 ? accA : (tid == 1 ? accB : accC);
+          dst[si] = dst[si] + acc;
+        }
       }
     }
     // ---- write du / ddelta (/ ddeltaA) through the staging area
-    const bool bulk_out = tma_ok && (c + 1) * kChunk <= L;
-    if (bulk_out) {
-      if (tid == 0 && stores_pending) bulk_wait_read<0>();   // previous chunk's stores have left the staging area
+    if (async_chunk) {
+      if (tid == 0 && stores_pending) bulk_wait_read<0>();   // previous stores have left the staging area
       __syncthreads();
       cf *so = reinterpret_cast<cf *>(out_stage);
       float *sod = reinterpret_cast<float *>(out_stage + B_U_BYTES);
@@ -532,9 +631,9 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
       fence_proxy_async();
       __syncthreads();
       if (tid == 0) {
-        bulk_s2g(du_row + t0, so, B_U_BYTES);
-        bulk_s2g(dd_row + t0, sod, B_D_BYTES);
-        if (HAS_DA) bulk_s2g(ddA_row + t0, sodA, B_D_BYTES);
+        bulk_s2g(rp.du + t0, so, B_U_BYTES);
+        bulk_s2g(rp.dd + t0, sod, B_D_BYTES);
+        if (HAS_DA) bulk_s2g(rp.ddA + t0, sodA, B_D_BYTES);
         bulk_commit();
       }
       stores_pending = true;
@@ -543,30 +642,57 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
       for (int i = 0; i < BI; ++i) {
         const int t = t0 + tid * BI + i;
         if (t < L) {
-          du_row[t] = du[i];
-          dd_row[t] = ddl[i];
-          if (HAS_DA) ddA_row[t] = ddA[i];
+          rp.du[t] = du[i];
+          rp.dd[t] = ddl[i];
+          if (HAS_DA) rp.ddA[t] = ddA[i];
+        }
+      }
+    }
+    // ---- end of a row: fold the parameter gradients into dA / dB / dC
+    if (c == 0) {
+      const int d = (int)(row % p.dim);
+      cf *dAp = reinterpret_cast<cf *>(p.dA) + (int64_t)d * p.A_ds;
+      cf *dBp = reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds;
+      cf *dCp = reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds;
+      if (S1) {
+        const cf ra = warp_sum(dA_acc), rb = warp_sum(dB_acc), rc = warp_sum(dC_acc);
+        __syncthreads();   // sh.red is free (no state loop in flight)
+        if (lane == 0) { sh.red[0][warp] = ra; sh.red[1][warp] = rb; sh.red[2][warp] = rc; }
+        __syncthreads();
+        if (tid < 3) {
+          cf acc = cf(0.f, 0.f);
+#pragma unroll
+          for (int w = 0; w < BWARPS; ++w) acc = acc + sh.red[tid][w];
+          cf *dst = tid == 0 ? dAp : (tid == 1 ? dBp : dCp);
+          atomicAdd(&dst->re, acc.re);
+          atomicAdd(&dst->im, acc.im);
+        }
+      } else {
+        __syncthreads();
+        for (int i = tid; i < S; i += BT) {
+          atomicAdd(&dAp[(int64_t)i * p.A_ns].re, accA[i].re);
+          atomicAdd(&dAp[(int64_t)i * p.A_ns].im, accA[i].im);
+          atomicAdd(&dBp[(int64_t)i * p.B_ns].re, accB[i].re);
+          atomicAdd(&dBp[(int64_t)i * p.B_ns].im, accB[i].im);
+          atomicAdd(&dCp[(int64_t)i * p.C_ns].re, accC[i].re);
+          atomicAdd(&dCp[(int64_t)i * p.C_ns].im, accC[i].im);
         }
       }
     }
   }
   if (tid == 0) bulk_wait<0>();
   __syncthreads();
-  if (failed) {
-    if (tid == 0) atomicExch(&g_simpscan_status, 2);
-    return;
+  if (failed && tid == 0) atomicExch(&g_simpscan_status, 2);
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
   }
-  cf *dAp = reinterpret_cast<cf *>(p.dA) + (int64_t)d * p.A_ds;
-  cf *dBp = reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds;
-  cf *dCp = reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds;
-  for (int i = tid; i < S; i += BT) {
-    atomicAdd(&dAp[(int64_t)i * p.A_ns].re, accA[i].re);
-    atomicAdd(&dAp[(int64_t)i * p.A_ns].im, accA[i].im);
-    atomicAdd(&dBp[(int64_t)i * p.B_ns].re, accB[i].re);
-    atomicAdd(&dBp[(int64_t)i * p.B_ns].im, accB[i].im);
-    atomicAdd(&dCp[(int64_t)i * p.C_ns].re, accC[i].re);
-    atomicAdd(&dCp[(int64_t)i * p.C_ns].im, accC[i].im);
-  }
+  return n;
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes) {
@@ -577,14 +703,20 @@ template <typename K> int set_smem(K kernel, size_t bytes) {
   return 0;
 }
 
-template <int DM, bool HAS_DA> int launch_fwd(const b200_simpscan_args &a, cudaStream_t st) {
+template <int DM, bool HAS_DA, bool S1> int launch_fwd_s(const b200_simpscan_args &a, cudaStream_t st) {
   constexpr int SLOT_BYTES = F_U_BYTES + F_D_BYTES * (HAS_DA ? 2 : 1);
   const int64_t rows = (int64_t)a.batch * a.dim;
   const size_t smem = (size_t)FWARPS * FNS * SLOT_BYTES + FWARPS * FNS * 8 + (size_t)FWARPS * 2 * a.dstate * sizeof(cf);
-  auto k = simpscan_fwd_kernel<DM, HAS_DA>;
+  auto k = simpscan_fwd_kernel<DM, HAS_DA, S1>;
   if (int e = set_smem(k, smem)) return e;
-  k<<<(unsigned)((rows + FWARPS - 1) / FWARPS), FWARPS * 32, smem, st>>>(a);
+  int64_t grid = (rows + FWARPS - 1) / FWARPS;
+  const int64_t resident = (int64_t)sm_count() * 7;   // CTAs that fit at once (7 per SM)
+  if (grid > resident) grid = resident;
+  k<<<(unsigned)grid, FWARPS * 32, smem, st>>>(a);
   return launch_status();
+}
+template <int DM, bool HAS_DA> int launch_fwd(const b200_simpscan_args &a, cudaStream_t st) {
+  return a.dstate == 1 ? launch_fwd_s<DM, HAS_DA, true>(a, st) : launch_fwd_s<DM, HAS_DA, false>(a, st);
 }
 template <int DM, bool HAS_DA, bool S1> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
   constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
@@ -593,7 +725,10 @@ template <int DM, bool HAS_DA, bool S1> int launch_bwd_s(const b200_simpscan_arg
   const size_t smem = 2 * (size_t)BUF_BYTES + OUT_BYTES + sizeof(BwdShared) + (size_t)5 * a.dstate * sizeof(cf);
   auto k = simpscan_bwd_kernel<DM, HAS_DA, S1>;
   if (int e = set_smem(k, smem)) return e;
-  k<<<(unsigned)rows, BT, smem, st>>>(a);
+  int64_t grid = rows;
+  const int64_t resident = (int64_t)sm_count() * (HAS_DA ? 1 : 2);   // CTAs that fit at once
+  if (grid > resident) grid = resident;
+  k<<<(unsigned)grid, BT, smem, st>>>(a);
   return launch_status();
 }
 template <int DM, bool HAS_DA> int launch_bwd(const b200_simpscan_args &a, cudaStream_t st) {
