@@ -245,6 +245,24 @@ typedef struct b200_s4_args {
 int64_t b200_s4_bwd_scratch_bytes(int32_t batch, int32_t n, int32_t seqlen);
 int b200_cauchy_fwd(const b200_s4_args *args, void *stream);
 int b200_cauchy_bwd(const b200_s4_args *args, void *stream);
+
+/* Cauchy backward for callers that cannot provide scratch memory.  It has no
+ * counterpart in lrnnx.  Same inputs, outputs and results as b200_cauchy_bwd, but
+ * `scratch` / `scratch_bytes` of the argument block are ignored: the partial sums
+ * go to a fixed B200_CAUCHY_STATIC_SCRATCH_BYTES area that is part of the library
+ * image on every GPU that loads it.  The call performs no cudaMalloc / cudaFree
+ * and uses no allocating library routine.
+ *  - Limit: problems whose b200_s4_bwd_scratch_bytes(batch, n, seqlen) exceeds the
+ *    area are rejected with B200_ERR_TOO_LARGE (nothing is launched).
+ *  - The first call on each device looks up the area's device address (the device
+ *    the call should run on must be current); make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the one area, which keeps the previous call's
+ *    contents (no part of it needs clearing: each call overwrites every slot it
+ *    later reads).  Two calls that overlap in time on the same GPU, e.g. on
+ *    different streams, race on it; serialise them. */
+#define B200_CAUCHY_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int b200_cauchy_bwd_static(const b200_s4_args *args, void *stream);
 int b200_vand_fwd(const b200_s4_args *args, void *stream);
 int b200_vand_bwd(const b200_s4_args *args, void *stream);
 

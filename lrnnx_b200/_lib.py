@@ -23,7 +23,7 @@ ENTRY_POINTS = (
     "b200_selscan_fwd", "b200_selscan_bwd", "b200_selscan_fixup",
     "b200_simpscan_fwd", "b200_simpscan_bwd",
     "b200_ssu_step",
-    "b200_cauchy_fwd", "b200_cauchy_bwd", "b200_vand_fwd", "b200_vand_bwd",
+    "b200_cauchy_fwd", "b200_cauchy_bwd", "b200_cauchy_bwd_static", "b200_vand_fwd", "b200_vand_bwd",
 )
 
 _SCALARS = {"int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "uint32_t": ctypes.c_uint32,

@@ -243,6 +243,58 @@ int b200_cauchy_bwd(const b200_s4_args *args, void *stream) {
   return run_bwd<false>(*args, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------------------
+// Cauchy backward without any allocation by anybody.
+//
+// Some users of this library cannot hand it device memory beyond the tensors of
+// the call: a plain C or C++ host that links the ABI without a framework
+// allocator, or a serving loop that runs under a frozen memory budget where a
+// cudaMalloc (which may synchronise the device or fail late) is not acceptable.
+// For them the per-chunk partial sums live in a fixed array inside the library
+// image.  Every GPU that loads the library holds the array until the process
+// exits; its size bounds the problem size.
+static __device__ __align__(256) unsigned char g_cauchy_static_scratch[B200_CAUCHY_STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle; the device address has to be
+// asked for, per device, with that device current.
+static void *g_static_scratch_ptr[64] = {};
+
+static int static_scratch_for_current_device(void **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_error("cudaGetDevice: %s", cudaGetErrorString(e)); return (int)e; }
+  B200_REQUIRE(dev >= 0 && dev < 64, B200_ERR_UNSUPPORTED, "cauchy_bwd_static: device ordinal %d not supported", dev);
+  if (!g_static_scratch_ptr[dev]) {
+    void *ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_cauchy_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : B200_ERR_UNSUPPORTED;
+    }
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+int b200_cauchy_bwd_static(const b200_s4_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "cauchy_bwd_static: null argument block");
+  const int64_t need = b200_s4_bwd_scratch_bytes(args->batch, args->n, args->seqlen);
+  B200_REQUIRE(need <= (int64_t)B200_CAUCHY_STATIC_SCRATCH_BYTES, B200_ERR_TOO_LARGE,
+               "cauchy_bwd_static: this problem needs %lld bytes of scratch, the built-in area holds %lld; "
+               "use b200_cauchy_bwd with caller-provided scratch",
+               (long long)need, (long long)B200_CAUCHY_STATIC_SCRATCH_BYTES);
+  b200_s4_args a = *args;
+  void *ptr = nullptr;
+  if (int e = static_scratch_for_current_device(&ptr)) return e;
+  a.scratch = ptr;
+  a.scratch_bytes = B200_CAUCHY_STATIC_SCRATCH_BYTES;
+  if (int e = check(a, true, false)) return e;
+  // Nothing in the area has to start at zero: the first kernel writes every partial-sum slot
+  // that the second kernel reads.
+  return run_bwd<false>(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int b200_vand_fwd(const b200_s4_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "vand_fwd: null argument block");
   if (int e = check(*args, false, true)) return e;
