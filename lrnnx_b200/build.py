@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 
 
 def _newest_header() -> float:
-    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [ROOT.parent / "include" / "lrnnx_b200.h"]
+    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.inc")) + [ROOT.parent / "include" / "lrnnx_b200.h"]
     return max(h.stat().st_mtime for h in hs)
 
 

@@ -163,3 +163,29 @@ def test_argument_errors():
         selective_scan_cuda.fwd(u, u, A, B, B, None, None, None, None, False, "euler")
     with pytest.raises(RuntimeError):
         selective_scan_cuda.fwd(u.cpu(), u, A, B, B, None, None, None, None, False, "mamba")
+
+
+@pytest.mark.parametrize("L", [8, 264, 2048, 2312, 4104])
+@pytest.mark.parametrize("dtype,groups", [(torch.float32, 1), (torch.float32, 2), (torch.bfloat16, 1),
+                                          (torch.float16, 2)])
+def test_throughput_kernel_shape_class(L, dtype, groups):
+    """Shapes served by the packed-fp32 throughput kernels (real A, mamba, variable B/C, dstate 16,
+    channel count a multiple of 16 per group, L a multiple of 8): one and several 256-step
+    stages, a ragged last stage, and a 2048-step checkpoint boundary."""
+    t, g = _make_inputs(2, 32 * groups, 16, L, seed=L, dtype=dtype, groups=groups)
+    if dtype == torch.float32:
+        _oracle_vs_gpu(t, g, "mamba", RTOL32, ATOL32, GRAD_RTOL32, GRAD_ATOL32)
+    else:
+        _oracle_vs_gpu(t, g, "mamba", 3e-2, 1e-2, 3e-2, 2e-2)
+
+
+def test_throughput_kernel_checkpoints():
+    from lrnnx_b200 import selective_scan_cuda
+    t, g = _make_inputs(1, 16, 16, 4360, seed=8, with_z=False)
+    _, _, x_c = O.selective_scan_oracle(**t, delta_softplus=True, return_last_state=True, return_checkpoints=True)
+    cu = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items()}
+    out, x = selective_scan_cuda.fwd(cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], None,
+                                     cu["delta_bias"], None, True, "mamba")
+    assert x.shape == x_c.shape == (1, 16, 3, 32)
+    assert_close(x.cpu()[..., 1::2], x_c[..., 1::2], rtol=RTOL32, atol_scale=ATOL32, name="x state")
+    assert_close(x.cpu()[..., 0::2], x_c[..., 0::2], rtol=1e-3, atol_scale=1e-6, name="x product")
