@@ -116,3 +116,4 @@ __device__ __forceinline__ void stage_rows(unsigned char *dst, const T *src, int
 }  // namespace b200
 
 #include "selscan_fast_fwd.inc"
+#include "selscan_fast_bwd.inc"
