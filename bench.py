@@ -22,7 +22,7 @@ x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
              host cores on a bounded sample of the same workload.
 
 ``--impl reference`` times that CPU implementation alone (rank 0 only).
-Other workloads (``--workload``): s6_cfg0, s6_layer, s6_long, ssu_step, cauchy.
+Other workloads (``--workload``): s6_cfg0, s6_layer, s6_layer_f32, s6_long (sequence-parallel when N > 1), ssu_step.
 """
 from __future__ import annotations
 
@@ -98,6 +98,16 @@ class ClockSampler:
         load = sorted(sm)[len(sm) // 2:] if sm else []
         return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
+# profiles/ (same workload, same kernel); None where no capture exists.
+NCU_TRAFFIC = {
+    ("s5_scan_cfg1", "simpscan_fwd_kernel"): 128.6e6,
+    ("s5_scan_cfg1", "simpscan_bwd_kernel"): 227.2e6,
+    ("s6_layer_cfg2", "selscan_fwd"): 216.5e6,
+    ("s6_layer_cfg2", "selscan_bwd"): 378.8e6,
+}
 
 
 def cn(g, *shape):
@@ -243,6 +253,19 @@ class S6Scan:
         from lrnnx_b200.ops import selective_scan_fn
         self.dev, self.pg, self.ext, self.op = dev, pg, selective_scan_cuda, selective_scan_fn
         h = self.host_inputs()
+        # the long forward-only configuration runs sequence-parallel on N > 1 GPUs: every rank keeps
+        # its slice of the sequence (fixed total work: strong scaling)
+        self.sp = pg is not None and not self.backward
+        if self.sp:
+            import torch.distributed as dist
+            from lrnnx_b200.sp import sp_selective_scan_fwd
+            self.sp_fwd = sp_selective_scan_fwd
+            self.scaling = "strong"
+            r, w = dist.get_rank(), dist.get_world_size()
+            lo, hi = (r * self.L // w) // 8 * 8, ((r + 1) * self.L // w) // 8 * 8 if r + 1 < w else self.L
+            h = {k: (v[..., lo:hi].contiguous() if v.dim() >= 3 else v) for k, v in h.items()}
+            self.describe["parallelism"] = f"sequence-parallel over {w} GPUs: chunk-state all-gather + fix-up"
+            self.fwd_bytes //= w
         self.h = {k: v.pin_memory() for k, v in h.items()}
         self.t = {k: v.to(dev) for k, v in h.items()}
         self.ev = []
@@ -255,6 +278,13 @@ class S6Scan:
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
+        if self.sp:
+            self.sp_fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"], True, self.pg)
+            if record:
+                e[1].record()
+                e[2].record()
+                self.ev.append(e)
+            return None
         out, x, out_z = self.ext.fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"],
                                      None, True, "mamba")
         if record:
@@ -272,6 +302,10 @@ class S6Scan:
 
     def e2e_step(self):
         t = {k: (self.t[k].copy_(self.h[k], non_blocking=True)) for k in ("u", "delta", "B", "C", "z")}
+        if self.sp:
+            y, _ = self.sp_fwd(t["u"], t["delta"], self.t["A"], t["B"], t["C"], self.t["D"], t["z"],
+                               self.t["delta_bias"], True, self.pg)
+            return float((y.float() * self.t["gout"].float()).sum().item())
         leaves = {k: v.detach().requires_grad_(self.backward) for k, v in t.items()}
         A, D, bias = (self.t[k].detach().requires_grad_(self.backward) for k in ("A", "D", "delta_bias"))
         y = self.op(leaves["u"], leaves["delta"], A, leaves["B"], leaves["C"], D, leaves["z"], bias,
@@ -311,6 +345,90 @@ class S6Scan:
         return self.batch * self._cpu_L * self._cpu_dim / self.dim
 
 
+class SsuStep:
+    """Decode step kernel at the BASELINE config 4 shape: 48 layers x selective_state_update with
+    batch 64, d_inner 4096, dstate 16, bf16 activations, fp32 state (one step = 48 launches; the
+    projections, conv and norms of the model are outside the path)."""
+    name = "ssu_step_cfg4"
+    dtype = "bf16 i/o, f32 state"
+    metric, unit = "generated tokens/s (state-update kernels only)", "tokens/s"
+    launches_per_step = 48
+    cpu_sample = "2 of 48 layers, full batch"
+
+    def __init__(self, batch=64, dim=4096, N=16, layers=48):
+        self.batch, self.dim, self.N, self.layers = batch, dim, N, layers
+        self.tokens = batch
+        per_layer = 2 * batch * dim * N * 4 + 4 * batch * dim * 2 + 2 * batch * N * 2 + 4 * dim * N + 8 * dim
+        self.fwd_bytes = per_layer
+        self.describe = {"workload": f"{self.name}: {layers} layers, batch {batch}, d_inner {dim}, dstate {N}",
+                         "global_batch": batch, "seq_len": 1, "launch": "CUDA graph replay of the 48 launches",
+                         "l2": "48 layer states (805 MB) cycle through the 126 MB L2"}
+
+    def _layer(self, g, batch=None):
+        b = batch or self.batch
+        r = lambda *s: torch.randn(*s, generator=g)
+        return dict(state=r(b, self.dim, self.N), x=r(b, self.dim).bfloat16(), dt=r(b, self.dim).bfloat16(),
+                    A=-torch.rand(self.dim, self.N, generator=g) - 0.5, B=r(b, self.N).bfloat16(),
+                    C=r(b, self.N).bfloat16(), D=r(self.dim), z=r(b, self.dim).bfloat16(),
+                    dt_bias=torch.rand(self.dim, generator=g) - 4.0)
+
+    def setup(self, dev, pg):
+        from lrnnx_b200.ops import selective_state_update
+        self.op, self.pg = selective_state_update, pg
+        g = torch.Generator().manual_seed(0)
+        self.layers_t = [{k: v.to(dev) for k, v in self._layer(g).items()} for _ in range(self.layers)]
+        self.h_x = self.layers_t[0]["x"].cpu().pin_memory()
+        self.ev = []
+        # the decode path replays a captured CUDA graph (warm-up on a side stream, then capture),
+        # the pattern of lrnnx/utils/generation.py:143-155
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._eager()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = self._eager()
+
+    def _eager(self):
+        for t in self.layers_t:
+            out = self.op(t["state"], t["x"], t["dt"], t["A"], t["B"], t["C"], t["D"], t["z"], t["dt_bias"], True)
+        return out
+
+    def step(self, record=False):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(2)] if record else None
+        if record:
+            e[0].record()
+        self.graph.replay()
+        if record:
+            e[1].record()
+            self.ev.append(e)
+        return self.out
+
+    def e2e_step(self):
+        self.layers_t[0]["x"].copy_(self.h_x, non_blocking=True)
+        out = self.step()
+        return float(out.float().sum().item())
+
+    def e2e_bytes(self):
+        return self.h_x.numel() * 2, 4
+
+    def kernel_rooflines(self):
+        ms = statistics.mean(a[0].elapsed_time(a[1]) for a in self.ev) / self.layers
+        return {"ssu_vec_kernel": (self.fwd_bytes, ms)}
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            g = torch.Generator().manual_seed(0)
+            self._cpu = [self._layer(g) for _ in range(2)]
+        for t in self._cpu:
+            a = {k: (v.float() if v.dtype == torch.bfloat16 else v) for k, v in t.items() if k != "state"}
+            O.selective_state_update_oracle(t["state"], **a, dt_softplus=True)
+        return self.batch * 2 / self.layers
+
+
 def make_workload(name):
     if name in ("s5_scan", "s5_scan_cfg1", "default"):
         return S5Scan()
@@ -322,6 +440,8 @@ def make_workload(name):
         return S6Scan("s6_layer_f32", 8, 1536, 2048, 16, torch.float32)
     if name == "s6_long":
         return S6Scan("s6_long_cfg3", 1, 5120, 131072, 16, torch.bfloat16, backward=False)
+    if name in ("ssu_step", "ssu_step_cfg4"):
+        return SsuStep()
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -405,17 +525,20 @@ def run_ours(args, wl):
         for kname, (nbytes, ms) in wl.kernel_rooflines().items():
             ach = nbytes / (ms * 1e-3) / 1e9
             roofs[kname] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                            "traffic": None, "algorithmic_bytes": nbytes, "ms_per_launch": ms,
+                            "traffic": NCU_TRAFFIC.get((wl.name, kname)), "algorithmic_bytes": nbytes,
+                            "ms_per_launch": ms,
                             "peak_source": peak_kind}
         dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
         cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
         h2d, d2h = wl.e2e_bytes()
-        line = {"metric": wl.metric, "value": world * wl.tokens / (ms_step * 1e-3), "unit": wl.unit,
+        total_tokens = wl.tokens if getattr(wl, "scaling", "weak") == "strong" else world * wl.tokens
+        line = {"metric": wl.metric, "value": total_tokens / (ms_step * 1e-3), "unit": wl.unit,
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+                "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
+                "dtype": wl.dtype,
                 "data": "synthetic (seeded CPU generator, copied to the GPU)", "config": wl.describe,
                 "clocks": clocks,
-                "e2e": {"value": world * wl.tokens / (ms_e2e * 1e-3), "unit": wl.unit, "ms_per_step": ms_e2e,
+                "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": wl.unit, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
                 "gpu_launches": wl.launches_per_step * args.steps,
                 "roofline": dict(roofs[dominant], kernel=dominant),

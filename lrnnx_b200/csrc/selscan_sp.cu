@@ -1,0 +1,119 @@
+// Sequence-parallel fix-up pass of the selective scan (no counterpart in lrnnx, which is
+// single-GPU).  A rank that scanned its slice of the sequence from a zero state receives the
+// state h_in that actually enters the slice (folded from the summaries of the earlier ranks)
+// and adds what that state contributes:
+//     out[t]   += sum_n C[t, n] * exp(A_n * cum_t) * h_in[n],   cum_t = sum_{k <= t} delta'_k
+//     x[c].h   += x[c].P * h_in,      x[c].P *= p_in            (checkpoints of the slice)
+// and recomputes out_z = out * silu(z) where out changed.  delta' is delta after bias and
+// softplus.  Valid for real A with a = exp(delta' A) ("mamba", and "zoh"/"dirac" without
+// deltaA, whose transition is the same) and variable C.
+//
+// One warp per (batch, channel) row, one timestep per lane, 32 steps per iteration: delta is
+// read coalesced, its running sum is a warp scan plus a carried total, and C[n, t] is a
+// coalesced read per state.  The contribution decays like exp(A cum_t); a row stops as soon
+// as its slowest-decaying state is below 2^-60 of its entry value, so the pass usually
+// touches only the first few hundred steps of a slice instead of all of it.
+#include "common.cuh"
+#include "dispatch.h"
+
+namespace b200 {
+namespace {
+
+constexpr int SPW = 4;   // rows (warps) per CTA
+
+__global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_selscan_fixup_args q) {
+  const b200_selscan_fwd_args &p = q.f;
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * SPW + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int g = d / (p.dim / p.n_groups);
+  const int N = p.dstate, L = p.seqlen, dt = p.dtype;
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  float *A2 = sm + warp * 2 * N;     // A * log2(e)
+  float *hin = A2 + N;
+  const float *A = reinterpret_cast<const float *>(p.A) + (int64_t)d * p.A_ds;
+  const float *hsrc = reinterpret_cast<const float *>(q.h_in) + row * N;
+  const float *psrc = reinterpret_cast<const float *>(q.p_in) + row * N;
+  float amax = -INFINITY;            // slowest decay of the row
+  for (int n = lane; n < N; n += 32) {
+    const float a = A[(int64_t)n * p.A_ns];
+    A2[n] = a * kLog2e;
+    hin[n] = hsrc[n];
+    amax = fmaxf(amax, a * kLog2e);
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  __syncwarp();
+  // checkpoints: state and product entries of every chunk of the slice
+  float *xrow = reinterpret_cast<float *>(p.x) + row * n_chunks * 2 * N;
+  for (int i = lane; i < n_chunks * N; i += 32) {
+    const int c = i / N, n = i % N;
+    const float P = xrow[(int64_t)c * 2 * N + 2 * n];
+    xrow[(int64_t)c * 2 * N + 2 * n + 1] += P * hin[n];
+    xrow[(int64_t)c * 2 * N + 2 * n] = P * psrc[n];
+  }
+  const int64_t dl_off = (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const int64_t o_off = (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const int64_t z_off = (int64_t)b * p.z_bs + (int64_t)d * p.z_ds;
+  const int64_t oz_off = (int64_t)b * p.out_z_bs + (int64_t)d * p.out_z_ds;
+  const int64_t c_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
+  float carry = 0.f;                 // sum of delta' over the steps already processed
+  for (int t0 = 0; t0 < L; t0 += 32) {
+    if (amax * carry < -60.f) break; // every state has decayed below 2^-60 (carry is warp-uniform)
+    const int t = t0 + lane;
+    float dv = 0.f;
+    if (t < L) {
+      dv = ld_act(p.delta, dt, dl_off + t) + bias;
+      if (p.delta_softplus) dv = softplus20(dv);
+    }
+    float cum = dv;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, cum, off);
+      if (lane >= off) cum += v;
+    }
+    cum += carry;
+    carry = __shfl_sync(0xffffffffu, cum, 31);
+    if (t < L) {
+      float acc = 0.f;
+      for (int n = 0; n < N; ++n) {
+        const float cv = ld_act(p.C, dt, c_off + (int64_t)n * p.C_ns + t);
+        acc = fmaf(cv * exp2f(A2[n] * cum), hin[n], acc);
+      }
+      // out holds the rounded zero-state result; the correction is added in fp32
+      const float o = ld_act(p.out, dt, o_off + t) + acc;
+      st_act(p.out, dt, o_off + t, o);
+      if (p.z) {
+        const float zv = ld_act(p.z, dt, z_off + t);
+        st_act(p.out_z, dt, oz_off + t, o * zv * sigmoidf_(zv));
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "selscan_fixup: null argument block");
+  const b200_selscan_fwd_args &a = args->f;
+  B200_REQUIRE(a.delta && a.A && a.C && a.out && a.x && args->h_in && args->p_in, B200_ERR_NULL,
+               "selscan_fixup: delta, A, C, out, x, h_in, p_in must be non-null");
+  B200_REQUIRE(!a.z || a.out_z, B200_ERR_NULL, "selscan_fixup: out_z is required when z is given");
+  B200_REQUIRE(a.batch > 0 && a.dim > 0 && a.seqlen > 0 && a.dstate > 0 && a.dstate <= kMaxDState && a.n_groups >= 1 &&
+                   a.dim % a.n_groups == 0,
+               B200_ERR_SHAPE, "selscan_fixup: bad sizes");
+  B200_REQUIRE(!a.is_complex && a.var_B && a.var_C && !a.deltaA &&
+                   (a.method == B200_DISC_MAMBA || a.method == B200_DISC_ZOH || a.method == B200_DISC_DIRAC),
+               B200_ERR_UNSUPPORTED,
+               "selscan_fixup supports real A, variable B and C, no deltaA and the mamba / zoh / dirac transitions");
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = (size_t)SPW * 2 * a.dstate * sizeof(float);
+  selscan_fixup_kernel<<<(unsigned)((rows + SPW - 1) / SPW), SPW * 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(*args);
+  return launch_status();
+}
