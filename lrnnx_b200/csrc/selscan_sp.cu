@@ -11,7 +11,8 @@
 // One warp per (batch, channel) row, one timestep per lane, 32 steps per iteration: delta is
 // read coalesced, its running sum is a warp scan plus a carried total, and C[n, t] is a
 // coalesced read per state.  The contribution decays like exp(A cum_t); a row stops as soon
-// as its slowest-decaying state is below 2^-60 of its entry value, so the pass usually
+// as its slowest-decaying state is below 2^-40 (fp32 output) or 2^-20 (16-bit output) of its
+// entry value — far under the output's own rounding —, so the pass usually
 // touches only the first few hundred steps of a slice instead of all of it.
 #include "common.cuh"
 #include "dispatch.h"
@@ -61,8 +62,9 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   const int64_t c_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
   const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
   float carry = 0.f;                 // sum of delta' over the steps already processed
+  const float cutoff = dt == B200_F32 ? -40.f : -20.f;
   for (int t0 = 0; t0 < L; t0 += 32) {
-    if (amax * carry < -60.f) break; // every state has decayed below 2^-60 (carry is warp-uniform)
+    if (amax * carry < cutoff) break;   // every state has decayed away (carry is warp-uniform)
     const int t = t0 + lane;
     float dv = 0.f;
     if (t < L) {

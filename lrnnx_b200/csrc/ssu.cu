@@ -64,7 +64,7 @@ template <> struct Vec16<__half> {
   }
 };
 
-struct RowScalars { float x, dt, dA, Dv, z; bool has_z; };
+struct RowScalars { float x, dt, dA, Dv, z; bool has_z; };   // generic kernel only
 
 __device__ __forceinline__ void step_coef(int method, float A, float dt, float dA, float &a, float &kb) {
   // a: transition; kb: factor multiplying B (per state)
@@ -99,59 +99,110 @@ __device__ __forceinline__ RowScalars load_row(const b200_ssu_args &p, int b, in
   return r;
 }
 
-// Dense rows: state and A contiguous along dstate, 16-byte aligned; A float32.
-template <typename ST, int LPR>
-__global__ void __launch_bounds__(128) ssu_vec_kernel(const b200_ssu_args p) {
+template <typename T> __device__ __forceinline__ float ldt(const void *p, int64_t i);
+template <> __device__ __forceinline__ float ldt<float>(const void *p, int64_t i) { return reinterpret_cast<const float *>(p)[i]; }
+template <> __device__ __forceinline__ float ldt<__nv_bfloat16>(const void *p, int64_t i) {
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+}
+template <> __device__ __forceinline__ float ldt<__half>(const void *p, int64_t i) {
+  return __half2float(reinterpret_cast<const __half *>(p)[i]);
+}
+template <typename T> __device__ __forceinline__ void stt(void *p, int64_t i, float v);
+template <> __device__ __forceinline__ void stt<float>(void *p, int64_t i, float v) { reinterpret_cast<float *>(p)[i] = v; }
+template <> __device__ __forceinline__ void stt<__nv_bfloat16>(void *p, int64_t i, float v) {
+  reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ void stt<__half>(void *p, int64_t i, float v) {
+  reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+}
+
+// Dense rows: state and A contiguous along dstate, 16-byte aligned; A, D, dt_bias float32;
+// x, dt, z, deltaA, B, C, out all of type XT.  Every load of a thread is issued up front and
+// unconditionally typed, so the ~14 independent loads overlap instead of forming a chain.
+// RPT rows per lane group (rows r, r + ROWS, ...; all in the same (batch, head) when RPT > 1, so
+// they share B and C): the state, A and scalar loads of all RPT rows are in flight together,
+// which is what keeps enough bytes in flight to approach the HBM rate on a one-pass kernel.
+template <typename ST, typename XT, int LPR, int RPT>
+__global__ void __launch_bounds__(128, RPT > 1 ? 6 : 8) ssu_vec_kernel(const b200_ssu_args p) {
   constexpr int VEC = Vec16<ST>::N;
   constexpr int ROWS = 128 / LPR;
   const int sub = threadIdx.x % LPR;
-  const int64_t row = (int64_t)blockIdx.x * ROWS + threadIdx.x / LPR;
   const int64_t nrows = (int64_t)p.batch * p.nheads * p.dim;
-  const bool active = row < nrows;
-  const int64_t rr = active ? row : 0;
-  const int m = (int)(rr % p.dim);
-  const int h = (int)((rr / p.dim) % p.nheads);
-  const int b = (int)(rr / ((int64_t)p.dim * p.nheads));
+  const int64_t row0 = (int64_t)blockIdx.x * ROWS * RPT + threadIdx.x / LPR;
+  // with RPT > 1 the launcher guarantees dim % (ROWS * RPT) == 0: no partial CTAs, one (b, h) per CTA
+  const bool active = row0 < nrows;   // inactive lanes recompute row 0 and store nothing (they stay for the shuffles)
+  // 32-bit row decomposition (the launcher sends row counts >= 2^31 to the generic kernel):
+  // 64-bit div/mod would cost more instructions than the whole update of the row
+  const uint32_t rr = active ? (uint32_t)row0 : 0u;
+  const uint32_t rq = rr / (uint32_t)p.dim;
+  const int m0 = (int)(rr - rq * (uint32_t)p.dim);
+  const int b = (int)(rq / (uint32_t)p.nheads);
+  const int h = (int)(rq - (uint32_t)b * (uint32_t)p.nheads);
   const int sb = p.state_batch_indices ? p.state_batch_indices[b] : b;
   const int g = h / (p.nheads / p.ngroups);
-  const RowScalars r = load_row(p, b, h, m);
-  ST *srow = reinterpret_cast<ST *>(p.state) + (int64_t)sb * p.state_bs + (int64_t)h * p.state_hs + (int64_t)m * p.state_ds;
-  const float *arow = reinterpret_cast<const float *>(p.A) + (int64_t)h * p.A_hs + (int64_t)m * p.A_ds;
   const int64_t boff = (int64_t)b * p.B_bs + (int64_t)g * p.B_gs;
   const int64_t coff = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
-  float acc = 0.f;
+  float xv[RPT], dt[RPT], dA[RPT], Dv[RPT], zv[RPT];
+#pragma unroll
+  for (int k = 0; k < RPT; ++k) {
+    const int m = m0 + k * ROWS;
+    xv[k] = ldt<XT>(p.x, (int64_t)b * p.x_bs + (int64_t)h * p.x_hs + (int64_t)m * p.x_ds);
+    dt[k] = ldt<XT>(p.dt, (int64_t)b * p.dt_bs + (int64_t)h * p.dt_hs + (int64_t)m * p.dt_ds);
+    if (p.dt_bias) dt[k] += reinterpret_cast<const float *>(p.dt_bias)[(int64_t)h * p.dt_bias_hs + (int64_t)m * p.dt_bias_ds];
+    Dv[k] = p.D ? reinterpret_cast<const float *>(p.D)[(int64_t)h * p.D_hs + (int64_t)m * p.D_ds] : 0.f;
+    zv[k] = p.z ? ldt<XT>(p.z, (int64_t)b * p.z_bs + (int64_t)h * p.z_hs + (int64_t)m * p.z_ds) : 0.f;
+    dA[k] = p.deltaA ? ldt<XT>(p.deltaA, (int64_t)b * p.deltaA_bs + (int64_t)h * p.deltaA_hs + (int64_t)m * p.deltaA_ds) : 0.f;
+  }
+  float acc[RPT];
+#pragma unroll
+  for (int k = 0; k < RPT; ++k) acc[k] = 0.f;
   for (int n0 = sub * VEC; n0 < p.dstate; n0 += LPR * VEC) {
-    Vec16<ST> sv;
-    if (active) sv.load(srow + n0);
-    float Av[VEC];
-    if (p.A_ns == 1) {
+    Vec16<ST> sv[RPT];
+    float Av[RPT][VEC], Bn[VEC], Cn[VEC];
 #pragma unroll
-      for (int q = 0; q < VEC / 4; ++q) {
-        const float4 t = *reinterpret_cast<const float4 *>(arow + n0 + 4 * q);
-        Av[4 * q] = t.x; Av[4 * q + 1] = t.y; Av[4 * q + 2] = t.z; Av[4 * q + 3] = t.w;
-      }
-    } else {
+    for (int k = 0; k < RPT; ++k) {
+      const int m = m0 + k * ROWS;
+      ST *srow = reinterpret_cast<ST *>(p.state) + (int64_t)sb * p.state_bs + (int64_t)h * p.state_hs + (int64_t)m * p.state_ds;
+      const float *arow = reinterpret_cast<const float *>(p.A) + (int64_t)h * p.A_hs + (int64_t)m * p.A_ds;
+      sv[k].load(srow + n0);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) Av[i] = arow[(int64_t)(n0 + i) * p.A_ns];
+      for (int i = 0; i < VEC; ++i) Av[k][i] = arow[(int64_t)(n0 + i) * p.A_ns];
     }
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-      const float Bn = ld_act(p.B, p.bc_dtype, boff + (int64_t)(n0 + i) * p.B_ns);
-      const float Cn = ld_act(p.C, p.bc_dtype, coff + (int64_t)(n0 + i) * p.C_ns);
-      float a, kb;
-      step_coef(p.method, Av[i], r.dt, r.dA, a, kb);
-      const float s = sv.v[i] * a + kb * Bn * r.x;
-      sv.v[i] = s;
-      acc += s * Cn;
+      Bn[i] = ldt<XT>(p.B, boff + (int64_t)(n0 + i) * p.B_ns);
+      Cn[i] = ldt<XT>(p.C, coff + (int64_t)(n0 + i) * p.C_ns);
     }
-    if (active) sv.store(srow + n0);
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+      float d = dt[k];
+      if (p.dt_softplus) d = softplus20(d);
+      const float da = p.deltaA ? dA[k] : d;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float a, kb;
+        step_coef(p.method, Av[k][i], d, da, a, kb);
+        const float s = sv[k].v[i] * a + kb * Bn[i] * xv[k];
+        sv[k].v[i] = s;
+        acc[k] += s * Cn[i];
+      }
+      if (active) {
+        const int m = m0 + k * ROWS;
+        ST *srow = reinterpret_cast<ST *>(p.state) + (int64_t)sb * p.state_bs + (int64_t)h * p.state_hs + (int64_t)m * p.state_ds;
+        sv[k].store(srow + n0);
+      }
+    }
   }
 #pragma unroll
-  for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (active && sub == 0) {
-    float out = acc + r.Dv * r.x;
-    if (r.has_z) out *= r.z * sigmoidf_(r.z);
-    st_act(p.out, p.x_dtype, (int64_t)b * p.out_bs + (int64_t)h * p.out_hs + (int64_t)m * p.out_ds, out);
+  for (int k = 0; k < RPT; ++k) {
+    float a = acc[k];
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (active && sub == 0) {
+      float out = a + Dv[k] * xv[k];
+      if (p.z) out *= zv[k] * sigmoidf_(zv[k]);
+      stt<XT>(p.out, (int64_t)b * p.out_bs + (int64_t)h * p.out_hs + (int64_t)(m0 + k * ROWS) * p.out_ds, out);
+    }
   }
 }
 
@@ -196,21 +247,33 @@ __global__ void __launch_bounds__(128) ssu_generic_kernel(const b200_ssu_args p)
   }
 }
 
-template <typename ST> int launch_vec(const b200_ssu_args &a, cudaStream_t st) {
-  constexpr int VEC = Vec16<ST>::N;
+template <typename ST, typename XT, int LPR> int launch_vec_l(const b200_ssu_args &a, cudaStream_t st) {
+  constexpr int ROWS = 128 / LPR;
   const int64_t nrows = (int64_t)a.batch * a.nheads * a.dim;
-  int lpr = 1;
-  while (lpr < 32 && lpr * VEC < a.dstate) lpr <<= 1;
-  const unsigned grid = (unsigned)((nrows + (128 / lpr) - 1) / (128 / lpr));
-  switch (lpr) {
-    case 1: ssu_vec_kernel<ST, 1><<<grid, 128, 0, st>>>(a); break;
-    case 2: ssu_vec_kernel<ST, 2><<<grid, 128, 0, st>>>(a); break;
-    case 4: ssu_vec_kernel<ST, 4><<<grid, 128, 0, st>>>(a); break;
-    case 8: ssu_vec_kernel<ST, 8><<<grid, 128, 0, st>>>(a); break;
-    case 16: ssu_vec_kernel<ST, 16><<<grid, 128, 0, st>>>(a); break;
-    default: ssu_vec_kernel<ST, 32><<<grid, 128, 0, st>>>(a); break;
+  if (a.dim % (ROWS * 2) == 0) {
+    ssu_vec_kernel<ST, XT, LPR, 2><<<(unsigned)(nrows / (ROWS * 2)), 128, 0, st>>>(a);
+  } else {
+    ssu_vec_kernel<ST, XT, LPR, 1><<<(unsigned)((nrows + ROWS - 1) / ROWS), 128, 0, st>>>(a);
   }
   return launch_status();
+}
+template <typename ST, typename XT> int launch_vec(const b200_ssu_args &a, cudaStream_t st) {
+  constexpr int VEC = Vec16<ST>::N;
+  int lpr = 1;
+  while (lpr < 32 && lpr * VEC < a.dstate) lpr <<= 1;
+  switch (lpr) {
+    case 1: return launch_vec_l<ST, XT, 1>(a, st);
+    case 2: return launch_vec_l<ST, XT, 2>(a, st);
+    case 4: return launch_vec_l<ST, XT, 4>(a, st);
+    case 8: return launch_vec_l<ST, XT, 8>(a, st);
+    case 16: return launch_vec_l<ST, XT, 16>(a, st);
+    default: return launch_vec_l<ST, XT, 32>(a, st);
+  }
+}
+template <typename ST> int launch_vec_x(const b200_ssu_args &a, cudaStream_t st) {
+  if (a.x_dtype == B200_F32) return launch_vec<ST, float>(a, st);
+  if (a.x_dtype == B200_BF16) return launch_vec<ST, __nv_bfloat16>(a, st);
+  return launch_vec<ST, __half>(a, st);
 }
 
 int launch_generic(const b200_ssu_args &a, cudaStream_t st) {
@@ -255,10 +318,14 @@ extern "C" int b200_ssu_step(const b200_ssu_args *args, void *stream) {
                      (reinterpret_cast<uintptr_t>(a.state) % 16 == 0) &&
                      (a.state_bs * es) % 16 == 0 && (a.state_hs * es) % 16 == 0 && (a.state_ds * es) % 16 == 0 &&
                      (a.A_ns != 1 || ((reinterpret_cast<uintptr_t>(a.A) % 16 == 0) && a.A_hs % 4 == 0 && a.A_ds % 4 == 0));
-  if (dense) {
-    if (a.state_dtype == B200_F32) return launch_vec<float>(a, st);
-    if (a.state_dtype == B200_BF16) return launch_vec<__nv_bfloat16>(a, st);
-    return launch_vec<__half>(a, st);
+  // the typed kernel wants one activation dtype (x, dt, z, deltaA, B, C) and float32 D / dt_bias
+  const bool uniform = a.dt_dtype == a.x_dtype && a.bc_dtype == a.x_dtype && (!a.z || a.z_dtype == a.x_dtype) &&
+                       (!a.deltaA || a.deltaA_dtype == a.x_dtype) && (!a.D || a.D_dtype == B200_F32) &&
+                       (!a.dt_bias || a.dt_bias_dtype == B200_F32);
+  if (dense && uniform && (int64_t)a.batch * a.nheads * a.dim < (int64_t(1) << 31)) {
+    if (a.state_dtype == B200_F32) return launch_vec_x<float>(a, st);
+    if (a.state_dtype == B200_BF16) return launch_vec_x<__nv_bfloat16>(a, st);
+    return launch_vec_x<__half>(a, st);
   }
   return launch_generic(a, st);
 }
