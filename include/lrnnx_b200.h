@@ -74,7 +74,13 @@ typedef struct b200_selscan_fwd_args {
   int32_t var_B, var_C;
   int32_t delta_softplus;
   int32_t method;           /* B200_DISC_* */
-  int32_t reserved0;
+  int32_t l_segments;       /* forward only; 0 or 1: plain scan.  S > 1: the sequence is cut into S
+                               segments of ceil(seqlen/S) steps rounded up to a multiple of 2048, each
+                               scanned from a zero state by its own thread blocks (more parallelism for
+                               long rows); out, out_z and x of segments >= 1 are then zero-start results
+                               that the caller must stitch with b200_selscan_fixup (n_segments = S).
+                               Honoured only on the shape class served by the throughput kernel,
+                               rejected with B200_ERR_UNSUPPORTED elsewhere. */
   const void *u, *delta, *A, *B, *C;
   const void *D, *z, *delta_bias, *deltaA;      /* nullable */
   void *out;                                    /* (batch, dim, seqlen) */
@@ -138,8 +144,12 @@ int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream);
  * ------------------------------------------------------------------------ */
 typedef struct b200_selscan_fixup_args {
   b200_selscan_fwd_args f;      /* same tensors as the forward call on this rank's slice */
-  const void *h_in;             /* (batch, dim, dstate) float32: state entering this slice */
-  const void *p_in;             /* (batch, dim, dstate) float32: product of a over all earlier slices */
+  const void *h_in;             /* (n_segments, batch, dim, dstate) float32: state entering each segment */
+  const void *p_in;             /* same shape: product of a over everything before the segment */
+  int32_t n_segments;           /* 0 or 1: the whole slice is one segment */
+  int32_t seg_len;              /* segment length in steps (multiple of 2048) when n_segments > 1;
+                                   segment s covers [s*seg_len, min(seqlen, (s+1)*seg_len)); entries of
+                                   h_in / p_in for a segment that needs no correction may be 0 / 1 */
 } b200_selscan_fixup_args;
 
 int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream);

@@ -42,7 +42,7 @@ using namespace b200;
 extern "C" {
 
 const char *b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 1; }
+int b200_abi_version(void) { return 2; }
 
 // size of an argument block as this library was compiled; lets a binding
 // verify its own struct layout before the first call
@@ -64,6 +64,8 @@ int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream) {
   B200_REQUIRE(!args->z || args->out_z, B200_ERR_NULL, "selscan_fwd: out_z is required when z is given");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (selscan_fwd_fast_supported(*args)) return selscan_fwd_fast(*args, st);
+  B200_REQUIRE(args->l_segments <= 1, B200_ERR_UNSUPPORTED,
+               "selscan_fwd: l_segments > 1 is only available on the throughput-kernel shape class");
   return selscan_fwd_generic(*args, st);
 }
 

@@ -11,7 +11,7 @@
 // One warp per (batch, channel) row, one timestep per lane, 32 steps per iteration: delta is
 // read coalesced, its running sum is a warp scan plus a carried total, and C[n, t] is a
 // coalesced read per state.  The contribution decays like exp(A cum_t); a row stops as soon
-// as its slowest-decaying state is below 2^-40 (fp32 output) or 2^-20 (16-bit output) of its
+// as its slowest-decaying state is below 2^-32 (fp32 output) or 2^-14 (16-bit output) of its
 // entry value — far under the output's own rounding —, so the pass usually
 // touches only the first few hundred steps of a slice instead of all of it.
 #include "common.cuh"
@@ -28,28 +28,42 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * SPW + warp;
   if (row >= (int64_t)p.batch * p.dim) return;
+  // blockIdx.y = segment of the slice; segment s covers [s*seg_len, (s+1)*seg_len)
+  const int nseg = q.n_segments > 1 ? q.n_segments : 1;
+  const int seg = (int)blockIdx.y;
+  const int t_begin = nseg > 1 ? seg * q.seg_len : 0;
+  const int t_end = nseg > 1 ? min(p.seqlen, t_begin + q.seg_len) : p.seqlen;
+  if (t_begin >= t_end) return;
   const int b = (int)(row / p.dim), d = (int)(row % p.dim);
   const int g = d / (p.dim / p.n_groups);
-  const int N = p.dstate, L = p.seqlen, dt = p.dtype;
-  const int n_chunks = (L + kChunk - 1) / kChunk;
+  const int N = p.dstate, dt = p.dtype;
+  const int n_chunks = (p.seqlen + kChunk - 1) / kChunk;
   float *A2 = sm + warp * 2 * N;     // A * log2(e)
   float *hin = A2 + N;
   const float *A = reinterpret_cast<const float *>(p.A) + (int64_t)d * p.A_ds;
-  const float *hsrc = reinterpret_cast<const float *>(q.h_in) + row * N;
-  const float *psrc = reinterpret_cast<const float *>(q.p_in) + row * N;
+  const float *hsrc = reinterpret_cast<const float *>(q.h_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
+  const float *psrc = reinterpret_cast<const float *>(q.p_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
   float amax = -INFINITY;            // slowest decay of the row
+  float hmax = 0.f;
   for (int n = lane; n < N; n += 32) {
     const float a = A[(int64_t)n * p.A_ns];
     A2[n] = a * kLog2e;
     hin[n] = hsrc[n];
     amax = fmaxf(amax, a * kLog2e);
+    hmax = fmaxf(hmax, fabsf(hsrc[n]));
   }
+  hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 16));
+  hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 8));
+  hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 4));
+  hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 2));
+  hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 1));
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
   __syncwarp();
   // checkpoints: state and product entries of every chunk of the slice
   float *xrow = reinterpret_cast<float *>(p.x) + row * n_chunks * 2 * N;
-  for (int i = lane; i < n_chunks * N; i += 32) {
+  const int c_begin = t_begin / kChunk, c_end = (t_end + kChunk - 1) / kChunk;
+  for (int i = lane + c_begin * N; i < c_end * N; i += 32) {
     const int c = i / N, n = i % N;
     const float P = xrow[(int64_t)c * 2 * N + 2 * n];
     xrow[(int64_t)c * 2 * N + 2 * n + 1] += P * hin[n];
@@ -62,35 +76,62 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   const int64_t c_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
   const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
   float carry = 0.f;                 // sum of delta' over the steps already processed
-  const float cutoff = dt == B200_F32 ? -40.f : -20.f;
-  for (int t0 = 0; t0 < L; t0 += 32) {
+  const float cutoff = dt == B200_F32 ? -32.f : -14.f;
+  if (hmax == 0.f) return;           // nothing enters this segment (first segment of the first rank)
+  const int L = t_end;
+  constexpr int K = 4;               // 32-step sub-blocks per iteration (independent loads and scans in flight)
+  for (int t0 = t_begin; t0 < L; t0 += 32 * K) {
     if (amax * carry < cutoff) break;   // every state has decayed away (carry is warp-uniform)
-    const int t = t0 + lane;
-    float dv = 0.f;
-    if (t < L) {
-      dv = ld_act(p.delta, dt, dl_off + t) + bias;
-      if (p.delta_softplus) dv = softplus20(dv);
+    float cum[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = t0 + k * 32 + lane;
+      float dv = 0.f;
+      if (t < L) {
+        dv = ld_act(p.delta, dt, dl_off + t) + bias;
+        if (p.delta_softplus) dv = softplus20(dv);
+      }
+      cum[k] = dv;
     }
-    float cum = dv;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, cum, off);
-      if (lane >= off) cum += v;
-    }
-    cum += carry;
-    carry = __shfl_sync(0xffffffffu, cum, 31);
-    if (t < L) {
-      float acc = 0.f;
-      for (int n = 0; n < N; ++n) {
-        const float cv = ld_act(p.C, dt, c_off + (int64_t)n * p.C_ns + t);
-        acc = fmaf(cv * exp2f(A2[n] * cum), hin[n], acc);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const float v = __shfl_up_sync(0xffffffffu, cum[k], off);
+        if (lane >= off) cum[k] += v;
       }
-      // out holds the rounded zero-state result; the correction is added in fp32
-      const float o = ld_act(p.out, dt, o_off + t) + acc;
-      st_act(p.out, dt, o_off + t, o);
-      if (p.z) {
-        const float zv = ld_act(p.z, dt, z_off + t);
-        st_act(p.out_z, dt, oz_off + t, o * zv * sigmoidf_(zv));
+    }
+    const float carry_before = carry;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      cum[k] += carry;
+      carry = __shfl_sync(0xffffffffu, cum[k], 31);
+    }
+    float acc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc[k] = 0.f;
+#pragma unroll 4
+    for (int n = 0; n < N; ++n) {
+      if (A2[n] * carry_before < cutoff) continue;   // this state has already decayed away (warp-uniform)
+      const float a2 = A2[n], hn = hin[n];
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int t = t0 + k * 32 + lane;
+        const float cv = t < L ? ld_act(p.C, dt, c_off + (int64_t)n * p.C_ns + t) : 0.f;
+        acc[k] = fmaf(cv * exp2f(a2 * cum[k]), hn, acc[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = t0 + k * 32 + lane;
+      if (t < L) {
+        // out holds the rounded zero-state result; the correction is added in fp32
+        const float o = ld_act(p.out, dt, o_off + t) + acc[k];
+        st_act(p.out, dt, o_off + t, o);
+        if (p.z) {
+          const float zv = ld_act(p.z, dt, z_off + t);
+          st_act(p.out_z, dt, oz_off + t, o * zv * sigmoidf_(zv));
+        }
       }
     }
   }
@@ -116,6 +157,9 @@ extern "C" int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *str
                "selscan_fixup supports real A, variable B and C, no deltaA and the mamba / zoh / dirac transitions");
   const int64_t rows = (int64_t)a.batch * a.dim;
   const size_t smem = (size_t)SPW * 2 * a.dstate * sizeof(float);
-  selscan_fixup_kernel<<<(unsigned)((rows + SPW - 1) / SPW), SPW * 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(*args);
+  B200_REQUIRE(args->n_segments <= 1 || (args->seg_len > 0 && args->seg_len % kChunk == 0), B200_ERR_SHAPE,
+               "selscan_fixup: seg_len must be a positive multiple of 2048 when n_segments > 1");
+  const dim3 grid((unsigned)((rows + SPW - 1) / SPW), (unsigned)(args->n_segments > 1 ? args->n_segments : 1));
+  selscan_fixup_kernel<<<grid, SPW * 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(*args);
   return launch_status();
 }

@@ -124,9 +124,65 @@ def _stream(t) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+_SM_COUNT = {}
+
+
+def _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C, deltaA, method):
+    """Number of sequence segments for the forward call: > 1 only for long rows that would leave
+    most of the GPU idle (few (batch, channel-tile) thread blocks), on the shape class of the
+    throughput kernel.  Segments are scanned concurrently from zero states and stitched by the
+    summary fold + fix-up that the multi-GPU sequence-parallel path uses."""
+    if is_complex or method != "mamba" or not (var_B and var_C) or deltaA is not None or dstate != 16:
+        return 1
+    if dim % 16 or (dim // n_groups) % 16 or seqlen % 8 or seqlen < 4 * CHUNK:
+        return 1
+    idx = u.device.index if u.device.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    slots = 2 * _SM_COUNT[idx]
+    ctas = batch * dim // 16
+    if ctas >= 4 * slots:
+        return 1
+    # pick the segment count whose thread blocks fill whole waves best (ties: fewer segments)
+    best, best_eff = 1, 0.0
+    for want in range(1, 17):
+        seg_len = -(-(-(-seqlen // want)) // CHUNK) * CHUNK
+        if want > 1 and seg_len < 2 * CHUNK:
+            break
+        S = -(-seqlen // seg_len)
+        waves = ctas * S / slots
+        # below one wave more segments simply mean more of the GPU in use; above, whole waves count.
+        # Every extra segment also costs a fix-up pass over its first steps: demand a clear gain.
+        eff = waves if waves <= 1.0 else waves / -(-waves // 1)
+        if eff > best_eff * 1.10 + 1e-9:
+            best, best_eff = S, eff
+    return best
+
+
+def _stitch_segments(a, x, S, seqlen, u):
+    """Fold the zero-start summaries of the segments and run the fix-up kernel on segments >= 1."""
+    n_chunks = x.shape[2]
+    seg_len = -(-(-(-seqlen // S)) // CHUNK) * CHUNK
+    cps = seg_len // CHUNK
+    last = [min((s + 1) * cps, n_chunks) - 1 for s in range(S)]
+    P = x[:, :, last, 0::2].permute(2, 0, 1, 3).contiguous()      # (S, batch, dim, dstate) zero-start products
+    h = x[:, :, last, 1::2].permute(2, 0, 1, 3).contiguous()
+    h_in = torch.zeros_like(h)
+    p_in = torch.ones_like(P)
+    for s in range(1, S):
+        h_in[s] = P[s - 1] * h_in[s - 1] + h[s - 1]
+        p_in[s] = p_in[s - 1] * P[s - 1]
+    q = _lib.struct("b200_selscan_fixup_args")()
+    a.l_segments = 0
+    q.f = a
+    q.h_in, q.p_in = h_in.data_ptr(), p_in.data_ptr()
+    q.n_segments, q.seg_len = S, seg_len
+    _lib.call("b200_selscan_fixup", q, _stream(u))
+
+
 def fwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, delta_softplus, discretization_method_str):
     """Returns ``[out, x]`` or ``[out, x, out_z]`` (selective_scan_cpu.cpp:418-420)."""
-    a, (batch, dim, seqlen, dstate, _, _, _, _) = _common(
+    a, (batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C) = _common(
         u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, discretization_method_str)
     n_chunks = (seqlen + CHUNK - 1) // CHUNK
     with torch.cuda.device(u.device):
@@ -138,7 +194,21 @@ def fwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, delta_softplus, discret
         a.out_bs, a.out_ds = out.stride(0), out.stride(1)
         if out_z is not None:
             a.out_z_bs, a.out_z_ds = out_z.stride(0), out_z.stride(1)
-        _lib.call("b200_selscan_fwd", a, _stream(u))
+        S = _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C, deltaA_,
+                          discretization_method_str)
+        if S > 1:
+            a.l_segments = S
+            try:
+                _lib.call("b200_selscan_fwd", a, _stream(u))
+            except RuntimeError as e:
+                if "l_segments" not in str(e):
+                    raise
+                S, a.l_segments = 1, 0       # operands not aligned for the throughput kernel
+                _lib.call("b200_selscan_fwd", a, _stream(u))
+            if S > 1:
+                _stitch_segments(a, x, S, seqlen, u)
+        else:
+            _lib.call("b200_selscan_fwd", a, _stream(u))
     return [out, x] if out_z is None else [out, x, out_z]
 
 

@@ -55,6 +55,7 @@ def apply_fixup(u, delta, A, B, C, D, z, delta_bias, delta_softplus, out, x, out
     h_in = h_in.float().contiguous()
     p_in = p_in.float().contiguous()
     q.h_in, q.p_in = h_in.data_ptr(), p_in.data_ptr()
+    q.n_segments, q.seg_len = 0, 0
     with torch.cuda.device(u.device):
         _lib.call("b200_selscan_fixup", q, torch.cuda.current_stream(u.device).cuda_stream)
 

@@ -189,3 +189,20 @@ def test_throughput_kernel_checkpoints():
     assert x.shape == x_c.shape == (1, 16, 3, 32)
     assert_close(x.cpu()[..., 1::2], x_c[..., 1::2], rtol=RTOL32, atol_scale=ATOL32, name="x state")
     assert_close(x.cpu()[..., 0::2], x_c[..., 0::2], rtol=1e-3, atol_scale=1e-6, name="x product")
+
+
+def test_long_row_segmented_forward_matches_oracle():
+    """Few rows and a long sequence: the forward is cut into concurrently scanned segments and
+    stitched (l_segments > 1 + fix-up); compare with the oracle and check the checkpoints."""
+    from lrnnx_b200 import selective_scan_cuda
+    t, g = _make_inputs(1, 16, 16, 5 * 2048 + 264, seed=21)
+    assert selective_scan_cuda._segments_for(t["u"].cuda(), 1, 16, t["u"].shape[-1], 16, 1, False, True, True, None,
+                                             "mamba") > 1
+    out_c, last_c, x_c = O.selective_scan_oracle(**t, delta_softplus=True, return_last_state=True,
+                                                 return_checkpoints=True)
+    cu = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items()}
+    out, x, out_z = selective_scan_cuda.fwd(cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], cu["z"],
+                                            cu["delta_bias"], None, True, "mamba")
+    assert_close(out_z.cpu(), out_c, rtol=RTOL32, atol_scale=ATOL32, name="out_z")
+    assert_close(x.cpu()[..., 1::2], x_c[..., 1::2], rtol=RTOL32, atol_scale=ATOL32, name="x state")
+    assert_close(x.cpu()[..., 0::2], x_c[..., 0::2], rtol=1e-3, atol_scale=1e-6, name="x product")
