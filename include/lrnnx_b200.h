@@ -227,6 +227,29 @@ typedef struct b200_ssu_args {
 int b200_ssu_step(const b200_ssu_args *args, void *stream);
 
 /* ------------------------------------------------------------------------
+ * One-token update of the S5 (simplified) recurrence with its projections fused.
+ * Replaces simplified_state_update and its Triton kernel
+ * (lrnnx/ops/triton/simplified_state_update.py:254-401, 13-251):
+ *   Bu = B x;  state <- a * state + k * Bu  (a, k as in the simplified scan, from dt / deltaA);
+ *   out = (conj_sym ? 2 : 1) * Re(C state) + D x.
+ *   state (batch, P) complex64, in place; x, out (batch, H) float32;
+ *   dt, deltaA (batch, P) float32 (batch stride 0 for a (P,) tensor); A (P) complex64;
+ *   B (P, H), C (H, P) complex64 row-major dense; D (H, H) float32 row-major dense, nullable.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_s5_step_args {
+  int32_t batch, P, H;
+  int32_t method;          /* ZOH, BILINEAR or DIRAC */
+  int32_t conj_sym;
+  int32_t reserved0;
+  void *state;
+  const void *x, *dt, *deltaA /* nullable */, *A, *B, *C, *D /* nullable */;
+  void *out;
+  int64_t state_bs, x_bs, dt_bs, deltaA_bs, out_bs;
+} b200_s5_step_args;
+
+int b200_s5_step(const b200_s5_step_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
  * S4 structured kernels (contiguous tensors).
  * Replace cauchy_mult_sym_fwd/bwd and vand_log_mult_sym_fwd/bwd
  * (csrc/s4/cauchy.cpp:20-102, csrc/s4/cauchy_cuda.cu:34-368).

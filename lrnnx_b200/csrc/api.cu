@@ -54,6 +54,7 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_simpscan_args")) return (int)sizeof(b200_simpscan_args);
   if (!strcmp(name, "b200_ssu_args")) return (int)sizeof(b200_ssu_args);
   if (!strcmp(name, "b200_s4_args")) return (int)sizeof(b200_s4_args);
+  if (!strcmp(name, "b200_s5_step_args")) return (int)sizeof(b200_s5_step_args);
   return -1;
 }
 

@@ -260,6 +260,25 @@ def selective_state_update_oracle(state, x, dt, A, B, C, D=None, z=None, dt_bias
     return out if has_heads else out.squeeze(1)
 
 
+def simplified_state_update_oracle(state, x, dt, A, B, C, D=None, deltaA=None, discretization="bilinear",
+                                   conj_sym=True):
+    """simplified_state_update_ref (lrnnx/ops/triton/simplified_state_update.py:404-469): one S5 step.
+    state (batch, P) complex, updated in place; x (batch, H) real; dt, deltaA (batch, P) or (P,);
+    A (P,), B (P, H), C (H, P) complex; D (H, H) real.  Returns y (batch, H) real."""
+    batch, P = state.shape
+    dtb = dt if dt.dim() == 2 else dt.unsqueeze(0).expand(batch, -1)
+    dA = dtb if deltaA is None else (deltaA if deltaA.dim() == 2 else deltaA.unsqueeze(0).expand(batch, -1))
+    a, k = _discretize(discretization.lower(), A.unsqueeze(-1), dtb, dA)      # (batch, P, 1)
+    Bu = torch.einsum("ph,bh->bp", B, x.to(B.dtype))
+    state.copy_(a.squeeze(-1) * state + k.squeeze(-1) * Bu)
+    y = torch.einsum("hp,bp->bh", C, state).real
+    if conj_sym:
+        y = 2.0 * y
+    if D is not None:
+        y = y + x @ D.T
+    return y
+
+
 def cauchy_oracle(v, z, w, compute_dtype=torch.complex128):
     """cauchy_mult_torch(..., symmetric=True) restricted to the half spectrum
     (csrc/s4/cauchy.py:26-49; kernel csrc/s4/cauchy_cuda.cu:68-79): v, w (batch, n) hold one

@@ -34,6 +34,7 @@ from lrnnx.ops.rglru_scan import rglru_scan_ref  # noqa: E402
 from lrnnx.ops.s7_scan import s7_scan_ref  # noqa: E402
 from lrnnx.ops.simplified_scan import simplified_scan_ref, s5_inner_ref  # noqa: E402
 from lrnnx.ops.triton.selective_state_update import selective_state_update_ref  # noqa: E402
+from lrnnx.ops.triton.simplified_state_update import simplified_state_update_ref  # noqa: E402
 from lrnnx.ops.s4_utils import log_vandermonde_naive  # noqa: E402
 from csrc.s4.cauchy import cauchy_mult_torch  # noqa: E402
 
@@ -198,6 +199,26 @@ def state_update_cases():
     return cases
 
 
+def s5_step_cases():
+    cases = {}
+    for disc in ("bilinear", "zoh", "dirac"):
+        for use_dA, conj_sym, dt_1d in ((False, True, False), (True, False, False), (False, True, True)):
+            g = gen(11)
+            batch, P, H = 3, 24, 40
+            A = torch.complex(-0.5 * rand(g, P) - 0.05, math.pi * rand(g, P)).to(torch.complex64)
+            t = dict(state=randn(g, batch, P, dtype=torch.complex64), x=randn(g, batch, H),
+                     dt=(0.1 * rand(g, P) + 0.01) if dt_1d else (0.1 * rand(g, batch, P) + 0.01), A=A,
+                     B=randn(g, P, H, dtype=torch.complex64) / math.sqrt(H),
+                     C=randn(g, H, P, dtype=torch.complex64) / math.sqrt(P), D=randn(g, H, H) / math.sqrt(H),
+                     deltaA=(0.1 * rand(g, batch, P) + 0.01) if use_dA else None)
+            state = t["state"].clone()
+            out = simplified_state_update_ref(state, t["x"], t["dt"], t["A"], t["B"], t["C"], t["D"], t["deltaA"],
+                                              discretization=disc, conj_sym=conj_sym)
+            cases[f"{disc}_dA{int(use_dA)}_cs{int(conj_sym)}_1d{int(dt_1d)}"] = {
+                "inputs": t, "kwargs": dict(discretization=disc, conj_sym=conj_sym), "outputs": [out, state]}
+    return cases
+
+
 def s4_cases():
     cases = {}
     for n_half, L in ((2, 3), (8, 17), (32, 129)):
@@ -229,9 +250,12 @@ def s4_cases():
 
 def main():
     torch.set_num_threads(4)
+    only = set(sys.argv[1:])
     for name, fn in (("selective_scan", selective_cases), ("rglru_s7", rglru_s7_cases),
                      ("simplified_scan", simplified_cases), ("state_update", state_update_cases),
-                     ("s4", s4_cases)):
+                     ("s5_step", s5_step_cases), ("s4", s4_cases)):
+        if only and name not in only:
+            continue
         cases = fn()
         path = OUT / f"{name}.pt"
         torch.save(cases, path)

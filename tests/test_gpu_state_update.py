@@ -135,3 +135,38 @@ def test_state_update_in_cuda_graph():
         graph.replay()
         torch.testing.assert_close(y, outs_ref[k], rtol=0, atol=0)
     torch.testing.assert_close(static_state, ref, rtol=0, atol=0)
+
+
+S5STEP = load_golden("s5_step")
+
+
+@pytest.mark.parametrize("name", sorted(S5STEP))
+def test_s5_step_golden(name):
+    from lrnnx_b200.ops import simplified_state_update
+    case = S5STEP[name]
+    t = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in case["inputs"].items()}
+    state = t.pop("state").clone()
+    out = simplified_state_update(state, **t, **case["kwargs"])
+    assert out.dtype == torch.float32
+    assert_close(out.cpu(), case["outputs"][0], rtol=1e-4, atol_scale=1e-5, name="out")
+    assert_close(state.cpu(), case["outputs"][1], rtol=1e-4, atol_scale=1e-5, name="state")
+
+
+@pytest.mark.parametrize("H,P", [(256, 16), (272, 32), (512, 64)])
+def test_s5_step_shapes(H, P):
+    """Shapes of tests/ops/s5/test_simplified_state_update.py (H in {256, 272, 512}, P in {16, 32, 64})."""
+    import math
+    from lrnnx_b200.ops import simplified_state_update
+    g = torch.Generator().manual_seed(H + P)
+    c = lambda *s: torch.complex(torch.randn(*s, generator=g), torch.randn(*s, generator=g))
+    batch = 5
+    t = dict(x=torch.randn(batch, H, generator=g), dt=0.1 * torch.rand(batch, P, generator=g) + 0.01,
+             A=torch.complex(-0.5 * torch.rand(P, generator=g) - 0.05, math.pi * torch.rand(P, generator=g)),
+             B=c(P, H) / math.sqrt(H), C=c(H, P) / math.sqrt(P), D=torch.randn(H, H, generator=g) / math.sqrt(H))
+    state = c(batch, P)
+    ref_state = state.clone()
+    out_c = O.simplified_state_update_oracle(ref_state, **t, discretization="zoh")
+    st = state.cuda()
+    out_g = simplified_state_update(st, **{k: v.cuda() for k, v in t.items()}, discretization="zoh")
+    assert_close(out_g.cpu(), out_c, rtol=1e-4, atol_scale=2e-5, name="out")
+    assert_close(st.cpu(), ref_state, rtol=1e-4, atol_scale=1e-5, name="state")

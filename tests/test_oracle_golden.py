@@ -118,3 +118,16 @@ def test_checkpoint_layout():
     torch.testing.assert_close(x[:, :, -1, 1::2], last)
     prod = torch.exp(delta.sum(-1)[..., None] * A)
     torch.testing.assert_close(x[:, :, -1, 0::2], prod, rtol=1e-4, atol=1e-30)
+
+
+S5STEP = load_golden("s5_step")
+
+
+@pytest.mark.parametrize("name", sorted(S5STEP))
+def test_s5_step_oracle(name):
+    case = S5STEP[name]
+    t = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in case["inputs"].items()}
+    state = t.pop("state")
+    out = O.simplified_state_update_oracle(state, **t, **case["kwargs"])
+    assert_close(out, case["outputs"][0], rtol=RTOL, name="out")
+    assert_close(state, case["outputs"][1], rtol=RTOL, name="state")
