@@ -161,7 +161,8 @@ int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream);
  * csrc/simplified_scan/simplified_scan_backward.cuh:91-420).
  *   u, out, dout, du : (batch, dim, seqlen) complex64
  *   delta, deltaA, ddelta, ddeltaA : (batch, dim, seqlen) float32
- *   A, B, C, dA, dB, dC : (dim, dstate) complex64  (dA/dB/dC zero-filled by caller)
+ *   A, B, C, dA, dB, dC : (dim, dstate) complex64  (dA/dB/dC zero-filled by caller;
+ *                         dB and dC may both be null when dstate == 1: the sums are then skipped)
  *   x : (batch, dim, n_chunks, 2*dstate) complex64
  *   method : ZOH, BILINEAR or DIRAC
  * ------------------------------------------------------------------------ */

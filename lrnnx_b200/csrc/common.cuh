@@ -73,7 +73,9 @@ __device__ __forceinline__ void sincos_cw(float x, float &sn, float &cs) {
   cs = ((qi + 1) & 2) ? -c0 : c0;
 }
 __device__ __forceinline__ cf cexp(cf z) {
-  float e = expf(z.re), s, c;
+  // magnitude by the SFU's ex2 (relative error 2^-22, the same class as expf's 1 ulp)
+  float e, s, c;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z.re * kLog2e));
   sincos_cw(z.im, s, c);
   return cf(e * c, e * s);
 }

@@ -18,14 +18,15 @@
 // addresses are not 16-byte aligned, and the ragged last stage, use plain
 // loads/stores on the same layout.
 //
-// Backward: one 256-thread CTA per row walks the 2048-step checkpoint chunks
-// in reverse with 8 timesteps per thread, so a whole chunk is resident in
-// registers: states are recomputed from the chunk's checkpoint with a block
-// scan, the adjoint g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C) runs as a
-// reverse block scan, and du / ddelta / ddeltaA / dA / dB / dC follow.  Chunk
-// inputs are double-buffered in shared memory by bulk copies (a buffer is
-// refilled as soon as its chunk sits in registers); du and ddelta are staged in
-// a separate shared-memory area and leave through bulk stores.
+// Backward: persistent 256-thread CTAs walk the 2048-step checkpoint chunks of
+// their rows in reverse with 8 timesteps per thread, so a whole chunk is
+// resident in registers: states are recomputed from the chunk's checkpoint
+// with a block scan, the adjoint g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C)
+// runs as a reverse block scan in the same pass, and du / ddelta / ddeltaA /
+// dA / dB / dC follow.  Each warp moves its own 256-step slice of a chunk:
+// double-buffered bulk loads on per-warp mbarriers (a slice is refilled as
+// soon as the warp holds it in registers) and bulk stores from a per-warp
+// staging slice, so the one block barrier per chunk is the scan exchange.
 #include "common.cuh"
 #include "dispatch.h"
 
@@ -311,28 +312,30 @@ constexpr int B_U_BYTES = kChunk * 8;
 constexpr int B_D_BYTES = kChunk * 4;
 
 struct __align__(16) BwdShared {
-  cf wtot_a[2][BWARPS];     // per-warp aggregates of the forward scan (double-buffered by parity)
+  cf wtot_a[2][BWARPS];     // per-warp aggregates of the forward scan (double-buffered by iteration parity)
   cf wtot_h[2][BWARPS];
   cf rtot_q[2][BWARPS];     // per-warp aggregates of the reverse scan
   cf rtot_g[2][BWARPS];
-  cf afirst[BWARPS];        // first transition of each warp (needed by the previous warp's last lane)
   cf red[3][BWARPS];        // block reduction scratch for dA, dB, dC
-  uint64_t bar[2];
+  uint64_t full[2][BWARPS]; // warp w's 256-step slice of chunk buffer k has been filled by its bulk copies
 };
 
-template <int DM, bool HAS_DA, bool S1>
+// NEED_BC = false skips dB / dC (the host passes null pointers: the caller scans B u with
+// identity B and C and has no use for them).
+template <int DM, bool HAS_DA, bool S1, bool NEED_BC>
 __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan_args p) {
   constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);   // u, dout, delta (, deltaA)
   constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);       // du, ddelta (, ddeltaA)
+  constexpr int SL = 32 * BI;                       // timesteps per warp slice
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  // layout: buf[2] | out staging | BwdShared | per-state: gcar, anext, accA, accB, accC (cf each)
+  // layout: buf[2] | out staging | BwdShared | per-state: gcar[2], accA, accB, accC (cf each)
   unsigned char *out_stage = smem_raw + 2 * (size_t)BUF_BYTES;
   BwdShared &sh = *reinterpret_cast<BwdShared *>(out_stage + OUT_BYTES);
   cf *st_arr = reinterpret_cast<cf *>(out_stage + OUT_BYTES + sizeof(BwdShared));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int L = p.seqlen, S = S1 ? 1 : p.dstate;
   const int n_chunks = (L + kChunk - 1) / kChunk;
-  cf *gcar = st_arr, *anext = st_arr + S, *accA = st_arr + 2 * S, *accB = st_arr + 3 * S, *accC = st_arr + 4 * S;
+  cf *gcar = st_arr, *accA = st_arr + 2 * S, *accB = st_arr + 3 * S, *accC = st_arr + 4 * S;
   // persistent CTAs: CTA g owns rows g, g + G, ...; the chunks of all its rows (each row walked
   // from its last chunk to its first) form one stream for the two-buffer pipeline
   const int64_t nrows = (int64_t)p.batch * p.dim;
@@ -363,33 +366,43 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
   auto buf_dA = [&](int k) {
     return reinterpret_cast<float *>(smem_raw + (size_t)k * BUF_BYTES + 2 * B_U_BYTES + B_D_BYTES);
   };
-  // stream item f: row blockIdx.x + (f / n_chunks) * gridDim.x, chunk n_chunks - 1 - f % n_chunks
-  auto issue = [&](int f) {   // one thread
+  // stream item f: row blockIdx.x + (f / n_chunks) * gridDim.x, chunk n_chunks - 1 - f % n_chunks.
+  // Every warp runs its own pipeline on its 256-step slice of the chunk: lane 0 issues the
+  // slice's bulk loads and stores, the warp alone reads and writes the slice, so loads and
+  // stores need no block-wide synchronisation.
+  auto issue = [&](int f) {   // lane 0 of a warp
     if (f >= total) return;
     const int c = n_chunks - 1 - f % n_chunks;
     if ((c + 1) * kChunk > L) return;
     const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x);
     if (!r.tma) return;
     const int k = f & 1;
-    const int64_t t0 = (int64_t)c * kChunk;
-    mbar_expect_tx(&sh.bar[k], BUF_BYTES);
-    bulk_g2s(buf_u(k), r.u + t0, B_U_BYTES, &sh.bar[k]);
-    bulk_g2s(buf_do(k), r.dout + t0, B_U_BYTES, &sh.bar[k]);
-    bulk_g2s(buf_d(k), r.d + t0, B_D_BYTES, &sh.bar[k]);
-    if (HAS_DA) bulk_g2s(buf_dA(k), r.dA + t0, B_D_BYTES, &sh.bar[k]);
+    const int64_t t0 = (int64_t)c * kChunk + warp * SL;
+    uint64_t *bar = &sh.full[k][warp];
+    mbar_expect_tx(bar, BUF_BYTES / BWARPS);
+    bulk_g2s(buf_u(k) + warp * SL, r.u + t0, B_U_BYTES / BWARPS, bar);
+    bulk_g2s(buf_do(k) + warp * SL, r.dout + t0, B_U_BYTES / BWARPS, bar);
+    bulk_g2s(buf_d(k) + warp * SL, r.d + t0, B_D_BYTES / BWARPS, bar);
+    if (HAS_DA) bulk_g2s(buf_dA(k) + warp * SL, r.dA + t0, B_D_BYTES / BWARPS, bar);
   };
 
   if (tid == 0) {
-    mbar_init(&sh.bar[0], 1);
-    mbar_init(&sh.bar[1], 1);
+    for (int i = 0; i < 2 * BWARPS; ++i) mbar_init(&sh.full[0][0] + i, 1);
     mbar_fence_init();
     fence_proxy_async();
   }
   __syncthreads();
-  if (tid == 0) { issue(0); issue(1); }
+  if (lane == 0) { issue(0); issue(1); }
 
+  // A bounded wait that expires marks the thread as failed; a failed thread skips every later
+  // wait (results are then garbage and the status word says so) but keeps taking part in the
+  // block barriers, so the CTA always terminates.
   bool failed = false;
-  uint32_t phase_bits = 0;
+  auto wait = [&](uint64_t *bar, uint32_t parity) {
+    if (!failed && !mbar_wait(bar, parity)) failed = true;
+  };
+  uint32_t full_phase = 0;
+  uint32_t iter = 0;          // (chunk, state) iterations so far: parity of the exchange arrays
   bool stores_pending = false;
   RowPtrs rp = row_ptrs(blockIdx.x);
   int64_t row = blockIdx.x;
@@ -411,11 +424,9 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
       C0 = Cp[0];
       c_one = S1 && C0.re == 1.f && C0.im == 0.f;
       dA_acc = dB_acc = dC_acc = cf(0.f, 0.f);
-      __syncthreads();   // the previous row's tail has consumed gcar / anext / acc*
-      for (int i = tid; i < S; i += BT) {
-        gcar[i] = cf(0.f, 0.f);
-        anext[i] = cf(1.f, 0.f);
-        accA[i] = accB[i] = accC[i] = cf(0.f, 0.f);
+      if (!S1) {
+        __syncthreads();   // the previous row's tail has consumed acc*
+        for (int i = tid; i < S; i += BT) accA[i] = accB[i] = accC[i] = cf(0.f, 0.f);
       }
     }
     const int k = f & 1;
@@ -424,18 +435,18 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     cf *su = buf_u(k), *sdo = buf_do(k);
     float *sd = buf_d(k), *sdA = buf_dA(k);
     if (async_chunk) {
-      if (!mbar_wait(&sh.bar[k], (phase_bits >> k) & 1u)) failed = true;
-      phase_bits ^= (1u << k);
+      wait(&sh.full[k][warp], (full_phase >> k) & 1u);
+      full_phase ^= (1u << k);
     } else {
-      for (int i = tid; i < kChunk; i += BT) {
+      for (int i = warp * SL + lane; i < (warp + 1) * SL; i += 32) {
         const int t = t0 + i;
         su[i] = t < L ? rp.u[t] : cf(0.f, 0.f);
         sdo[i] = t < L ? rp.dout[t] : cf(0.f, 0.f);
         sd[i] = t < L ? rp.d[t] : 0.f;
         if (HAS_DA) sdA[i] = t < L ? rp.dA[t] : 0.f;
       }
+      __syncwarp();
     }
-    if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
 
     cf u[BI], dy[BI];
     float dl[BI], dAv[BI];
@@ -466,9 +477,9 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         for (int i = 0; i < BI; ++i) dAv[i] = dl[i];
       }
     }
-    // the chunk now lives in registers: refill this buffer with the stream item two steps ahead
-    __syncthreads();
-    if (tid == 0) issue(f + 2);
+    // the warp's slice now lives in registers: refill it with the stream item two steps ahead
+    __syncwarp();
+    if (lane == 0) issue(f + 2);
     cf du[BI];
     float ddl[BI], ddA[BI];
     if (!S1) {
@@ -477,7 +488,8 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     }
 
     for (int si = 0; si < S; ++si) {
-      const int par = si & 1;
+      const int par = iter & 1;
+      ++iter;
       const cf An = S1 ? A0 : Ap[(int64_t)si * p.A_ns];
       const cf Cc = conj(S1 ? C0 : Cp[(int64_t)si * p.C_ns]);
       // checkpoint of the previous chunk: issued early so the load overlaps the local scans
@@ -491,26 +503,42 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         else s5_coef<DM>(An, dl[i], dAv[i], a[i], kk[i]);
       }
       auto beta = [&](int i) { return kUnitK ? u[i] : kk[kUnitK ? 0 : i] * u[i]; };
-      // forward, pass 1: per-thread aggregate, warp scan, cross-warp prefix
+      auto seed = [&](int i) { return c_one ? dy[i] : dy[i] * Cc; };   // dout_t conj(C)
+      // forward, pass 1: per-thread aggregate of h_t = a_t h_{t-1} + beta_t
       cf P = cf(1.f, 0.f), hh = cf(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
         hh = a[i] * hh + beta(i);
         P = P * a[i];
       }
+      // reverse, pass 1.  Inside a thread the adjoint g_t = seed_t + conj(a_{t+1}) g_{t+1} runs
+      // on g itself; across threads, warps and chunks it is carried as q_t = conj(a_t) g_t, so
+      // every transition used is the thread's own (no coefficient crosses a boundary) and the
+      // thread's transition product is the conjugate of the forward one.
+      cf gg = seed(BI - 1), Q = conj(P);
+#pragma unroll
+      for (int i = BI - 2; i >= 0; --i) gg = conj(a[i + 1]) * gg + seed(i);
+      gg = conj(a[0]) * gg;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
-        cf Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+        const cf Pp = shfl_up(P, off), hp = shfl_up(hh, off);
+        const cf Qr = shfl_down(Q, off), gr = shfl_down(gg, off);
         if (lane >= off) { hh = P * hp + hh; P = P * Pp; }
+        if (lane + off < 32) { gg = gg + Q * gr; Q = Q * Qr; }
       }
       if (lane == 31) { sh.wtot_a[par][warp] = P; sh.wtot_h[par][warp] = hh; }
-      if (lane == 0) sh.afirst[warp] = a[0];
-      cf a_next_lane = shfl_down(a[0], 1);   // a_{t+1} for this thread's last item
-      __syncthreads();
+      if (lane == 0) { sh.rtot_q[par][warp] = Q; sh.rtot_g[par][warp] = gg; }
+      __syncthreads();   // the only block barrier of the iteration
       for (int w = 0; w < warp; ++w) hpre = sh.wtot_a[par][w] * hpre + sh.wtot_h[par][w];
+      cf qpost = (j == 0) ? cf(0.f, 0.f) : gcar[(f & 1) * S + si];   // q entering the chunk from the later one
+      for (int w = BWARPS - 1; w > warp; --w) qpost = sh.rtot_g[par][w] + sh.rtot_q[par][w] * qpost;
       cf Pex = shfl_up(P, 1), hex = shfl_up(hh, 1);
       if (lane == 0) { Pex = cf(1.f, 0.f); hex = cf(0.f, 0.f); }
       const cf hin = Pex * hpre + hex;       // state entering this thread's first item
+      const cf g_right = shfl_down(gg, 1), Q_right = shfl_down(Q, 1);
+      cf qin = g_right + Q_right * qpost;    // q of the first item of the next thread
+      if (lane == 31) qin = qpost;
+      if (tid == 0) gcar[((f + 1) & 1) * S + si] = gg + Q * qpost;   // q of the first step of this chunk
       // forward, pass 2: the states
       {
         cf hc = hin;
@@ -520,56 +548,30 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
           h[i] = hc;
         }
       }
-      if (lane == 31) a_next_lane = (warp == BWARPS - 1) ? anext[si] : sh.afirst[warp + 1];
-      // reverse, pass 1: aggregate of g_t = conj(a_{t+1}) g_{t+1} + dout_t conj(C)
-      cf gg = cf(0.f, 0.f), Q = cf(1.f, 0.f);
-#pragma unroll
-      for (int i = BI - 1; i >= 0; --i) {
-        const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
-        gg = an * gg + (c_one ? dy[i] : dy[i] * Cc);
-        Q = Q * an;
-      }
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        cf Qr = shfl_down(Q, off), gr = shfl_down(gg, off);
-        if (lane + off < 32) { gg = gg + Q * gr; Q = Q * Qr; }
-      }
-      if (lane == 0) { sh.rtot_q[par][warp] = Q; sh.rtot_g[par][warp] = gg; }
-      const cf gc_chunk = gcar[si];
-      __syncthreads();
-      cf gpost = gc_chunk;                   // adjoint entering this warp from the later warps / chunk
-      for (int w = BWARPS - 1; w > warp; --w) gpost = sh.rtot_g[par][w] + sh.rtot_q[par][w] * gpost;
-      cf g_right = shfl_down(gg, 1), Q_right = shfl_down(Q, 1);
-      cf gin = g_right + Q_right * gpost;    // adjoint at the first item of the next thread
-      if (lane == 31) gin = gpost;
-      if (tid == 0) {
-        gcar[si] = gg + Q * gpost;           // adjoint at the first step of this chunk
-        anext[si] = a[0];
-      }
       // reverse, pass 2: adjoints and gradients
       cf dA_l = cf(0.f, 0.f), dB_l = cf(0.f, 0.f), dC_l = cf(0.f, 0.f);
-      cf G = gin;
+      cf q = qin;
 #pragma unroll
       for (int i = BI - 1; i >= 0; --i) {
-        const cf an = conj(i == BI - 1 ? a_next_lane : a[i + 1]);
-        G = an * G + (c_one ? dy[i] : dy[i] * Cc);
         const cf hprev = (i == 0) ? hin : h[i - 1];
+        const cf G = (i == BI - 1) ? seed(i) + q : conj(a[i == BI - 1 ? i : i + 1]) * q + seed(i);   // g_t
+        q = G;
+        const cf t = G * conj(h[i] - beta(i));   // g_t conj(a_t h_{t-1}), with a_t h_{t-1} = h_t - beta_t
         const float dv = dl[i], dav = dAv[i];
         if constexpr (kUnitK) {
           du[i] = S1 ? G : du[i] + G;
-          dB_l = dB_l + G * conj(u[i]);
+          if (NEED_BC) dB_l = dB_l + G * conj(u[i]);
         } else {
           du[i] = S1 ? G * conj(kk[kUnitK ? 0 : i]) : du[i] + G * conj(kk[kUnitK ? 0 : i]);
-          dB_l = dB_l + G * conj(beta(i));
+          if (NEED_BC) dB_l = dB_l + G * conj(beta(i));
         }
-        dC_l = dC_l + dy[i] * conj(h[i]);
+        if (NEED_BC) dC_l = dC_l + dy[i] * conj(h[i]);
         float d_dl = 0.f, d_dA = 0.f;
         if constexpr (DM == B200_DISC_ZOH) {
           const cf E = cexp(An * dv);
-          const cf ah = a[i] * hprev;
-          d_dA = (G * conj(An * ah)).re;
+          d_dA = (t * conj(An)).re;
           d_dl = (G * conj(E * u[i])).re;
-          dA_l = dA_l + G * conj(ah * dav + u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / An));
+          dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / An));
         } else if constexpr (DM == B200_DISC_BILINEAR) {
           const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dv));
           const cf rA = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dav));
@@ -578,8 +580,6 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
           d_dl = (G * conj(r2 * u[i])).re;
           dA_l = dA_l + G * conj(hprev * rA2 * dav + r2 * u[i] * (0.5f * dv * dv));
         } else {
-          // G conj(A a h_prev) and G conj(dA a h_prev) share t = G conj(a h_prev)
-          const cf t = G * conj(a[i] * hprev);
           d_dA = (t * conj(An)).re;
           dA_l = dA_l + t * dav;
         }
@@ -599,6 +599,7 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         dA_l = warp_sum(dA_l);
         dB_l = warp_sum(dB_l);
         dC_l = warp_sum(dC_l);
+        // sh.red is free: its readers of the previous iteration arrived at this iteration's barrier
         if (lane == 0) { sh.red[0][warp] = dA_l; sh.red[1][warp] = dB_l; sh.red[2][warp] = dC_l; }
         __syncthreads();
         if (tid < 3) {
@@ -612,8 +613,8 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     }
     // ---- write du / ddelta (/ ddeltaA) through the staging area
     if (async_chunk) {
-      if (tid == 0 && stores_pending) bulk_wait_read<0>();   // previous stores have left the staging area
-      __syncthreads();
+      if (lane == 0 && stores_pending) bulk_wait_read<0>();   // the warp's previous stores have left its staging slice
+      __syncwarp();
       cf *so = reinterpret_cast<cf *>(out_stage);
       float *sod = reinterpret_cast<float *>(out_stage + B_U_BYTES);
       float *sodA = reinterpret_cast<float *>(out_stage + B_U_BYTES + B_D_BYTES);
@@ -629,11 +630,12 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         for (int q = 0; q < BI / 4; ++q) dA4[q] = make_float4(ddA[4 * q], ddA[4 * q + 1], ddA[4 * q + 2], ddA[4 * q + 3]);
       }
       fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        bulk_s2g(rp.du + t0, so, B_U_BYTES);
-        bulk_s2g(rp.dd + t0, sod, B_D_BYTES);
-        if (HAS_DA) bulk_s2g(rp.ddA + t0, sodA, B_D_BYTES);
+      __syncwarp();
+      if (lane == 0) {
+        const int w0 = warp * SL;
+        bulk_s2g(rp.du + t0 + w0, so + w0, B_U_BYTES / BWARPS);
+        bulk_s2g(rp.dd + t0 + w0, sod + w0, B_D_BYTES / BWARPS);
+        if (HAS_DA) bulk_s2g(rp.ddA + t0 + w0, sodA + w0, B_D_BYTES / BWARPS);
         bulk_commit();
       }
       stores_pending = true;
@@ -652,14 +654,16 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     if (c == 0) {
       const int d = (int)(row % p.dim);
       cf *dAp = reinterpret_cast<cf *>(p.dA) + (int64_t)d * p.A_ds;
-      cf *dBp = reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds;
-      cf *dCp = reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds;
+      cf *dBp = NEED_BC ? reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds : nullptr;
+      cf *dCp = NEED_BC ? reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds : nullptr;
       if (S1) {
-        const cf ra = warp_sum(dA_acc), rb = warp_sum(dB_acc), rc = warp_sum(dC_acc);
-        __syncthreads();   // sh.red is free (no state loop in flight)
+        const cf ra = warp_sum(dA_acc);
+        cf rb, rc;
+        if (NEED_BC) { rb = warp_sum(dB_acc); rc = warp_sum(dC_acc); }
+        __syncthreads();   // sh.red is free (its readers of the previous row are done)
         if (lane == 0) { sh.red[0][warp] = ra; sh.red[1][warp] = rb; sh.red[2][warp] = rc; }
         __syncthreads();
-        if (tid < 3) {
+        if (tid < (NEED_BC ? 3 : 1)) {
           cf acc = cf(0.f, 0.f);
 #pragma unroll
           for (int w = 0; w < BWARPS; ++w) acc = acc + sh.red[tid][w];
@@ -672,17 +676,19 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
         for (int i = tid; i < S; i += BT) {
           atomicAdd(&dAp[(int64_t)i * p.A_ns].re, accA[i].re);
           atomicAdd(&dAp[(int64_t)i * p.A_ns].im, accA[i].im);
-          atomicAdd(&dBp[(int64_t)i * p.B_ns].re, accB[i].re);
-          atomicAdd(&dBp[(int64_t)i * p.B_ns].im, accB[i].im);
-          atomicAdd(&dCp[(int64_t)i * p.C_ns].re, accC[i].re);
-          atomicAdd(&dCp[(int64_t)i * p.C_ns].im, accC[i].im);
+          if (NEED_BC) {
+            atomicAdd(&dBp[(int64_t)i * p.B_ns].re, accB[i].re);
+            atomicAdd(&dBp[(int64_t)i * p.B_ns].im, accB[i].im);
+            atomicAdd(&dCp[(int64_t)i * p.C_ns].re, accC[i].re);
+            atomicAdd(&dCp[(int64_t)i * p.C_ns].im, accC[i].im);
+          }
         }
       }
     }
   }
-  if (tid == 0) bulk_wait<0>();
+  if (lane == 0) bulk_wait<0>();
   __syncthreads();
-  if (failed && tid == 0) atomicExch(&g_simpscan_status, 2);
+  if (failed) atomicExch(&g_simpscan_status, 2);
 }
 
 int sm_count() {
@@ -718,12 +724,12 @@ template <int DM, bool HAS_DA, bool S1> int launch_fwd_s(const b200_simpscan_arg
 template <int DM, bool HAS_DA> int launch_fwd(const b200_simpscan_args &a, cudaStream_t st) {
   return a.dstate == 1 ? launch_fwd_s<DM, HAS_DA, true>(a, st) : launch_fwd_s<DM, HAS_DA, false>(a, st);
 }
-template <int DM, bool HAS_DA, bool S1> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
+template <int DM, bool HAS_DA, bool S1, bool NEED_BC> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
   constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
   constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
   const int64_t rows = (int64_t)a.batch * a.dim;
   const size_t smem = 2 * (size_t)BUF_BYTES + OUT_BYTES + sizeof(BwdShared) + (size_t)5 * a.dstate * sizeof(cf);
-  auto k = simpscan_bwd_kernel<DM, HAS_DA, S1>;
+  auto k = simpscan_bwd_kernel<DM, HAS_DA, S1, NEED_BC>;
   if (int e = set_smem(k, smem)) return e;
   int64_t grid = rows;
   const int64_t resident = (int64_t)sm_count() * (HAS_DA ? 1 : 2);   // CTAs that fit at once
@@ -732,7 +738,8 @@ template <int DM, bool HAS_DA, bool S1> int launch_bwd_s(const b200_simpscan_arg
   return launch_status();
 }
 template <int DM, bool HAS_DA> int launch_bwd(const b200_simpscan_args &a, cudaStream_t st) {
-  return a.dstate == 1 ? launch_bwd_s<DM, HAS_DA, true>(a, st) : launch_bwd_s<DM, HAS_DA, false>(a, st);
+  if (a.dstate != 1) return launch_bwd_s<DM, HAS_DA, false, true>(a, st);
+  return a.dB ? launch_bwd_s<DM, HAS_DA, true, true>(a, st) : launch_bwd_s<DM, HAS_DA, true, false>(a, st);
 }
 
 int check(const b200_simpscan_args &a, bool bwd) {
@@ -745,8 +752,12 @@ int check(const b200_simpscan_args &a, bool bwd) {
   if (!bwd) {
     B200_REQUIRE(a.out && a.x, B200_ERR_NULL, "simpscan_fwd: out and x must be non-null");
   } else {
-    B200_REQUIRE(a.dout && a.du && a.ddelta && a.dA && a.dB && a.dC, B200_ERR_NULL,
-                 "simpscan_bwd: dout, du, ddelta, dA, dB, dC must be non-null");
+    B200_REQUIRE(a.dout && a.du && a.ddelta && a.dA, B200_ERR_NULL,
+                 "simpscan_bwd: dout, du, ddelta, dA must be non-null");
+    B200_REQUIRE((a.dB != nullptr) == (a.dC != nullptr), B200_ERR_NULL,
+                 "simpscan_bwd: dB and dC must be both given or both null");
+    B200_REQUIRE((a.dB && a.dC) || a.dstate == 1, B200_ERR_NULL,
+                 "simpscan_bwd: dB and dC may be null only when dstate == 1");
     B200_REQUIRE(a.x || a.seqlen <= kChunk, B200_ERR_NULL, "simpscan_bwd: x is required when seqlen > 2048");
     B200_REQUIRE(!a.deltaA || a.ddeltaA, B200_ERR_NULL, "simpscan_bwd: ddeltaA is required when deltaA is given");
   }

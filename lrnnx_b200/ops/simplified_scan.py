@@ -54,7 +54,8 @@ class SimplifiedScanFn(torch.autograd.Function):
         dC = torch.einsum("bhl,bpl->hp", dout, out.conj())
         if dx_out.stride(-1) != 1:
             dx_out = dx_out.contiguous()
-        res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dx_out, xs, ctx.discretization)
+        res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dx_out, xs, ctx.discretization,
+                                      need_dB_dC=False)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du = torch.einsum("ph,bpl->bhl", B.conj(), dBu)
@@ -109,7 +110,8 @@ class S5InnerFn(torch.autograd.Function):
         dC = torch.einsum("bhl,bpl->hp", dy_complex, scan_out.conj())
         if dscan.stride(-1) != 1:
             dscan = dscan.contiguous()
-        res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dscan, xs, ctx.discretization)
+        res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dscan, xs, ctx.discretization,
+                                      need_dB_dC=False)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du_scan = torch.einsum("ph,bpl->bhl", B.conj(), dBu)

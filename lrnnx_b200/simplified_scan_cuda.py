@@ -73,9 +73,10 @@ def fwd(u, delta, A, B, C, deltaA_, discretization_method_str):
     return [out, x]
 
 
-def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str):
+def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str, need_dB_dC=True):
     """Returns ``[du, ddelta, dA, dB, dC]`` plus ``ddeltaA`` when deltaA was given
-    (simplified_scan_cpu.cpp:328-330)."""
+    (simplified_scan_cpu.cpp:328-330).  ``need_dB_dC=False`` (an addition to the reference
+    signature, single-state rows only) skips the dB / dC sums and returns None in their place."""
     a, (batch, dim, seqlen, dstate) = _common(u, delta, A, B, C, deltaA_, discretization_method_str)
     _check(dout.dtype == torch.complex64 and dout.is_cuda, "dout must be a complex64 CUDA tensor")
     _check(dout.stride(-1) == 1 or dout.size(-1) == 1, "dout must be contiguous in the last dimension")
@@ -90,7 +91,10 @@ def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str):
     with torch.cuda.device(u.device):
         du = torch.empty_like(u)
         ddelta = torch.empty_like(delta)
-        dA, dB, dC = torch.zeros_like(A), torch.zeros_like(B), torch.zeros_like(C)
+        if A.is_contiguous() and B.is_contiguous() and C.is_contiguous():
+            dA, dB, dC = torch.zeros((3,) + tuple(A.shape), dtype=A.dtype, device=A.device).unbind(0)  # one fill
+        else:
+            dA, dB, dC = torch.zeros_like(A), torch.zeros_like(B), torch.zeros_like(C)
         ddeltaA = torch.empty_like(deltaA_) if deltaA_ is not None else None
         # the kernel addresses dA/dB/dC with the strides of A/B/C
         _check(dA.stride() == A.stride() and dB.stride() == B.stride() and dC.stride() == C.stride(),
@@ -98,7 +102,11 @@ def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str):
         a.x = None if x_ is None else x_.data_ptr()
         a.dout, a.du, a.ddelta = dout.data_ptr(), du.data_ptr(), ddelta.data_ptr()
         a.ddeltaA = None if ddeltaA is None else ddeltaA.data_ptr()
-        a.dA, a.dB, a.dC = dA.data_ptr(), dB.data_ptr(), dC.data_ptr()
+        a.dA = dA.data_ptr()
+        if need_dB_dC or dstate != 1:
+            a.dB, a.dC = dB.data_ptr(), dC.data_ptr()
+        else:
+            dB = dC = None
         a.dout_bs, a.dout_ds = dout.stride(0), dout.stride(1)
         a.du_bs, a.du_ds = du.stride(0), du.stride(1)
         a.ddelta_bs, a.ddelta_ds = ddelta.stride(0), ddelta.stride(1)
