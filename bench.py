@@ -12,9 +12,10 @@ x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
              every rank runs the full workload on its own batch shard (weak scaling) and the
              parameter gradients dA/dB/dC are all-reduced over NCCL inside the step.
   e2e        the same metric through the public op ``lrnnx_b200.ops.simplified_scan_fn``
-             starting from pinned HOST tensors: host->device copies of u and delta, the
-             complex projections (cuBLAS), both scan kernels, and a device->host read of the
-             loss every step.
+             starting from pinned HOST tensors: host->device copies of the layer's real
+             input x and of delta (micro-batched so the copies overlap the compute), the cast
+             to complex on the device, the complex projections (cuBLAS), both scan kernels,
+             and a device->host read of the loss every step.
   roofline   algorithmic HBM bytes of the dominant kernel / its mean launch time (CUDA
              events on the launching stream) against the measured copy bandwidth in
              MEASURED_PEAKS.json.
@@ -147,16 +148,18 @@ class S5Scan:
         from lrnnx_b200.ops import simplified_scan_fn
         self.dev, self.pg = dev, pg
         h = self.host_inputs()
-        self.h_u, self.h_delta, self.h_gout = h["u"].pin_memory(), h["delta"].pin_memory(), h["gout"].pin_memory()
+        self.h_x = h["u"].real.transpose(1, 2).contiguous().pin_memory()      # (batch, L, H) float32: the layer's input
+        self.h_delta, self.h_gout = h["delta"].pin_memory(), h["gout"].pin_memory()
         self.A, self.B, self.C = (h[k].to(dev) for k in ("A", "B", "C"))
-        self.u, self.delta, self.gout = self.h_u.to(dev), self.h_delta.to(dev), self.h_gout.to(dev)
+        self.u, self.delta, self.gout = h["u"].to(dev), self.h_delta.to(dev), self.h_gout.to(dev)
+        self.d_x = torch.empty_like(self.h_x, device=dev)
+        self.copy_stream = torch.cuda.Stream(device=dev)
         # kernel-level operands (what SimplifiedScanFn hands to the extension)
         self.Bu = torch.einsum("ph,bhl->bpl", self.B, self.u).contiguous()
         self.dBu_in = torch.einsum("hp,bhl->bpl", self.C.conj(), self.gout).contiguous()
         self.A_k = self.A.unsqueeze(-1).contiguous()
         self.one = torch.ones(self.P, 1, dtype=torch.complex64, device=dev)
         self.ext, self.op = simplified_scan_cuda, simplified_scan_fn
-        self.d_u = torch.empty_like(self.u)
         self.d_delta = torch.empty_like(self.delta)
         self.ev = []
 
@@ -168,7 +171,8 @@ class S5Scan:
         out, x = self.ext.fwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, "dirac")
         if record:
             e[1].record()
-        res = self.ext.bwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, self.dBu_in, x, "dirac")
+        res = self.ext.bwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, self.dBu_in, x, "dirac",
+                           need_dB_dC=False)   # as SimplifiedScanFn.backward calls it (identity B and C)
         if record:
             e[2].record()
             self.ev.append(e)
@@ -178,22 +182,45 @@ class S5Scan:
 
     launches_per_step = 2
 
+    e2e_micro_batches = 4
+
     def e2e_step(self):
-        u = self.d_u.copy_(self.h_u, non_blocking=True).requires_grad_(True)
-        delta = self.d_delta.copy_(self.h_delta, non_blocking=True).requires_grad_(True)
+        """One step as the LTV-S5 layer drives the op (lrnnx/models/ltv/s5.py:111-112): the real
+        input x (batch, L, H) and delta arrive from pinned host memory, u = x^T cast to complex64
+        on the device, then simplified_scan_fn forward + backward.  The batch is cut into
+        micro-batches so that the copy of micro-batch i+1 (copy stream) overlaps the compute of
+        micro-batch i; parameter gradients accumulate over the micro-batches."""
+        cur = torch.cuda.current_stream()
+        n = self.e2e_micro_batches if self.batch % self.e2e_micro_batches == 0 else 1
+        mb = self.batch // n
         A, B, C = (t.detach().requires_grad_(True) for t in (self.A, self.B, self.C))
-        y = self.op(u, delta, A, B, C, discretization="dirac")
-        loss = (y * self.gout.conj()).real.sum()
-        loss.backward()
+        self.copy_stream.wait_stream(cur)
+        evs = []
+        with torch.cuda.stream(self.copy_stream):
+            for i in range(n):
+                sl = slice(i * mb, (i + 1) * mb)
+                self.d_x[sl].copy_(self.h_x[sl], non_blocking=True)
+                self.d_delta[sl].copy_(self.h_delta[sl], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+                evs.append(ev)
+        total = torch.zeros((), device=self.dev)
+        for i in range(n):
+            sl = slice(i * mb, (i + 1) * mb)
+            cur.wait_event(evs[i])
+            u = self.d_x[sl].transpose(1, 2).contiguous().to(torch.complex64).requires_grad_(True)
+            delta = self.d_delta[sl].detach().requires_grad_(True)
+            y = self.op(u, delta, A, B, C, discretization="dirac")
+            loss = (y * self.gout[sl].conj()).real.sum()
+            loss.backward()
+            total += loss.detach()
         if self.pg is not None:
             for t in (A, B, C):
                 torch.distributed.all_reduce(torch.view_as_real(t.grad), group=self.pg)
-        val = float(loss.item())
-        self.d_u, self.d_delta = u.detach(), delta.detach()
-        return val
+        return float(total.item())
 
     def e2e_bytes(self):
-        return self.h_u.numel() * 8 + self.h_delta.numel() * 4, 4
+        return self.h_x.numel() * 4 + self.h_delta.numel() * 4, 4
 
     def kernel_rooflines(self):
         f = [a[0].elapsed_time(a[1]) for a in self.ev]

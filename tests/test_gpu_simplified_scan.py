@@ -89,6 +89,42 @@ def test_kernel_vs_oracle(disc, L, with_dA):
         assert_close(got[k].cpu(), want, rtol=GRTOL, atol_scale=GATOL, name=f"d{k}")
 
 
+@pytest.mark.parametrize("disc", ["bilinear", "zoh", "dirac"])
+@pytest.mark.parametrize("L,with_dA", [(700, False), (4097, True)])
+def test_kernel_constant_step(disc, L, with_dA):
+    """Rows whose step size does not change over time take the kernels' single-coefficient path;
+    rows 0-2 are constant over the whole row, row 3 over its first half only, row 4 never.
+    Also checks the need_dB_dC=False variant of the backward entry point."""
+    from lrnnx_b200 import simplified_scan_cuda
+    batch, P, S = 2, 5, 1
+    t, g, c = _kernel_inputs(batch, P, L, S, seed=100 + L, with_dA=with_dA)
+    for k in ("delta", "deltaA"):
+        if t[k] is not None:
+            t[k][:, :3, :] = t[k][:, :3, :1]
+            t[k][:, 3, : L // 2] = t[k][:, 3, :1]
+    one = torch.ones(P, S, dtype=torch.complex64)
+    cpu = {k: (v.clone().requires_grad_(True) if torch.is_tensor(v) else v) for k, v in t.items()}
+    out_c = O.simplified_kernel_oracle(cpu["u"], cpu["delta"], cpu["A"], one, one, cpu["deltaA"], disc)
+    cu = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items()}
+    out_g, x_g = simplified_scan_cuda.fwd(cu["u"], cu["delta"], cu["A"], one.cuda(), one.cuda(), cu["deltaA"], disc)
+    assert_close(out_g.cpu(), out_c.detach(), rtol=RTOL, atol_scale=ATOL, name="out")
+    gout = c(batch, P, L)
+    names = [k for k in ("u", "delta", "A", "deltaA") if cpu[k] is not None]
+    gc = torch.autograd.grad(out_c, [cpu[k] for k in names], gout, allow_unused=True)
+    for need in (True, False):
+        res = simplified_scan_cuda.bwd(cu["u"], cu["delta"], cu["A"], one.cuda(), one.cuda(), cu["deltaA"],
+                                       gout.cuda(), x_g, disc, need_dB_dC=need)
+        assert (res[3] is None) == (not need) and (res[4] is None) == (not need)
+        got = dict(u=res[0], delta=res[1], A=res[2])
+        if with_dA:
+            got["deltaA"] = res[5]
+        for k, want in zip(names, gc):
+            if want is None:
+                assert float(got[k].abs().max()) == 0.0
+                continue
+            assert_close(got[k].cpu(), want, rtol=GRTOL, atol_scale=GATOL, name=f"d{k}")
+
+
 def test_multi_state_kernel():
     """dstate > 1 with non-trivial B/C on the forward (out = sum_s h_s B_s C_s)."""
     from lrnnx_b200 import simplified_scan_cuda
