@@ -8,7 +8,8 @@ S5, complex64, B=8, P=256 states, H=512 channels, L=4096, forward + backward, re
 x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
 
   value      tokens/s of the scan hot path (forward + backward kernels through the C ABI,
-             operands resident in HBM); a token is one (batch, timestep) pair.  With N > 1
+             captured once and replayed as CUDA graphs, operands resident in HBM); a token is
+             one (batch, timestep) pair.  With N > 1
              every rank runs the full workload on its own batch shard (weak scaling) and the
              parameter gradients dA/dB/dC are all-reduced over NCCL inside the step.
   e2e        the same metric through the public op ``lrnnx_b200.ops.simplified_scan_fn``
@@ -162,23 +163,40 @@ class S5Scan:
         self.ext, self.op = simplified_scan_cuda, simplified_scan_fn
         self.d_delta = torch.empty_like(self.delta)
         self.ev = []
+        # The two extension calls are captured once as CUDA graphs (after a warm-up on a side
+        # stream); a step replays them, so the timed region holds the kernels and not the
+        # Python / ctypes launch path.
+        args = (self.Bu, self.delta, self.A_k, self.one, self.one, None)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                out, x = self.ext.fwd(*args, "dirac")
+                self.ext.bwd(*args, self.dBu_in, x, "dirac", need_dB_dC=False)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.g_fwd, self.g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.g_fwd):
+            self.out, self.x = self.ext.fwd(*args, "dirac")
+        with torch.cuda.graph(self.g_bwd):
+            # as SimplifiedScanFn.backward calls it (identity B and C: dB / dC are not needed)
+            self.res = self.ext.bwd(*args, self.dBu_in, self.x, "dirac", need_dB_dC=False)
 
     def step(self, record=False):
-        """forward + backward scan kernels through the extension entry points."""
+        """forward + backward scan kernels through the extension entry points (graph replay)."""
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
-        out, x = self.ext.fwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, "dirac")
+        self.g_fwd.replay()
         if record:
             e[1].record()
-        res = self.ext.bwd(self.Bu, self.delta, self.A_k, self.one, self.one, None, self.dBu_in, x, "dirac",
-                           need_dB_dC=False)   # as SimplifiedScanFn.backward calls it (identity B and C)
+        self.g_bwd.replay()
         if record:
             e[2].record()
             self.ev.append(e)
         if self.pg is not None:
-            torch.distributed.all_reduce(torch.view_as_real(res[2]), group=self.pg)
-        return res
+            torch.distributed.all_reduce(torch.view_as_real(self.res[2]), group=self.pg)
+        return self.res
 
     launches_per_step = 2
 
@@ -229,17 +247,17 @@ class S5Scan:
                 "simpscan_bwd_kernel": (self.bwd_bytes, statistics.mean(b))}
 
     # CPU arm: batch 1, first 1024 steps, same P and H (per-token work unchanged)
-    cpu_sample = "batch 1 of 8, first 1024 of 4096 timesteps, P=256, H=512 (same work per token)"
+    cpu_sample = "batch 2 of 8, all 4096 timesteps, P=256, H=512 (same work per token)"
 
     def cpu_step(self):
         from oracle import scan_oracle as O
         if not hasattr(self, "_cpu"):
-            self._cpu = self.host_inputs(batch=1, L=1024)
+            self._cpu = self.host_inputs(batch=2)
         h = self._cpu
         leaves = [h[k].clone().requires_grad_(True) for k in ("u", "delta", "A", "B", "C")]
         y = O.simplified_scan_oracle(*leaves, discretization="dirac")
         torch.autograd.grad(y, leaves, h["gout"])
-        return 1 * 1024
+        return 2 * self.L
 
 
 class S6Scan:
