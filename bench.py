@@ -461,7 +461,7 @@ class SsuStep:
 
     def kernel_rooflines(self):
         ms = statistics.mean(a[0].elapsed_time(a[1]) for a in self.ev) / self.layers
-        return {"ssu_vec_kernel": (self.fwd_bytes, ms)}
+        return {"ssu_tma_kernel": (self.fwd_bytes, ms)}
 
     def cpu_step(self):
         from oracle import scan_oracle as O

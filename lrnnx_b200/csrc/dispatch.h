@@ -15,4 +15,7 @@ bool selscan_bwd_fast_supported(const b200_selscan_bwd_args &a);
 int selscan_fwd_fast(const b200_selscan_fwd_args &a, cudaStream_t st);
 int selscan_bwd_fast(const b200_selscan_bwd_args &a, cudaStream_t st);
 
+// status word of the decode-step pipeline (ssu.cu): non-zero after an expired bounded wait
+int ssu_status_read();
+
 }  // namespace b200

@@ -829,7 +829,9 @@ int b200_simpscan_bwd(const b200_simpscan_args *args, void *stream) {
 int b200_device_status(void) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_simpscan_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+  const int w = ssu_status_read();
+  if (w < 0) return -1;
+  return v ? v : w;
 }
 
 }  // extern "C"

@@ -20,6 +20,16 @@
 #include "dispatch.h"
 
 namespace b200 {
+
+__device__ int g_ssu_status = 0;   // set to non-zero when a bounded barrier wait expires
+
+// host read of the status word (used by b200_device_status)
+int ssu_status_read() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ssu_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
 namespace {
 
 template <typename T> struct Vec16;   // 16-byte vector of state elements
@@ -276,6 +286,236 @@ template <typename ST> int launch_vec_x(const b200_ssu_args &a, cudaStream_t st)
   return launch_vec<ST, __half>(a, st);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Bulk-copy pipeline for dense operands.  A one-pass kernel with one 16-byte load per thread keeps
+// too few bytes in flight to reach the HBM rate, so here persistent CTAs stream tiles of 128 rows
+// through a 3-slot shared-memory ring: one thread issues 1-D bulk asynchronous copies (the TMA
+// engine) of the tile's state rows, A rows and per-row scalars onto the slot's mbarrier, the CTA
+// updates the state in place in shared memory, and the new state and the outputs leave through
+// bulk shared->global copies.  Two tiles per CTA are in flight while a third is computed.
+constexpr int TR = 128;   // rows per tile
+constexpr int TNS = 3;    // ring slots
+constexpr int TT = 256;   // threads per CTA
+
+template <typename ST, typename XT, int LPR> struct TmaSlot {
+  static constexpr int VEC = 16 / (int)sizeof(ST);
+  static constexpr int N = LPR * VEC;                    // dstate handled by this instantiation
+  static constexpr int ST_B = TR * N * (int)sizeof(ST);
+  static constexpr int A_B = TR * N * 4;
+  static constexpr int X_B = TR * (int)sizeof(XT);       // x, dt, z, deltaA, out
+  static constexpr int F_B = TR * 4;                     // D, dt_bias
+  static constexpr int BC_B = N * (int)sizeof(XT);       // a multiple of 16 for every supported N
+  static constexpr int OFF_S = 0;
+  static constexpr int OFF_A = OFF_S + ST_B;
+  static constexpr int OFF_X = OFF_A + A_B;
+  static constexpr int OFF_DT = OFF_X + X_B;
+  static constexpr int OFF_Z = OFF_DT + X_B;
+  static constexpr int OFF_DA = OFF_Z + X_B;
+  static constexpr int OFF_OUT = OFF_DA + X_B;
+  static constexpr int OFF_D = OFF_OUT + X_B;
+  static constexpr int OFF_BIAS = OFF_D + F_B;
+  static constexpr int OFF_B = OFF_BIAS + F_B;
+  static constexpr int OFF_C = OFF_B + BC_B;
+  static constexpr int SIZE = (OFF_C + BC_B + 127) / 128 * 128;
+  static constexpr int TOTAL = TNS * SIZE + TNS * 8;
+};
+
+template <typename XT> __device__ __forceinline__ float lds_act(const unsigned char *base, int i) {
+  return ldt<XT>(base, i);
+}
+
+template <typename ST, typename XT, int LPR>
+__global__ void __launch_bounds__(TT) ssu_tma_kernel(const b200_ssu_args p, int tiles_per_bh) {
+  using SL = TmaSlot<ST, XT, LPR>;
+  constexpr int VEC = SL::VEC, N = SL::N, RPP = TT / LPR, PASSES = TR / RPP;   // rows per pass
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + TNS * SL::SIZE);
+  const int tid = threadIdx.x, part = tid % LPR, r0 = tid / LPR;
+  const int64_t ntiles = (int64_t)p.batch * p.nheads * tiles_per_bh;
+  const int my = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  const int es = (int)sizeof(ST);
+
+  struct Tile { int b, h, m0, sb, g; };
+  auto tile_of = [&](int it) {
+    const int64_t tile = blockIdx.x + (int64_t)it * gridDim.x;
+    Tile t;
+    const int64_t bh = tile / tiles_per_bh;
+    t.m0 = (int)(tile - bh * tiles_per_bh) * TR;
+    t.b = (int)(bh / p.nheads);
+    t.h = (int)(bh - (int64_t)t.b * p.nheads);
+    t.sb = p.state_batch_indices ? p.state_batch_indices[t.b] : t.b;
+    t.g = t.h / (p.nheads / p.ngroups);
+    return t;
+  };
+  auto issue = [&](int it) {   // one thread
+    if (it >= my) return;
+    const Tile t = tile_of(it);
+    unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
+    uint64_t *bar = &full[it % TNS];
+    uint32_t bytes = SL::ST_B + SL::A_B + 2 * SL::X_B + 2 * SL::BC_B;
+    if (p.z) bytes += SL::X_B;
+    if (p.deltaA) bytes += SL::X_B;
+    if (p.D) bytes += SL::F_B;
+    if (p.dt_bias) bytes += SL::F_B;
+    mbar_expect_tx(bar, bytes);
+    const XT *xp = reinterpret_cast<const XT *>(p.x), *dtp = reinterpret_cast<const XT *>(p.dt);
+    bulk_g2s(s + SL::OFF_S, reinterpret_cast<const unsigned char *>(p.state) +
+                                ((int64_t)t.sb * p.state_bs + (int64_t)t.h * p.state_hs + (int64_t)t.m0 * p.state_ds) * es,
+             SL::ST_B, bar);
+    bulk_g2s(s + SL::OFF_A, reinterpret_cast<const float *>(p.A) + (int64_t)t.h * p.A_hs + (int64_t)t.m0 * p.A_ds, SL::A_B, bar);
+    bulk_g2s(s + SL::OFF_X, xp + (int64_t)t.b * p.x_bs + (int64_t)t.h * p.x_hs + t.m0, SL::X_B, bar);
+    bulk_g2s(s + SL::OFF_DT, dtp + (int64_t)t.b * p.dt_bs + (int64_t)t.h * p.dt_hs + t.m0, SL::X_B, bar);
+    if (p.z)
+      bulk_g2s(s + SL::OFF_Z, reinterpret_cast<const XT *>(p.z) + (int64_t)t.b * p.z_bs + (int64_t)t.h * p.z_hs + t.m0, SL::X_B, bar);
+    if (p.deltaA)
+      bulk_g2s(s + SL::OFF_DA,
+               reinterpret_cast<const XT *>(p.deltaA) + (int64_t)t.b * p.deltaA_bs + (int64_t)t.h * p.deltaA_hs + t.m0, SL::X_B, bar);
+    if (p.D) bulk_g2s(s + SL::OFF_D, reinterpret_cast<const float *>(p.D) + (int64_t)t.h * p.D_hs + t.m0, SL::F_B, bar);
+    if (p.dt_bias)
+      bulk_g2s(s + SL::OFF_BIAS, reinterpret_cast<const float *>(p.dt_bias) + (int64_t)t.h * p.dt_bias_hs + t.m0, SL::F_B, bar);
+    bulk_g2s(s + SL::OFF_B, reinterpret_cast<const XT *>(p.B) + (int64_t)t.b * p.B_bs + (int64_t)t.g * p.B_gs, SL::BC_B, bar);
+    bulk_g2s(s + SL::OFF_C, reinterpret_cast<const XT *>(p.C) + (int64_t)t.b * p.C_bs + (int64_t)t.g * p.C_gs, SL::BC_B, bar);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < TNS; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 0; i < TNS - 1; ++i) issue(i);
+  }
+  bool failed = false;
+  for (int it = 0; it < my; ++it) {
+    unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
+    if (!failed && !mbar_wait(&full[it % TNS], (uint32_t)(it / TNS) & 1u)) failed = true;
+    float Bn[VEC], Cn[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      Bn[i] = lds_act<XT>(s + SL::OFF_B, part * VEC + i);
+      Cn[i] = lds_act<XT>(s + SL::OFF_C, part * VEC + i);
+    }
+    const bool plain_exp = p.method == B200_DISC_MAMBA || p.method == B200_DISC_DIRAC;
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+      const int row = r0 + j * RPP;
+      const float xv = lds_act<XT>(s + SL::OFF_X, row);
+      float d = lds_act<XT>(s + SL::OFF_DT, row);
+      if (p.dt_bias) d += reinterpret_cast<const float *>(s + SL::OFF_BIAS)[row];
+      if (p.dt_softplus) d = softplus20(d);
+      const float da = p.deltaA ? lds_act<XT>(s + SL::OFF_DA, row) : d;
+      ST *srow = reinterpret_cast<ST *>(s + SL::OFF_S) + row * N + part * VEC;
+      const float *arow = reinterpret_cast<const float *>(s + SL::OFF_A) + row * N + part * VEC;
+      Vec16<ST> sv;
+      sv.load(srow);
+      float Av[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(arow + i);
+        Av[i] = a4.x; Av[i + 1] = a4.y; Av[i + 2] = a4.z; Av[i + 3] = a4.w;
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float a, kb;
+        if (plain_exp) {   // a = exp(A dA) by the SFU's ex2 (relative error 2^-22); kb = dt or 1
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(Av[i] * da * kLog2e));
+          kb = p.method == B200_DISC_MAMBA ? d : 1.f;
+        } else {
+          step_coef(p.method, Av[i], d, da, a, kb);
+        }
+        const float v = sv.v[i] * a + kb * Bn[i] * xv;
+        sv.v[i] = v;
+        acc += v * Cn[i];
+      }
+      sv.store(srow);
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (part == 0) {
+        float out = acc;
+        if (p.D) out += reinterpret_cast<const float *>(s + SL::OFF_D)[row] * xv;
+        if (p.z) {
+          const float zv = lds_act<XT>(s + SL::OFF_Z, row);
+          out *= zv * sigmoidf_(zv);
+        }
+        stt<XT>(s + SL::OFF_OUT, row, out);
+      }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      const Tile t = tile_of(it);
+      bulk_s2g(reinterpret_cast<unsigned char *>(p.state) +
+                   ((int64_t)t.sb * p.state_bs + (int64_t)t.h * p.state_hs + (int64_t)t.m0 * p.state_ds) * es,
+               s + SL::OFF_S, SL::ST_B);
+      bulk_s2g(reinterpret_cast<XT *>(p.out) + (int64_t)t.b * p.out_bs + (int64_t)t.h * p.out_hs + t.m0, s + SL::OFF_OUT, SL::X_B);
+      bulk_commit();
+      // the slot refilled next held tile it-1: its stores (the group before this one) must have been read out
+      bulk_wait_read<1>();
+      issue(it + TNS - 1);
+    }
+  }
+  if (tid == 0) bulk_wait<0>();
+  if (failed) atomicExch(&g_ssu_status, 3);
+}
+
+int ssu_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <typename ST, typename XT, int LPR> int launch_tma_l(const b200_ssu_args &a, cudaStream_t st) {
+  using SL = TmaSlot<ST, XT, LPR>;
+  auto k = ssu_tma_kernel<ST, XT, LPR>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  const int tiles_per_bh = a.dim / TR;
+  const int64_t ntiles = (int64_t)a.batch * a.nheads * tiles_per_bh;
+  const int per_sm = (227 * 1024) / (SL::TOTAL + 1024);
+  int64_t grid = (int64_t)ssu_sm_count() * (per_sm < 1 ? 1 : per_sm);
+  if (grid > ntiles) grid = ntiles;
+  k<<<(unsigned)grid, TT, SL::TOTAL, st>>>(a, tiles_per_bh);
+  return launch_status();
+}
+template <typename ST, typename XT> int launch_tma(const b200_ssu_args &a, cudaStream_t st) {
+  constexpr int VEC = 16 / (int)sizeof(ST);
+  return a.dstate == 2 * VEC ? launch_tma_l<ST, XT, 2>(a, st) : launch_tma_l<ST, XT, 4>(a, st);
+}
+template <typename ST> int launch_tma_x(const b200_ssu_args &a, cudaStream_t st) {
+  if (a.x_dtype == B200_F32) return launch_tma<ST, float>(a, st);
+  if (a.x_dtype == B200_BF16) return launch_tma<ST, __nv_bfloat16>(a, st);
+  return launch_tma<ST, __half>(a, st);
+}
+
+// Operands the bulk-copy pipeline can address: dense state / A tiles, unit-stride rows for the
+// per-row tensors, every tile start on a 16-byte boundary.
+bool tma_ok(const b200_ssu_args &a) {
+  const int es = act_size(a.state_dtype), xs = act_size(a.x_dtype);
+  const int vec = 16 / es;
+  if (a.dstate != 2 * vec && a.dstate != 4 * vec) return false;
+  if (a.dim % TR != 0) return false;
+  auto al = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const int64_t xm = 16 / xs;   // elements of the activation dtype per 16 bytes
+  if (a.state_ns != 1 || a.state_ds != a.dstate || !al(a.state) || (a.state_bs * es) % 16 || (a.state_hs * es) % 16) return false;
+  if (a.A_ns != 1 || a.A_ds != a.dstate || !al(a.A) || a.A_hs % 4) return false;
+  if (a.x_ds != 1 || !al(a.x) || a.x_bs % xm || a.x_hs % xm) return false;
+  if (a.dt_ds != 1 || !al(a.dt) || a.dt_bs % xm || a.dt_hs % xm) return false;
+  if (a.out_ds != 1 || !al(a.out) || a.out_bs % xm || a.out_hs % xm) return false;
+  if (a.z && (a.z_ds != 1 || !al(a.z) || a.z_bs % xm || a.z_hs % xm)) return false;
+  if (a.deltaA && (a.deltaA_ds != 1 || !al(a.deltaA) || a.deltaA_bs % xm || a.deltaA_hs % xm)) return false;
+  if (a.D && (a.D_ds != 1 || !al(a.D) || a.D_hs % 4)) return false;
+  if (a.dt_bias && (a.dt_bias_ds != 1 || !al(a.dt_bias) || a.dt_bias_hs % 4)) return false;
+  if (a.B_ns != 1 || !al(a.B) || a.B_bs % xm || a.B_gs % xm) return false;
+  if (a.C_ns != 1 || !al(a.C) || a.C_bs % xm || a.C_gs % xm) return false;
+  return true;
+}
+
 int launch_generic(const b200_ssu_args &a, cudaStream_t st) {
   const int64_t nrows = (int64_t)a.batch * a.nheads * a.dim;
   int lpr = 1;
@@ -323,6 +563,11 @@ extern "C" int b200_ssu_step(const b200_ssu_args *args, void *stream) {
                        (!a.deltaA || a.deltaA_dtype == a.x_dtype) && (!a.D || a.D_dtype == B200_F32) &&
                        (!a.dt_bias || a.dt_bias_dtype == B200_F32);
   if (dense && uniform && (int64_t)a.batch * a.nheads * a.dim < (int64_t(1) << 31)) {
+    if (tma_ok(a)) {
+      if (a.state_dtype == B200_F32) return launch_tma_x<float>(a, st);
+      if (a.state_dtype == B200_BF16) return launch_tma_x<__nv_bfloat16>(a, st);
+      return launch_tma_x<__half>(a, st);
+    }
     if (a.state_dtype == B200_F32) return launch_vec_x<float>(a, st);
     if (a.state_dtype == B200_BF16) return launch_vec_x<__nv_bfloat16>(a, st);
     return launch_vec_x<__half>(a, st);

@@ -110,6 +110,44 @@ def test_state_batch_indices_and_bf16():
     assert torch.equal(big_g.cpu()[untouched], big[untouched])
 
 
+@pytest.mark.parametrize("stype,itype,N", [(torch.float32, torch.float32, 8), (torch.float32, torch.bfloat16, 16),
+                                           (torch.bfloat16, torch.bfloat16, 16), (torch.float16, torch.float16, 32)])
+@pytest.mark.parametrize("method,heads,with_dA", [("mamba", None, False), ("zoh", 3, True), ("bilinear", None, False),
+                                                  ("dirac", 3, False), ("rglru", None, True), ("s7", None, False)])
+def test_state_update_tile_pipeline(stype, itype, N, method, heads, with_dA):
+    """Dense operands with dim a multiple of 128 take the bulk-copy tile pipeline; enough tiles
+    (batch 5 x 3 heads x 3 tiles, or 5 x 6) that the persistent CTAs wrap around their 3-slot
+    ring, with optional z / D / dt_bias / deltaA, every discretization and indirect state rows."""
+    from lrnnx_b200.ops import selective_state_update
+    batch, hd = 5, 384
+    dim = hd * (heads or 2)
+    t = _inputs(batch, dim, N, seed=N + len(method), itype=itype, stype=stype, heads=heads, ngroups=1)
+    g = torch.Generator().manual_seed(17)
+    if method == "rglru":
+        t["A"] = torch.rand(t["A"].shape, generator=g) * 0.5 + 0.4      # A ** deltaA needs A > 0
+    if with_dA:
+        t["deltaA"] = (torch.rand(t["x"].shape, generator=g) * 0.5 + 0.05).to(itype)
+    if method in ("bilinear", "s7"):
+        t["z"] = None
+    pool = batch + 2
+    big = torch.randn(pool, *t["state"].shape[1:], generator=g).to(stype)
+    idx = torch.tensor([6, 0, 3, 1, 4], dtype=torch.int32)
+    args = {k: v for k, v in t.items() if k != "state"}
+    ref_state = big[idx.long()].clone()
+    out_c = O.selective_state_update_oracle(ref_state, **args, dt_softplus=True, discretization=method)
+    big_g = big.cuda()
+    out_g = selective_state_update(big_g, **{k: (v.cuda() if torch.is_tensor(v) else v) for k, v in args.items()},
+                                   dt_softplus=True, discretization=method, state_batch_indices=idx.cuda())
+    lo = stype != torch.float32 or itype != torch.float32
+    rtol, atol = (3e-2, 1e-2) if lo else (1e-4, 1e-5)
+    assert_close(out_g.float().cpu(), out_c.float(), rtol=rtol, atol_scale=atol, name="out")
+    assert_close(big_g.cpu()[idx.long()].float(), ref_state.float(), rtol=rtol, atol_scale=atol, name="state")
+    untouched = [i for i in range(pool) if i not in idx.tolist()]
+    assert torch.equal(big_g.cpu()[untouched], big[untouched])
+    from lrnnx_b200 import _lib
+    assert _lib.lib().b200_device_status() == 0
+
+
 def test_state_update_in_cuda_graph():
     """The step is capturable: static buffers, launch on the capturing stream, output allocated by
     the caching allocator (pattern of lrnnx/utils/generation.py:143-155)."""
