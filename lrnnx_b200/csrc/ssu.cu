@@ -290,9 +290,14 @@ template <typename ST> int launch_vec_x(const b200_ssu_args &a, cudaStream_t st)
 // Bulk-copy pipeline for dense operands.  A one-pass kernel with one 16-byte load per thread keeps
 // too few bytes in flight to reach the HBM rate, so here persistent CTAs stream tiles of 128 rows
 // through a 3-slot shared-memory ring: one thread issues 1-D bulk asynchronous copies (the TMA
-// engine) of the tile's state rows, A rows and per-row scalars onto the slot's mbarrier, the CTA
-// updates the state in place in shared memory, and the new state and the outputs leave through
-// bulk shared->global copies.  Two tiles per CTA are in flight while a third is computed.
+// engine) of the tile's state rows and per-row scalars onto the slot's mbarrier, the CTA updates
+// the state in place in shared memory, and the new state and the outputs leave through bulk
+// shared->global copies.  Two tiles per CTA are in flight while a third is computed.  Per tile:
+//   phase A  one thread per row: dt' = softplus(dt + bias), x and deltaA as float32
+//   phase B  LPR lanes per row: the state update and the row's partial sum of state * C
+//            (A comes straight from global memory: it is shared by all batch rows and L2-resident)
+//   phase C  one thread per row: + D x, * silu(z), conversion to the output dtype
+// so the per-row scalar work is done once per row and not once per lane of the row.
 constexpr int TR = 128;   // rows per tile
 constexpr int TNS = 3;    // ring slots
 constexpr int TT = 256;   // threads per CTA
@@ -301,13 +306,11 @@ template <typename ST, typename XT, int LPR> struct TmaSlot {
   static constexpr int VEC = 16 / (int)sizeof(ST);
   static constexpr int N = LPR * VEC;                    // dstate handled by this instantiation
   static constexpr int ST_B = TR * N * (int)sizeof(ST);
-  static constexpr int A_B = TR * N * 4;
   static constexpr int X_B = TR * (int)sizeof(XT);       // x, dt, z, deltaA, out
   static constexpr int F_B = TR * 4;                     // D, dt_bias
   static constexpr int BC_B = N * (int)sizeof(XT);       // a multiple of 16 for every supported N
   static constexpr int OFF_S = 0;
-  static constexpr int OFF_A = OFF_S + ST_B;
-  static constexpr int OFF_X = OFF_A + A_B;
+  static constexpr int OFF_X = OFF_S + ST_B;
   static constexpr int OFF_DT = OFF_X + X_B;
   static constexpr int OFF_Z = OFF_DT + X_B;
   static constexpr int OFF_DA = OFF_Z + X_B;
@@ -317,7 +320,9 @@ template <typename ST, typename XT, int LPR> struct TmaSlot {
   static constexpr int OFF_B = OFF_BIAS + F_B;
   static constexpr int OFF_C = OFF_B + BC_B;
   static constexpr int SIZE = (OFF_C + BC_B + 127) / 128 * 128;
-  static constexpr int TOTAL = TNS * SIZE + TNS * 8;
+  static constexpr int OFF_ROW = TNS * SIZE;             // float [4][TR]: dt', x, deltaA, row sums
+  static constexpr int OFF_BAR = OFF_ROW + 4 * TR * 4;
+  static constexpr int TOTAL = OFF_BAR + TNS * 8;
 };
 
 template <typename XT> __device__ __forceinline__ float lds_act(const unsigned char *base, int i) {
@@ -325,34 +330,36 @@ template <typename XT> __device__ __forceinline__ float lds_act(const unsigned c
 }
 
 template <typename ST, typename XT, int LPR>
-__global__ void __launch_bounds__(TT) ssu_tma_kernel(const b200_ssu_args p, int tiles_per_bh) {
+__global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, int tiles_per_bh) {
   using SL = TmaSlot<ST, XT, LPR>;
   constexpr int VEC = SL::VEC, N = SL::N, RPP = TT / LPR, PASSES = TR / RPP;   // rows per pass
   extern __shared__ __align__(128) unsigned char smem[];
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + TNS * SL::SIZE);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + SL::OFF_BAR);
+  float *row_d = reinterpret_cast<float *>(smem + SL::OFF_ROW), *row_x = row_d + TR, *row_da = row_d + 2 * TR,
+        *row_acc = row_d + 3 * TR;
   const int tid = threadIdx.x, part = tid % LPR, r0 = tid / LPR;
-  const int64_t ntiles = (int64_t)p.batch * p.nheads * tiles_per_bh;
+  const uint32_t ntiles = (uint32_t)p.batch * (uint32_t)p.nheads * (uint32_t)tiles_per_bh;   // < 2^31 (host check)
   const int my = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
   const int es = (int)sizeof(ST);
 
   struct Tile { int b, h, m0, sb, g; };
-  auto tile_of = [&](int it) {
-    const int64_t tile = blockIdx.x + (int64_t)it * gridDim.x;
+  auto tile_of = [&](int it, bool need_sb) {
+    const uint32_t tile = blockIdx.x + (uint32_t)it * gridDim.x;
     Tile t;
-    const int64_t bh = tile / tiles_per_bh;
-    t.m0 = (int)(tile - bh * tiles_per_bh) * TR;
-    t.b = (int)(bh / p.nheads);
-    t.h = (int)(bh - (int64_t)t.b * p.nheads);
-    t.sb = p.state_batch_indices ? p.state_batch_indices[t.b] : t.b;
+    const uint32_t bh = tile / (uint32_t)tiles_per_bh;
+    t.m0 = (int)(tile - bh * (uint32_t)tiles_per_bh) * TR;
+    t.b = (int)(bh / (uint32_t)p.nheads);
+    t.h = (int)(bh - (uint32_t)t.b * (uint32_t)p.nheads);
+    t.sb = (need_sb && p.state_batch_indices) ? p.state_batch_indices[t.b] : t.b;
     t.g = t.h / (p.nheads / p.ngroups);
     return t;
   };
   auto issue = [&](int it) {   // one thread
     if (it >= my) return;
-    const Tile t = tile_of(it);
+    const Tile t = tile_of(it, true);
     unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
     uint64_t *bar = &full[it % TNS];
-    uint32_t bytes = SL::ST_B + SL::A_B + 2 * SL::X_B + 2 * SL::BC_B;
+    uint32_t bytes = SL::ST_B + 2 * SL::X_B + 2 * SL::BC_B;
     if (p.z) bytes += SL::X_B;
     if (p.deltaA) bytes += SL::X_B;
     if (p.D) bytes += SL::F_B;
@@ -362,7 +369,6 @@ __global__ void __launch_bounds__(TT) ssu_tma_kernel(const b200_ssu_args p, int 
     bulk_g2s(s + SL::OFF_S, reinterpret_cast<const unsigned char *>(p.state) +
                                 ((int64_t)t.sb * p.state_bs + (int64_t)t.h * p.state_hs + (int64_t)t.m0 * p.state_ds) * es,
              SL::ST_B, bar);
-    bulk_g2s(s + SL::OFF_A, reinterpret_cast<const float *>(p.A) + (int64_t)t.h * p.A_hs + (int64_t)t.m0 * p.A_ds, SL::A_B, bar);
     bulk_g2s(s + SL::OFF_X, xp + (int64_t)t.b * p.x_bs + (int64_t)t.h * p.x_hs + t.m0, SL::X_B, bar);
     bulk_g2s(s + SL::OFF_DT, dtp + (int64_t)t.b * p.dt_bs + (int64_t)t.h * p.dt_hs + t.m0, SL::X_B, bar);
     if (p.z)
@@ -386,44 +392,57 @@ __global__ void __launch_bounds__(TT) ssu_tma_kernel(const b200_ssu_args p, int 
   if (tid == 0) {
     for (int i = 0; i < TNS - 1; ++i) issue(i);
   }
+  const bool plain_exp = p.method == B200_DISC_MAMBA || p.method == B200_DISC_DIRAC;
   bool failed = false;
   for (int it = 0; it < my; ++it) {
     unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
+    const Tile t = tile_of(it, false);
+    // A rows of this thread's passes: plain 16-byte loads, issued before the wait for the tile
+    float Av[PASSES][VEC];
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+      const float *arow = reinterpret_cast<const float *>(p.A) + (int64_t)t.h * p.A_hs +
+                          (int64_t)(t.m0 + r0 + j * RPP) * N + part * VEC;
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(arow + i);
+        Av[j][i] = a4.x; Av[j][i + 1] = a4.y; Av[j][i + 2] = a4.z; Av[j][i + 3] = a4.w;
+      }
+    }
     if (!failed && !mbar_wait(&full[it % TNS], (uint32_t)(it / TNS) & 1u)) failed = true;
+    // ---- phase A: per-row scalars
+    if (tid < TR) {
+      float d = lds_act<XT>(s + SL::OFF_DT, tid);
+      if (p.dt_bias) d += reinterpret_cast<const float *>(s + SL::OFF_BIAS)[tid];
+      if (p.dt_softplus) d = softplus20(d);
+      row_d[tid] = d;
+      row_x[tid] = lds_act<XT>(s + SL::OFF_X, tid);
+      row_da[tid] = p.deltaA ? lds_act<XT>(s + SL::OFF_DA, tid) : d;
+    }
     float Bn[VEC], Cn[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       Bn[i] = lds_act<XT>(s + SL::OFF_B, part * VEC + i);
       Cn[i] = lds_act<XT>(s + SL::OFF_C, part * VEC + i);
     }
-    const bool plain_exp = p.method == B200_DISC_MAMBA || p.method == B200_DISC_DIRAC;
+    __syncthreads();
+    // ---- phase B: state update
 #pragma unroll
     for (int j = 0; j < PASSES; ++j) {
       const int row = r0 + j * RPP;
-      const float xv = lds_act<XT>(s + SL::OFF_X, row);
-      float d = lds_act<XT>(s + SL::OFF_DT, row);
-      if (p.dt_bias) d += reinterpret_cast<const float *>(s + SL::OFF_BIAS)[row];
-      if (p.dt_softplus) d = softplus20(d);
-      const float da = p.deltaA ? lds_act<XT>(s + SL::OFF_DA, row) : d;
+      const float xv = row_x[row], d = row_d[row], da = row_da[row];
       ST *srow = reinterpret_cast<ST *>(s + SL::OFF_S) + row * N + part * VEC;
-      const float *arow = reinterpret_cast<const float *>(s + SL::OFF_A) + row * N + part * VEC;
       Vec16<ST> sv;
       sv.load(srow);
-      float Av[VEC];
-#pragma unroll
-      for (int i = 0; i < VEC; i += 4) {
-        const float4 a4 = *reinterpret_cast<const float4 *>(arow + i);
-        Av[i] = a4.x; Av[i + 1] = a4.y; Av[i + 2] = a4.z; Av[i + 3] = a4.w;
-      }
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         float a, kb;
         if (plain_exp) {   // a = exp(A dA) by the SFU's ex2 (relative error 2^-22); kb = dt or 1
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(Av[i] * da * kLog2e));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(Av[j][i] * da * kLog2e));
           kb = p.method == B200_DISC_MAMBA ? d : 1.f;
         } else {
-          step_coef(p.method, Av[i], d, da, a, kb);
+          step_coef(p.method, Av[j][i], d, da, a, kb);
         }
         const float v = sv.v[i] * a + kb * Bn[i] * xv;
         sv.v[i] = v;
@@ -432,24 +451,28 @@ __global__ void __launch_bounds__(TT) ssu_tma_kernel(const b200_ssu_args p, int 
       sv.store(srow);
 #pragma unroll
       for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (part == 0) {
-        float out = acc;
-        if (p.D) out += reinterpret_cast<const float *>(s + SL::OFF_D)[row] * xv;
-        if (p.z) {
-          const float zv = lds_act<XT>(s + SL::OFF_Z, row);
-          out *= zv * sigmoidf_(zv);
-        }
-        stt<XT>(s + SL::OFF_OUT, row, out);
+      if (part == 0) row_acc[row] = acc;
+    }
+    __syncthreads();
+    // ---- phase C: outputs
+    if (tid < TR) {
+      float out = row_acc[tid];
+      if (p.D) out += reinterpret_cast<const float *>(s + SL::OFF_D)[tid] * row_x[tid];
+      if (p.z) {
+        const float zv = lds_act<XT>(s + SL::OFF_Z, tid);
+        out *= zv * sigmoidf_(zv);
       }
+      stt<XT>(s + SL::OFF_OUT, tid, out);
     }
     fence_proxy_async();
     __syncthreads();
     if (tid == 0) {
-      const Tile t = tile_of(it);
+      const Tile ts = tile_of(it, true);
       bulk_s2g(reinterpret_cast<unsigned char *>(p.state) +
-                   ((int64_t)t.sb * p.state_bs + (int64_t)t.h * p.state_hs + (int64_t)t.m0 * p.state_ds) * es,
+                   ((int64_t)ts.sb * p.state_bs + (int64_t)ts.h * p.state_hs + (int64_t)ts.m0 * p.state_ds) * es,
                s + SL::OFF_S, SL::ST_B);
-      bulk_s2g(reinterpret_cast<XT *>(p.out) + (int64_t)t.b * p.out_bs + (int64_t)t.h * p.out_hs + t.m0, s + SL::OFF_OUT, SL::X_B);
+      bulk_s2g(reinterpret_cast<XT *>(p.out) + (int64_t)ts.b * p.out_bs + (int64_t)ts.h * p.out_hs + ts.m0, s + SL::OFF_OUT,
+               SL::X_B);
       bulk_commit();
       // the slot refilled next held tile it-1: its stores (the group before this one) must have been read out
       bulk_wait_read<1>();
@@ -477,8 +500,9 @@ template <typename ST, typename XT, int LPR> int launch_tma_l(const b200_ssu_arg
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
   const int tiles_per_bh = a.dim / TR;
   const int64_t ntiles = (int64_t)a.batch * a.nheads * tiles_per_bh;
-  const int per_sm = (227 * 1024) / (SL::TOTAL + 1024);
-  int64_t grid = (int64_t)ssu_sm_count() * (per_sm < 1 ? 1 : per_sm);
+  int per_sm = (227 * 1024) / (SL::TOTAL + 1024);
+  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);   // the launch bounds allow 4 CTAs per SM
+  int64_t grid = (int64_t)ssu_sm_count() * per_sm;
   if (grid > ntiles) grid = ntiles;
   k<<<(unsigned)grid, TT, SL::TOTAL, st>>>(a, tiles_per_bh);
   return launch_status();
