@@ -137,6 +137,183 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   }
 }
 
+// ---- vectorized variant: 8 consecutive timesteps per lane (256 per iteration), 16-byte typed
+// loads and stores.  Needs 16-byte aligned rows, a sequence length and segment starts that are
+// multiples of 8 — what the throughput forward kernel, the only producer of in-GPU segments,
+// requires as well.
+template <typename T> struct V8;
+template <> struct V8<float> {
+  __device__ static void load(const float *p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4 *>(p)[0], b = reinterpret_cast<const float4 *>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  __device__ static void store(float *p, const float (&v)[8]) {
+    reinterpret_cast<float4 *>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4 *>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct V8<__nv_bfloat16> {
+  __device__ static void load(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4 *>(p);
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  __device__ static void store(__nv_bfloat16 *p, const float (&v)[8]) {
+    uint4 t;
+    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(p) = t;
+  }
+};
+template <> struct V8<__half> {
+  __device__ static void load(const __half *p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  __device__ static void store(__half *p, const float (&v)[8]) {
+    uint4 t;
+    __half2 *h = reinterpret_cast<__half2 *>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(p) = t;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SPW * 32) selscan_fixup_vec_kernel(const b200_selscan_fixup_args q) {
+  const b200_selscan_fwd_args &p = q.f;
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * SPW + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int nseg = q.n_segments > 1 ? q.n_segments : 1;
+  const int seg = (int)blockIdx.y;
+  const int t_begin = nseg > 1 ? seg * q.seg_len : 0;
+  const int L = nseg > 1 ? min(p.seqlen, t_begin + q.seg_len) : p.seqlen;
+  if (t_begin >= L) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int g = d / (p.dim / p.n_groups);
+  const int N = p.dstate;
+  const int n_chunks = (p.seqlen + kChunk - 1) / kChunk;
+  float *A2 = sm + warp * 2 * N;     // A * log2(e)
+  float *hin = A2 + N;
+  const float *A = reinterpret_cast<const float *>(p.A) + (int64_t)d * p.A_ds;
+  const float *hsrc = reinterpret_cast<const float *>(q.h_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
+  const float *psrc = reinterpret_cast<const float *>(q.p_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
+  float amax = -INFINITY, hmax = 0.f;
+  for (int n = lane; n < N; n += 32) {
+    const float a = A[(int64_t)n * p.A_ns];
+    A2[n] = a * kLog2e;
+    hin[n] = hsrc[n];
+    amax = fmaxf(amax, a * kLog2e);
+    hmax = fmaxf(hmax, fabsf(hsrc[n]));
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, m));
+  }
+  __syncwarp();
+  float *xrow = reinterpret_cast<float *>(p.x) + row * n_chunks * 2 * N;
+  const int c_begin = t_begin / kChunk, c_end = (L + kChunk - 1) / kChunk;
+  for (int i = lane + c_begin * N; i < c_end * N; i += 32) {
+    const int c = i / N, n = i % N;
+    const float P = xrow[(int64_t)c * 2 * N + 2 * n];
+    xrow[(int64_t)c * 2 * N + 2 * n + 1] += P * hin[n];
+    xrow[(int64_t)c * 2 * N + 2 * n] = P * psrc[n];
+  }
+  if (hmax == 0.f) return;           // nothing enters this segment
+  const T *dl = reinterpret_cast<const T *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const T *Cg = reinterpret_cast<const T *>(p.C) + (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const T *zr = p.z ? reinterpret_cast<const T *>(p.z) + (int64_t)b * p.z_bs + (int64_t)d * p.z_ds : nullptr;
+  T *oz = p.z ? reinterpret_cast<T *>(p.out_z) + (int64_t)b * p.out_z_bs + (int64_t)d * p.out_z_ds : nullptr;
+  const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
+  const float cutoff = sizeof(T) == 4 ? -32.f : -14.f;
+  float carry = 0.f;                 // sum of delta' over the steps already processed (warp-uniform)
+  for (int t0 = t_begin; t0 < L; t0 += 256) {
+    if (amax * carry < cutoff) break;   // every state has decayed away
+    const int t = t0 + lane * 8;
+    const bool live = t < L;            // L and t are multiples of 8: a lane's 8 steps are all valid or all past the end
+    float cum[8];
+    if (live) {
+      V8<T>::load(dl + t, cum);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float dv = cum[i] + bias;
+        if (p.delta_softplus) dv = softplus20(dv);
+        cum[i] = dv;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cum[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 1; i < 8; ++i) cum[i] += cum[i - 1];
+    float incl = cum[7];
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    const float before = carry + incl - cum[7];      // delta' summed over everything before this lane
+    const float carry_before = carry;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cum[i] += before;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int n = 0; n < N; ++n) {
+      const float a2 = A2[n];
+      if (a2 * carry_before < cutoff) continue;      // this state has already decayed away (warp-uniform)
+      if (live) {
+        const float hn = hin[n];
+        float cv[8];
+        V8<T>::load(Cg + (int64_t)n * p.C_ns + t, cv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float e;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a2 * cum[i]));
+          acc[i] = fmaf(cv[i] * e, hn, acc[i]);
+        }
+      }
+    }
+    if (live) {
+      // out holds the rounded zero-state result; the correction is added in fp32
+      float o[8];
+      V8<T>::load(out + t, o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += acc[i];
+      V8<T>::store(out + t, o);
+      if (zr) {
+        float zv[8];
+        V8<T>::load(zr + t, zv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] *= zv[i] * sigmoidf_(zv[i]);
+        V8<T>::store(oz + t, o);
+      }
+    }
+  }
+}
+
+bool fixup_vec_ok(const b200_selscan_fixup_args &q) {
+  const b200_selscan_fwd_args &a = q.f;
+  const int es = a.dtype == B200_F32 ? 4 : 2;
+  const int64_t m = 16 / es;
+  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (a.seqlen % 8 != 0 || (q.n_segments > 1 && q.seg_len % 8 != 0)) return false;
+  if (!al(a.delta) || !al(a.C) || !al(a.out) || a.delta_bs % m || a.delta_ds % m || a.out_bs % m || a.out_ds % m ||
+      a.C_bs % m || a.C_gs % m || a.C_ns % m)
+    return false;
+  if (a.z && (!al(a.z) || !al(a.out_z) || a.z_bs % m || a.z_ds % m || a.out_z_bs % m || a.out_z_ds % m)) return false;
+  return true;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -160,6 +337,13 @@ extern "C" int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *str
   B200_REQUIRE(args->n_segments <= 1 || (args->seg_len > 0 && args->seg_len % kChunk == 0), B200_ERR_SHAPE,
                "selscan_fixup: seg_len must be a positive multiple of 2048 when n_segments > 1");
   const dim3 grid((unsigned)((rows + SPW - 1) / SPW), (unsigned)(args->n_segments > 1 ? args->n_segments : 1));
-  selscan_fixup_kernel<<<grid, SPW * 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(*args);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (fixup_vec_ok(*args)) {
+    if (a.dtype == B200_F32) selscan_fixup_vec_kernel<float><<<grid, SPW * 32, smem, st>>>(*args);
+    else if (a.dtype == B200_BF16) selscan_fixup_vec_kernel<__nv_bfloat16><<<grid, SPW * 32, smem, st>>>(*args);
+    else selscan_fixup_vec_kernel<__half><<<grid, SPW * 32, smem, st>>>(*args);
+  } else {
+    selscan_fixup_kernel<<<grid, SPW * 32, smem, st>>>(*args);
+  }
   return launch_status();
 }
