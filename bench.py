@@ -105,10 +105,10 @@ class ClockSampler:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
 # profiles/ (same workload, same kernel); None where no capture exists.
 NCU_TRAFFIC = {
-    ("s5_scan_cfg1", "simpscan_fwd_kernel"): 128.6e6,
-    ("s5_scan_cfg1", "simpscan_bwd_kernel"): 227.2e6,
-    ("s6_layer_cfg2", "selscan_fwd"): 216.5e6,
-    ("s6_layer_cfg2", "selscan_bwd"): 378.8e6,
+    ("s5_scan_cfg1", "simpscan_fwd_kernel"): 129.3e6,
+    ("s5_scan_cfg1", "simpscan_bwd_kernel"): 226.0e6,
+    ("s6_layer_cfg2", "selscan_fwd"): 219.9e6,
+    ("s6_layer_cfg2", "selscan_bwd"): 382.9e6,
 }
 
 
@@ -247,17 +247,17 @@ class S5Scan:
                 "simpscan_bwd_kernel": (self.bwd_bytes, statistics.mean(b))}
 
     # CPU arm: batch 1, first 1024 steps, same P and H (per-token work unchanged)
-    cpu_sample = "batch 2 of 8, all 4096 timesteps, P=256, H=512 (same work per token)"
+    cpu_sample = "the full workload: batch 8, 4096 timesteps, P=256, H=512"
 
     def cpu_step(self):
         from oracle import scan_oracle as O
         if not hasattr(self, "_cpu"):
-            self._cpu = self.host_inputs(batch=2)
+            self._cpu = self.host_inputs()
         h = self._cpu
         leaves = [h[k].clone().requires_grad_(True) for k in ("u", "delta", "A", "B", "C")]
         y = O.simplified_scan_oracle(*leaves, discretization="dirac")
         torch.autograd.grad(y, leaves, h["gout"])
-        return 2 * self.L
+        return self.batch * self.L
 
 
 class S6Scan:

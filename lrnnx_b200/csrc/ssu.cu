@@ -332,12 +332,16 @@ template <typename XT> __device__ __forceinline__ float lds_act(const unsigned c
 template <typename ST, typename XT, int LPR>
 __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, int tiles_per_bh) {
   using SL = TmaSlot<ST, XT, LPR>;
-  constexpr int VEC = SL::VEC, N = SL::N, RPP = TT / LPR, PASSES = TR / RPP;   // rows per pass
+  // a warp owns 16 consecutive rows of the tile through all three phases, so the phases are
+  // separated by warp barriers only; the one block barrier per tile precedes the bulk stores
+  constexpr int VEC = SL::VEC, N = SL::N, WROWS = TR / (TT / 32), RPP = 32 / LPR, PASSES = WROWS / RPP;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + SL::OFF_BAR);
   float *row_d = reinterpret_cast<float *>(smem + SL::OFF_ROW), *row_x = row_d + TR, *row_da = row_d + 2 * TR,
         *row_acc = row_d + 3 * TR;
-  const int tid = threadIdx.x, part = tid % LPR, r0 = tid / LPR;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, part = lane % LPR;
+  const int r0 = warp * WROWS + lane / LPR;         // first row of this lane group in phase B
+  const int rowA = warp * WROWS + lane;             // row of this lane in phases A and C (lanes < WROWS)
   const uint32_t ntiles = (uint32_t)p.batch * (uint32_t)p.nheads * (uint32_t)tiles_per_bh;   // < 2^31 (host check)
   const int my = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
   const int es = (int)sizeof(ST);
@@ -411,13 +415,13 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
     }
     if (!failed && !mbar_wait(&full[it % TNS], (uint32_t)(it / TNS) & 1u)) failed = true;
     // ---- phase A: per-row scalars
-    if (tid < TR) {
-      float d = lds_act<XT>(s + SL::OFF_DT, tid);
-      if (p.dt_bias) d += reinterpret_cast<const float *>(s + SL::OFF_BIAS)[tid];
+    if (lane < WROWS) {
+      float d = lds_act<XT>(s + SL::OFF_DT, rowA);
+      if (p.dt_bias) d += reinterpret_cast<const float *>(s + SL::OFF_BIAS)[rowA];
       if (p.dt_softplus) d = softplus20(d);
-      row_d[tid] = d;
-      row_x[tid] = lds_act<XT>(s + SL::OFF_X, tid);
-      row_da[tid] = p.deltaA ? lds_act<XT>(s + SL::OFF_DA, tid) : d;
+      row_d[rowA] = d;
+      row_x[rowA] = lds_act<XT>(s + SL::OFF_X, rowA);
+      row_da[rowA] = p.deltaA ? lds_act<XT>(s + SL::OFF_DA, rowA) : d;
     }
     float Bn[VEC], Cn[VEC];
 #pragma unroll
@@ -425,7 +429,7 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
       Bn[i] = lds_act<XT>(s + SL::OFF_B, part * VEC + i);
       Cn[i] = lds_act<XT>(s + SL::OFF_C, part * VEC + i);
     }
-    __syncthreads();
+    __syncwarp();
     // ---- phase B: state update
 #pragma unroll
     for (int j = 0; j < PASSES; ++j) {
@@ -453,16 +457,16 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
       for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (part == 0) row_acc[row] = acc;
     }
-    __syncthreads();
+    __syncwarp();
     // ---- phase C: outputs
-    if (tid < TR) {
-      float out = row_acc[tid];
-      if (p.D) out += reinterpret_cast<const float *>(s + SL::OFF_D)[tid] * row_x[tid];
+    if (lane < WROWS) {
+      float out = row_acc[rowA];
+      if (p.D) out += reinterpret_cast<const float *>(s + SL::OFF_D)[rowA] * row_x[rowA];
       if (p.z) {
-        const float zv = lds_act<XT>(s + SL::OFF_Z, tid);
+        const float zv = lds_act<XT>(s + SL::OFF_Z, rowA);
         out *= zv * sigmoidf_(zv);
       }
-      stt<XT>(s + SL::OFF_OUT, tid, out);
+      stt<XT>(s + SL::OFF_OUT, rowA, out);
     }
     fence_proxy_async();
     __syncthreads();

@@ -154,7 +154,7 @@ def _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, va
         # below one wave more segments simply mean more of the GPU in use; above, whole waves count.
         # Every extra segment also costs a fix-up pass over its first steps: demand a clear gain.
         eff = waves if waves <= 1.0 else waves / -(-waves // 1)
-        if eff > best_eff * 1.05 + 1e-9:
+        if eff > best_eff * 1.10 + 1e-9:
             best, best_eff = S, eff
     return best
 
