@@ -24,7 +24,7 @@ x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
              host cores on a bounded sample of the same workload.
 
 ``--impl reference`` times that CPU implementation alone (rank 0 only).
-Other workloads (``--workload``): s6_cfg0, s6_layer, s6_layer_f32, s6_long (sequence-parallel when N > 1), ssu_step.
+Other workloads (``--workload``): s6_cfg0, s6_layer, s6_layer_f32, s6_long (sequence-parallel when N > 1), ssu_step, cauchy.
 """
 from __future__ import annotations
 
@@ -474,6 +474,83 @@ class SsuStep:
         return self.batch * 2 / self.layers
 
 
+class CauchyKernel:
+    """S4 kernel generation: the symmetric Cauchy multiply at the shape of the reference's
+    micro-benchmark (benchmarks/benchmark_cauchy.py:49-51): 1024 rows, 32 conjugate-pair poles,
+    16384 frequencies, complex64, forward + backward.  A unit is one output element (row,
+    frequency).  The kernel is bound by the fp32 pipe (two complex reciprocals per
+    (row, frequency, pole)), not by HBM; the HBM fraction is reported for completeness."""
+    name = "cauchy_s4"
+    dtype = "c64"
+    metric, unit = "Cauchy output elements/s (fwd+bwd)", "elements/s"
+    launches_per_step = 3      # forward, backward partials, backward fold
+
+    def __init__(self, rows=1024, n=32, L=16384):
+        self.rows, self.n, self.L = rows, n, L
+        self.tokens = rows * L
+        self.fwd_bytes = 16 * rows * n + 8 * L + 8 * rows * L            # v, w, z read; out written
+        self.bwd_bytes = 16 * rows * n + 8 * L + 8 * rows * L + 16 * rows * n   # + dout read, dv, dw written
+        self.describe = {"workload": f"{self.name}: rows={rows} pole pairs={n} L={L} complex64 fwd+bwd",
+                         "l2": "a 256 MB write flushes the 126 MB L2 before every step"}
+
+    def host_inputs(self, rows=None, L=None):
+        g = torch.Generator().manual_seed(2357)
+        rows, L = rows or self.rows, L or self.L
+        return dict(v=cn(g, rows, self.n), w=cn(g, rows, self.n) - 1.0,
+                    z=torch.polar(torch.ones(L), torch.randn(L, generator=g)), gout=cn(g, rows, L))
+
+    def setup(self, dev, pg):
+        from lrnnx_b200 import structured_kernels
+        from lrnnx_b200.ops import cauchy_mult
+        self.dev, self.pg, self.ext, self.op = dev, pg, structured_kernels, cauchy_mult
+        self.h = {k: v.pin_memory() for k, v in self.host_inputs().items()}
+        self.t = {k: v.to(dev) for k, v in self.h.items()}
+        self.ev = []
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(self, record=False):
+        t = self.t
+        self.flush_buf.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            e[0].record()
+        self.ext.cauchy_mult_sym_fwd(t["v"], t["z"], t["w"])
+        if record:
+            e[1].record()
+        res = self.ext.cauchy_mult_sym_bwd(t["v"], t["z"], t["w"], t["gout"])
+        if record:
+            e[2].record()
+            self.ev.append(e)
+        return res
+
+    def e2e_step(self):
+        v, w = (self.t[k].copy_(self.h[k], non_blocking=True).detach().requires_grad_(True) for k in ("v", "w"))
+        z = self.t["z"].copy_(self.h["z"], non_blocking=True)
+        y = self.op(v, z, w)
+        torch.autograd.backward(y, self.t["gout"])
+        return float(torch.view_as_real(v.grad).sum().item())
+
+    def e2e_bytes(self):
+        return sum(self.h[k].numel() * 8 for k in ("v", "w", "z")), 4
+
+    def kernel_rooflines(self):
+        f = [a[0].elapsed_time(a[1]) for a in self.ev]
+        b = [a[1].elapsed_time(a[2]) for a in self.ev]
+        return {"cauchy_fwd": (self.fwd_bytes, statistics.mean(f)), "cauchy_bwd": (self.bwd_bytes, statistics.mean(b))}
+
+    cpu_sample = "64 of 1024 rows, all 16384 frequencies"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            self._cpu = self.host_inputs(rows=64)
+        h = self._cpu
+        v, w = (h[k].clone().requires_grad_(True) for k in ("v", "w"))
+        y = O.cauchy_oracle(v, h["z"], w, compute_dtype=torch.complex64)
+        torch.autograd.grad(y, [v, w], h["gout"])
+        return 64 * self.L
+
+
 def make_workload(name):
     if name in ("s5_scan", "s5_scan_cfg1", "default"):
         return S5Scan()
@@ -487,6 +564,8 @@ def make_workload(name):
         return S6Scan("s6_long_cfg3", 1, 5120, 131072, 16, torch.bfloat16, backward=False)
     if name in ("ssu_step", "ssu_step_cfg4"):
         return SsuStep()
+    if name in ("cauchy", "cauchy_s4"):
+        return CauchyKernel()
     raise SystemExit(f"unknown workload {name}")
 
 
