@@ -315,6 +315,37 @@ class S6Scan:
         self.t = {k: v.to(dev) for k, v in h.items()}
         self.ev = []
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
+        self.g_fwd = self.g_bwd = None
+        if not self.sp and self.L < 4 * 2048:      # (long rows run segmented: host-side stitching, not captured)
+            # the extension calls are captured once as CUDA graphs (after a warm-up on a side stream);
+            # a step replays them, so the timed region holds the kernels and not the Python launch path
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._call_fwd()
+                    if self.backward:
+                        self._call_bwd()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.g_fwd = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_fwd):
+                self._call_fwd()
+            if self.backward:
+                self.g_bwd = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.g_bwd):
+                    self._call_bwd()
+
+    def _call_fwd(self):
+        t = self.t
+        self.fwd_out = self.ext.fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"],
+                                    None, True, "mamba")
+
+    def _call_bwd(self):
+        t = self.t
+        out, x, _ = self.fwd_out
+        self.bwd_out = self.ext.bwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"], None,
+                                    t["gout"], x, out, None, True, False, "mamba")
 
     def step(self, record=False):
         t = self.t
@@ -323,6 +354,18 @@ class S6Scan:
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
+        if self.g_fwd is not None:
+            self.g_fwd.replay()
+            if record:
+                e[1].record()
+            if self.g_bwd is not None:
+                self.g_bwd.replay()
+            if record:
+                e[2].record()
+                self.ev.append(e)
+            if self.pg is not None and self.backward:
+                torch.distributed.all_reduce(self.bwd_out[2], group=self.pg)
+            return self.bwd_out if self.backward else None
         if self.sp:
             self.sp_fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"], True, self.pg)
             if record:

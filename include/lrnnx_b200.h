@@ -86,6 +86,12 @@ typedef struct b200_selscan_fwd_args {
   void *out;                                    /* (batch, dim, seqlen) */
   void *out_z;                                  /* required iff z != NULL */
   void *x;                                      /* required */
+  void *stage_h;                                /* nullable; no counterpart in the reference.  (batch, dim,
+                                                   ceil(seqlen/256), dstate) float32: the state at the end of
+                                                   every 256-step stage.  Written by the forward call and read
+                                                   by the backward call (which then skips its recomputation
+                                                   of these states) only where b200_selscan_stage_states()
+                                                   says so; ignored otherwise. */
   int64_t u_bs, u_ds;
   int64_t delta_bs, delta_ds;
   int64_t z_bs, z_ds;
@@ -98,6 +104,11 @@ typedef struct b200_selscan_fwd_args {
 } b200_selscan_fwd_args;
 
 int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream);
+
+/* 1 if b200_selscan_fwd with these arguments (stage_h aside) would write stage_h and
+ * b200_selscan_bwd on the same problem would read it, else 0: true on the shape class of the
+ * throughput kernels with l_segments <= 1. */
+int b200_selscan_stage_states(const b200_selscan_fwd_args *args);
 
 /* ------------------------------------------------------------------------
  * Selective scan backward (reverse scan with recomputation of the states).

@@ -20,6 +20,7 @@ LIB_PATH = _PKG / "lib" / "liblrnnx_b200.so"
 
 ENTRY_POINTS = (
     "b200_last_error", "b200_abi_version", "b200_sizeof", "b200_device_status", "b200_s4_bwd_scratch_bytes",
+    "b200_selscan_stage_states",
     "b200_selscan_fwd", "b200_selscan_bwd", "b200_selscan_fixup",
     "b200_simpscan_fwd", "b200_simpscan_bwd",
     "b200_ssu_step", "b200_s5_step",
@@ -111,7 +112,9 @@ def lib() -> ctypes.CDLL:
     handle.b200_device_status.argtypes = []
     handle.b200_s4_bwd_scratch_bytes.restype = ctypes.c_int64
     handle.b200_s4_bwd_scratch_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
-    for fn in ENTRY_POINTS[5:]:
+    handle.b200_selscan_stage_states.restype = ctypes.c_int
+    handle.b200_selscan_stage_states.argtypes = [ctypes.c_void_p]
+    for fn in ENTRY_POINTS[6:]:
         f = getattr(handle, fn)
         f.restype = ctypes.c_int
         f.argtypes = [ctypes.c_void_p, ctypes.c_void_p]

@@ -42,7 +42,7 @@ using namespace b200;
 extern "C" {
 
 const char *b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 2; }
+int b200_abi_version(void) { return 3; }
 
 // size of an argument block as this library was compiled; lets a binding
 // verify its own struct layout before the first call
@@ -68,6 +68,11 @@ int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream) {
   B200_REQUIRE(args->l_segments <= 1, B200_ERR_UNSUPPORTED,
                "selscan_fwd: l_segments > 1 is only available on the throughput-kernel shape class");
   return selscan_fwd_generic(*args, st);
+}
+
+int b200_selscan_stage_states(const b200_selscan_fwd_args *args) {
+  if (!args || check_selscan(*args)) return 0;
+  return (args->l_segments <= 1 && selscan_fwd_fast_supported(*args)) ? 1 : 0;
 }
 
 int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream) {

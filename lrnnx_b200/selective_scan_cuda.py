@@ -11,6 +11,8 @@ recurrence state is always fp32.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -159,6 +161,23 @@ def _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, va
     return best
 
 
+STAGE = 256   # steps per stage of the throughput kernels
+
+
+def _stage_numel(batch, dim, seqlen, dstate):
+    return batch * dim * (-(-seqlen // STAGE)) * dstate
+
+
+def _stage_states_of(x_, batch, dim, seqlen, dstate):
+    """Device address of the stage states behind the checkpoints of an x made by fwd(), else None."""
+    if x_ is None or x_.dtype != torch.float32 or x_.storage_offset() != 0 or not x_.is_contiguous():
+        return None
+    need = (x_.numel() + _stage_numel(batch, dim, seqlen, dstate)) * 4
+    if x_.untyped_storage().nbytes() != need:
+        return None
+    return x_.data_ptr() + x_.numel() * 4
+
+
 def _stitch_segments(a, x, S, seqlen, u):
     """Fold the zero-start summaries of the segments and run the fix-up kernel on segments >= 1."""
     n_chunks = x.shape[2]
@@ -196,6 +215,16 @@ def fwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, delta_softplus, discret
             a.out_z_bs, a.out_z_ds = out_z.stride(0), out_z.stride(1)
         S = _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C, deltaA_,
                           discretization_method_str)
+        if S <= 1 and _lib.lib().b200_selscan_stage_states(ctypes.byref(a)) == 1:
+            # The throughput kernels pass the state at every 256-step stage boundary from the forward
+            # to the backward call (which then skips recomputing them).  The states live behind the
+            # checkpoints in x's own allocation, so the reference's call signatures stay as they are;
+            # bwd() recognises the allocation by its size and falls back to recomputation for any other x.
+            x_numel = x.numel()
+            flat = torch.empty(x_numel + _stage_numel(batch, dim, seqlen, dstate), dtype=x.dtype, device=u.device)
+            x = flat[:x_numel].view(batch, dim, n_chunks, dstate * 2)
+            a.x = x.data_ptr()
+            a.stage_h = x.data_ptr() + x_numel * x.element_size()
         if S > 1:
             a.l_segments = S
             try:
@@ -258,6 +287,7 @@ def bwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, dout, x_, out_, dz_, de
         q = _lib.struct("b200_selscan_bwd_args")()
         f.delta_softplus = int(bool(delta_softplus))
         f.x = _ptr(x_)
+        f.stage_h = _stage_states_of(x_, batch, dim, seqlen, dstate)
         f.out = _ptr(out)
         if out is not None:
             f.out_bs, f.out_ds = out.stride(0), out.stride(1)

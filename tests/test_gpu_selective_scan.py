@@ -191,6 +191,30 @@ def test_throughput_kernel_checkpoints():
     assert_close(x.cpu()[..., 0::2], x_c[..., 0::2], rtol=1e-3, atol_scale=1e-6, name="x product")
 
 
+@pytest.mark.parametrize("dtype,L", [(torch.float32, 4360), (torch.bfloat16, 2048), (torch.bfloat16, 520)])
+def test_backward_with_and_without_saved_stage_states(dtype, L):
+    """The forward call of the throughput kernels leaves the state at every 256-step boundary
+    behind the checkpoints of x; the backward call uses them when it is handed that x and
+    recomputes them (its first sweep) when it is handed a copy.  Both must give the same gradients."""
+    from lrnnx_b200 import selective_scan_cuda as ext
+    t, g = _make_inputs(2, 16, 16, L, seed=31, dtype=dtype)
+    cu = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items()}
+    args = (cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], cu["z"], cu["delta_bias"], None)
+    out, x, out_z = ext.fwd(*args, True, "mamba")
+    assert ext._stage_states_of(x, 2, 16, L, 16) is not None
+    assert ext._stage_states_of(x.clone(), 2, 16, L, 16) is None
+    dout = torch.randn(out.shape, generator=g).to(dtype).cuda()
+    with_states = ext.bwd(*args, dout, x, out, None, True, False, "mamba")
+    recomputed = ext.bwd(*args, dout, x.clone(), out, None, True, False, "mamba")
+    f32 = dtype == torch.float32
+    for i, (a, b) in enumerate(zip(with_states, recomputed)):
+        if a is None:
+            assert b is None
+            continue
+        assert_close(a.float().cpu(), b.float().cpu(), rtol=2e-5 if f32 else 2e-2, atol_scale=2e-6 if f32 else 1e-2,
+                     name=f"gradient {i}")
+
+
 def test_long_row_segmented_forward_matches_oracle():
     """Few rows and a long sequence: the forward is cut into concurrently scanned segments and
     stitched (l_segments > 1 + fix-up); compare with the oracle and check the checkpoints."""
