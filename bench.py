@@ -172,15 +172,16 @@ class S5Scan:
         with torch.cuda.stream(side):
             for _ in range(2):
                 out, x = self.ext.fwd(*args, "dirac")
-                self.ext.bwd(*args, self.dBu_in, x, "dirac", need_dB_dC=False)
+                self.ext.bwd(*args, self.dBu_in, x, "dirac", need_dB_dC=False, out_=out)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.g_fwd, self.g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.g_fwd):
             self.out, self.x = self.ext.fwd(*args, "dirac")
         with torch.cuda.graph(self.g_bwd):
-            # as SimplifiedScanFn.backward calls it (identity B and C: dB / dC are not needed)
-            self.res = self.ext.bwd(*args, self.dBu_in, self.x, "dirac", need_dB_dC=False)
+            # as SimplifiedScanFn.backward calls it (identity B and C: dB / dC are not needed, and the
+            # forward output, which is the state sequence, is handed back)
+            self.res = self.ext.bwd(*args, self.dBu_in, self.x, "dirac", need_dB_dC=False, out_=self.out)
 
     def step(self, record=False):
         """forward + backward scan kernels through the extension entry points (graph replay)."""

@@ -183,7 +183,9 @@ typedef struct b200_simpscan_args {
   int32_t reserved0;
   const void *u, *delta, *A, *B, *C;
   const void *deltaA;              /* nullable */
-  void *out;                       /* fwd: output; bwd: unused */
+  void *out;                       /* fwd: output.  bwd: optional (nullable), the forward output for the
+                                      same arguments; with dstate == 1 and B C != 0 it is the state sequence
+                                      and the backward then skips the forward recomputation */
   void *x;                         /* fwd: written; bwd: read (may be NULL when seqlen <= 2048) */
   int64_t u_bs, u_ds, delta_bs, delta_ds, deltaA_bs, deltaA_ds, out_bs, out_ds;
   int64_t A_ds, A_ns, B_ds, B_ns, C_ds, C_ns;

@@ -721,6 +721,348 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
   if (failed) atomicExch(&g_simpscan_status, 2);
 }
 
+// --------------------------------------------- backward from the forward output (single state)
+// For single-state rows the forward output is the state sequence itself, out_t = h_t B C.  When
+// the caller hands it back (the autograd wrapper keeps it anyway), the backward needs no forward
+// recomputation at all: a_t h_{t-1} = h_t - beta_t, so only the reverse (adjoint) scan is left.
+// Without the checkpoints the tile size is free: 128-thread CTAs walk 1024-step tiles (four
+// CTAs per SM), each warp with its own 256-step slice pipeline; du and ddelta are written over
+// the u / delta slices in shared memory and leave through bulk stores.  8 bytes per element more
+// traffic than the recomputing kernel, a third fewer instructions.
+constexpr int HSL = 32 * BI;          // 256 timesteps per warp slice
+
+template <int HWARPS> struct __align__(16) BwdHShared {
+  cf rtot_q[2][HWARPS];     // per-warp aggregates of the reverse scan (double-buffered by tile parity)
+  cf rtot_g[2][HWARPS];
+  cf red[3][HWARPS];
+  cf gcar[2];               // q entering the tile from the later one (double-buffered)
+  uint64_t full_rw[2][HWARPS];   // u / delta slices (double-buffered: outputs are written over them)
+  uint64_t full_ro[HWARPS];      // dout / h slices (single: refilled as soon as they sit in registers)
+};
+
+template <int DM, bool HAS_DA, bool NEED_BC, int HT>
+__global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200_simpscan_args p) {
+  constexpr int HWARPS = HT / 32, HTILE = HT * BI;   // warps per CTA, timesteps per tile
+  constexpr int WU = HSL * 8, WD = HSL * 4;
+  constexpr int ROB = 2 * WU;                             // dout | h of one warp slice (read-only)
+  constexpr int RWB = WU + WD * (HAS_DA ? 2 : 1);         // u | delta (| deltaA): overwritten by du | ddelta (| ddeltaA)
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  BwdHShared<HWARPS> &sh = *reinterpret_cast<BwdHShared<HWARPS> *>(smem_raw + HWARPS * (ROB + 2 * RWB));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int L = p.seqlen;
+  const int n_tiles = (L + HTILE - 1) / HTILE;
+  const int64_t nrows = (int64_t)p.batch * p.dim;
+  const int my_rows = (int)((nrows - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  const int total = my_rows * n_tiles;
+
+  struct RowPtrs { const cf *u, *dout, *h; const float *d, *dA; cf *du; float *dd, *ddA; bool tma; };
+  auto row_ptrs = [&](int64_t row) {
+    const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+    RowPtrs r;
+    r.u = reinterpret_cast<const cf *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d * p.u_ds;
+    r.dout = reinterpret_cast<const cf *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
+    r.h = reinterpret_cast<const cf *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+    r.d = reinterpret_cast<const float *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+    r.dA = HAS_DA ? reinterpret_cast<const float *>(p.deltaA) + (int64_t)b * p.deltaA_bs + (int64_t)d * p.deltaA_ds
+                  : nullptr;
+    r.du = reinterpret_cast<cf *>(p.du) + (int64_t)b * p.du_bs + (int64_t)d * p.du_ds;
+    r.dd = reinterpret_cast<float *>(p.ddelta) + (int64_t)b * p.ddelta_bs + (int64_t)d * p.ddelta_ds;
+    r.ddA = HAS_DA ? reinterpret_cast<float *>(p.ddeltaA) + (int64_t)b * p.ddeltaA_bs + (int64_t)d * p.ddeltaA_ds
+                   : nullptr;
+    r.tma = ((reinterpret_cast<uintptr_t>(r.u) | reinterpret_cast<uintptr_t>(r.dout) | reinterpret_cast<uintptr_t>(r.h) |
+              reinterpret_cast<uintptr_t>(r.d) | reinterpret_cast<uintptr_t>(r.du) | reinterpret_cast<uintptr_t>(r.dd)) & 15) == 0;
+    if (HAS_DA) r.tma = r.tma && (((reinterpret_cast<uintptr_t>(r.dA) | reinterpret_cast<uintptr_t>(r.ddA)) & 15) == 0);
+    return r;
+  };
+  unsigned char *ro = smem_raw + (size_t)warp * ROB;
+  auto rwbuf = [&](int k) { return smem_raw + (size_t)HWARPS * ROB + (size_t)(k * HWARPS + warp) * RWB; };
+  // stream item f: row blockIdx.x + (f / n_tiles) * gridDim.x, tile n_tiles - 1 - f % n_tiles;
+  // `which` selects the read-only slices (1), the overwritten ones (2) or both (3)
+  auto issue = [&](int f, int which) {   // lane 0 of a warp
+    if (f >= total) return;
+    const int c = n_tiles - 1 - f % n_tiles;
+    if ((c + 1) * HTILE > L) return;
+    const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x);
+    if (!r.tma) return;
+    const int64_t t0 = (int64_t)c * HTILE + warp * HSL;
+    if (which & 1) {
+      uint64_t *bar = &sh.full_ro[warp];
+      mbar_expect_tx(bar, ROB);
+      bulk_g2s(ro, r.dout + t0, WU, bar);
+      bulk_g2s(ro + WU, r.h + t0, WU, bar);
+    }
+    if (which & 2) {
+      unsigned char *s = rwbuf(f & 1);
+      uint64_t *bar = &sh.full_rw[f & 1][warp];
+      mbar_expect_tx(bar, RWB);
+      bulk_g2s(s, r.u + t0, WU, bar);
+      bulk_g2s(s + WU, r.d + t0, WD, bar);
+      if (HAS_DA) bulk_g2s(s + WU + WD, r.dA + t0, WD, bar);
+    }
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < 2 * HWARPS; ++i) mbar_init(&sh.full_rw[0][0] + i, 1);
+    for (int i = 0; i < HWARPS; ++i) mbar_init(&sh.full_ro[i], 1);
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (lane == 0) issue(0, 3);
+
+  bool failed = false;
+  auto wait = [&](uint64_t *bar, uint32_t parity) {
+    if (!failed && !mbar_wait(bar, parity)) failed = true;
+  };
+  uint32_t full_phase = 0;   // bits 0, 1: the two overwritten buffers; bit 2: the read-only slices
+  bool stores_pending = false;
+  RowPtrs rp = row_ptrs(blockIdx.x);
+  int64_t row = blockIdx.x;
+  cf A0, Cc, inv_bc;
+  bool c_one = false, bc_one = false;
+  cf dA_acc, dB_acc, dC_acc;
+  for (int f = 0; f < total; ++f) {
+    const int j = f % n_tiles;
+    const int c = n_tiles - 1 - j;
+    if (j == 0) {   // new row
+      row = blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x;
+      rp = row_ptrs(row);
+      const int d = (int)(row % p.dim);
+      A0 = reinterpret_cast<const cf *>(p.A)[(int64_t)d * p.A_ds];
+      const cf B0 = reinterpret_cast<const cf *>(p.B)[(int64_t)d * p.B_ds];
+      const cf C0 = reinterpret_cast<const cf *>(p.C)[(int64_t)d * p.C_ds];
+      const cf bc = B0 * C0;
+      Cc = conj(C0);
+      c_one = C0.re == 1.f && C0.im == 0.f;
+      bc_one = bc.re == 1.f && bc.im == 0.f;
+      inv_bc = cf(1.f, 0.f) / bc;
+      dA_acc = dB_acc = dC_acc = cf(0.f, 0.f);
+    }
+    const int k = f & 1;
+    const int t0 = c * HTILE;                 // first step of the tile
+    const int tw = t0 + warp * HSL;           // first step of this warp's slice
+    const bool async_tile = rp.tma && (c + 1) * HTILE <= L;
+    unsigned char *s = rwbuf(k);
+    cf *su = reinterpret_cast<cf *>(s), *sdo = reinterpret_cast<cf *>(ro), *shh = reinterpret_cast<cf *>(ro + WU);
+    float *sd = reinterpret_cast<float *>(s + WU), *sdA = reinterpret_cast<float *>(s + WU + WD);
+    if (async_tile) {
+      wait(&sh.full_rw[k][warp], (full_phase >> k) & 1u);
+      wait(&sh.full_ro[warp], (full_phase >> 2) & 1u);
+      full_phase ^= (1u << k) | 4u;
+    } else {
+      for (int i = lane; i < HSL; i += 32) {
+        const int t = tw + i;
+        su[i] = t < L ? rp.u[t] : cf(0.f, 0.f);
+        sdo[i] = t < L ? rp.dout[t] : cf(0.f, 0.f);
+        shh[i] = t < L ? rp.h[t] : cf(0.f, 0.f);
+        sd[i] = t < L ? rp.d[t] : 0.f;
+        if (HAS_DA) sdA[i] = t < L ? rp.dA[t] : 0.f;
+      }
+      __syncwarp();
+    }
+    cf u[BI], dy[BI], h[BI];
+    float dl[BI], dAv[BI];
+    {
+      const float4 *s4 = reinterpret_cast<const float4 *>(su + lane * BI);
+      const float4 *o4 = reinterpret_cast<const float4 *>(sdo + lane * BI);
+      const float4 *h4 = reinterpret_cast<const float4 *>(shh + lane * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 2; ++q) {
+        const float4 v = s4[q], w = o4[q], x = h4[q];
+        u[2 * q] = cf(v.x, v.y);
+        u[2 * q + 1] = cf(v.z, v.w);
+        dy[2 * q] = cf(w.x, w.y);
+        dy[2 * q + 1] = cf(w.z, w.w);
+        h[2 * q] = cf(x.x, x.y);
+        h[2 * q + 1] = cf(x.z, x.w);
+      }
+      const float4 *d4 = reinterpret_cast<const float4 *>(sd + lane * BI);
+      const float4 *dA4 = reinterpret_cast<const float4 *>(sdA + lane * BI);
+#pragma unroll
+      for (int q = 0; q < BI / 4; ++q) {
+        const float4 v = d4[q];
+        dl[4 * q] = v.x; dl[4 * q + 1] = v.y; dl[4 * q + 2] = v.z; dl[4 * q + 3] = v.w;
+        if (HAS_DA) {
+          const float4 w = dA4[q];
+          dAv[4 * q] = w.x; dAv[4 * q + 1] = w.y; dAv[4 * q + 2] = w.z; dAv[4 * q + 3] = w.w;
+        }
+      }
+      if (!HAS_DA) {
+#pragma unroll
+        for (int i = 0; i < BI; ++i) dAv[i] = dl[i];
+      }
+    }
+    if (!bc_one) {
+#pragma unroll
+      for (int i = 0; i < BI; ++i) h[i] = h[i] * inv_bc;
+    }
+    // the state before this lane's first step (only the bilinear gradient needs h_{t-1} itself)
+    cf hprev0 = cf(0.f, 0.f);
+    if constexpr (DM == B200_DISC_BILINEAR) {
+      hprev0 = shfl_up(h[BI - 1], 1);
+      if (lane == 0) {
+        hprev0 = tw > 0 ? rp.h[tw - 1] : cf(0.f, 0.f);
+        if (!bc_one) hprev0 = hprev0 * inv_bc;
+      }
+    }
+    // the read-only slices sit in registers: refill them at once; the other overwritten buffer
+    // first has to be read out by the stores of the previous item
+    __syncwarp();
+    if (lane == 0) {
+      issue(f + 1, 1);
+      if (stores_pending) bulk_wait_read<0>();
+      issue(f + 1, 2);
+    }
+    bool same_step = true;
+#pragma unroll
+    for (int i = 1; i < BI; ++i) same_step = same_step && dl[i] == dl[0] && dAv[i] == dAv[0];
+    same_step = __all_sync(0xffffffffu, same_step);
+    constexpr bool kUnitK = (DM == B200_DISC_DIRAC);
+    cf a[BI], kk[kUnitK ? 1 : BI];
+    if (same_step) {
+      cf a0, k0;
+      s5_coef<DM>(A0, dl[0], dAv[0], a0, k0);
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        a[i] = a0;
+        if constexpr (!kUnitK) kk[i] = k0;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        if constexpr (kUnitK) a[i] = cexp(A0 * dAv[i]);
+        else s5_coef<DM>(A0, dl[i], dAv[i], a[i], kk[i]);
+      }
+    }
+    auto beta = [&](int i) { return kUnitK ? u[i] : kk[kUnitK ? 0 : i] * u[i]; };
+    auto seed = [&](int i) { return c_one ? dy[i] : dy[i] * Cc; };
+    // reverse scan of g_t = seed_t + conj(a_{t+1}) g_{t+1}, carried across threads as q_t = conj(a_t) g_t
+    cf gg = seed(BI - 1), Q = conj(a[BI - 1]);
+#pragma unroll
+    for (int i = BI - 2; i >= 0; --i) {
+      gg = conj(a[i + 1]) * gg + seed(i);
+      Q = Q * conj(a[i]);
+    }
+    gg = conj(a[0]) * gg;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const cf Qr = shfl_down(Q, off), gr = shfl_down(gg, off);
+      if (lane + off < 32) { gg = gg + Q * gr; Q = Q * Qr; }
+    }
+    const int par = f & 1;
+    if (lane == 0) { sh.rtot_q[par][warp] = Q; sh.rtot_g[par][warp] = gg; }
+    __syncthreads();   // the only block barrier of the tile
+    cf qpost = (j == 0) ? cf(0.f, 0.f) : sh.gcar[par];
+    for (int w = HWARPS - 1; w > warp; --w) qpost = sh.rtot_g[par][w] + sh.rtot_q[par][w] * qpost;
+    const cf g_right = shfl_down(gg, 1), Q_right = shfl_down(Q, 1);
+    cf qin = g_right + Q_right * qpost;
+    if (lane == 31) qin = qpost;
+    if (tid == 0) sh.gcar[par ^ 1] = gg + Q * qpost;
+    // adjoints and gradients
+    cf dA_l = cf(0.f, 0.f), dB_l = cf(0.f, 0.f), dC_l = cf(0.f, 0.f);
+    cf du[BI];
+    float ddl[BI], ddA[BI];
+    cf q = qin;
+#pragma unroll
+    for (int i = BI - 1; i >= 0; --i) {
+      const cf G = (i == BI - 1) ? seed(i) + q : conj(a[i == BI - 1 ? i : i + 1]) * q + seed(i);   // g_t
+      q = G;
+      const cf t = G * conj(h[i] - beta(i));   // g_t conj(a_t h_{t-1})
+      const float dv = dl[i], dav = dAv[i];
+      if constexpr (kUnitK) {
+        du[i] = G;
+        if (NEED_BC) dB_l = dB_l + G * conj(u[i]);
+      } else {
+        du[i] = G * conj(kk[kUnitK ? 0 : i]);
+        if (NEED_BC) dB_l = dB_l + G * conj(beta(i));
+      }
+      if (NEED_BC) dC_l = dC_l + dy[i] * conj(h[i]);
+      float d_dl = 0.f, d_dA = 0.f;
+      if constexpr (DM == B200_DISC_ZOH) {
+        const cf E = cexp(A0 * dv);
+        d_dA = (t * conj(A0)).re;
+        d_dl = (G * conj(E * u[i])).re;
+        dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / A0));
+      } else if constexpr (DM == B200_DISC_BILINEAR) {
+        const cf hprev = (i == 0) ? hprev0 : h[i == 0 ? 0 : i - 1];
+        const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - A0 * (0.5f * dv));
+        const cf rA = cf(1.f, 0.f) / (cf(1.f, 0.f) - A0 * (0.5f * dav));
+        const cf r2 = r * r, rA2 = rA * rA;
+        d_dA = (G * conj(hprev * A0 * rA2)).re;
+        d_dl = (G * conj(r2 * u[i])).re;
+        dA_l = dA_l + G * conj(hprev * rA2 * dav + r2 * u[i] * (0.5f * dv * dv));
+      } else {
+        d_dA = (t * conj(A0)).re;
+        dA_l = dA_l + t * dav;
+      }
+      if (HAS_DA) { ddl[i] = d_dl; ddA[i] = d_dA; }
+      else ddl[i] = d_dl + d_dA;
+    }
+    dA_acc = dA_acc + dA_l;
+    dB_acc = dB_acc + dB_l;
+    dC_acc = dC_acc + dC_l;
+    // ---- du / ddelta (/ ddeltaA): over the u / delta (/ deltaA) slices, then bulk stores
+    if (async_tile) {
+      float4 *s4 = reinterpret_cast<float4 *>(su + lane * BI);
+#pragma unroll
+      for (int qq = 0; qq < BI / 2; ++qq)
+        s4[qq] = make_float4(du[2 * qq].re, du[2 * qq].im, du[2 * qq + 1].re, du[2 * qq + 1].im);
+      float4 *d4 = reinterpret_cast<float4 *>(sd + lane * BI);
+#pragma unroll
+      for (int qq = 0; qq < BI / 4; ++qq) d4[qq] = make_float4(ddl[4 * qq], ddl[4 * qq + 1], ddl[4 * qq + 2], ddl[4 * qq + 3]);
+      if (HAS_DA) {
+        float4 *dA4 = reinterpret_cast<float4 *>(sdA + lane * BI);
+#pragma unroll
+        for (int qq = 0; qq < BI / 4; ++qq) dA4[qq] = make_float4(ddA[4 * qq], ddA[4 * qq + 1], ddA[4 * qq + 2], ddA[4 * qq + 3]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        bulk_s2g(rp.du + tw, su, WU);
+        bulk_s2g(rp.dd + tw, sd, WD);
+        if (HAS_DA) bulk_s2g(rp.ddA + tw, sdA, WD);
+        bulk_commit();
+      }
+      stores_pending = true;
+    } else {
+#pragma unroll
+      for (int i = 0; i < BI; ++i) {
+        const int t = tw + lane * BI + i;
+        if (t < L) {
+          rp.du[t] = du[i];
+          rp.dd[t] = ddl[i];
+          if (HAS_DA) rp.ddA[t] = ddA[i];
+        }
+      }
+      __syncwarp();   // the slice may be refilled by plain loads two items later
+    }
+    // ---- end of a row: fold the parameter gradients into dA / dB / dC
+    if (c == 0) {
+      const int d = (int)(row % p.dim);
+      cf *dAp = reinterpret_cast<cf *>(p.dA) + (int64_t)d * p.A_ds;
+      cf *dBp = NEED_BC ? reinterpret_cast<cf *>(p.dB) + (int64_t)d * p.B_ds : nullptr;
+      cf *dCp = NEED_BC ? reinterpret_cast<cf *>(p.dC) + (int64_t)d * p.C_ds : nullptr;
+      const cf ra = warp_sum(dA_acc);
+      cf rb, rc;
+      if (NEED_BC) { rb = warp_sum(dB_acc); rc = warp_sum(dC_acc); }
+      __syncthreads();   // sh.red is free (its readers of the previous row are done)
+      if (lane == 0) { sh.red[0][warp] = ra; sh.red[1][warp] = rb; sh.red[2][warp] = rc; }
+      __syncthreads();
+      if (tid < (NEED_BC ? 3 : 1)) {
+        cf acc = cf(0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < HWARPS; ++w) acc = acc + sh.red[tid][w];
+        cf *dst = tid == 0 ? dAp : (tid == 1 ? dBp : dCp);
+        atomicAdd(&dst->re, acc.re);
+        atomicAdd(&dst->im, acc.im);
+      }
+    }
+  }
+  if (lane == 0) bulk_wait<0>();
+  __syncthreads();
+  if (failed) atomicExch(&g_simpscan_status, 4);
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -767,7 +1109,27 @@ template <int DM, bool HAS_DA, bool S1, bool NEED_BC> int launch_bwd_s(const b20
   k<<<(unsigned)grid, BT, smem, st>>>(a);
   return launch_status();
 }
+template <int DM, bool HAS_DA, bool NEED_BC, int HT> int launch_bwd_h_t(const b200_simpscan_args &a, cudaStream_t st) {
+  constexpr int HWARPS = HT / 32;
+  constexpr int ROB = 2 * HSL * 8, RWB = HSL * 8 + HSL * 4 * (HAS_DA ? 2 : 1);
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = (size_t)HWARPS * (ROB + 2 * RWB) + sizeof(BwdHShared<HWARPS>);
+  auto k = simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT>;
+  if (int e = set_smem(k, smem)) return e;
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  per_sm = per_sm > 512 / HT ? 512 / HT : (per_sm < 1 ? 1 : per_sm);
+  int64_t grid = rows;
+  const int64_t resident = (int64_t)sm_count() * per_sm;
+  if (grid > resident) grid = resident;
+  k<<<(unsigned)grid, HT, smem, st>>>(a);
+  return launch_status();
+}
+template <int DM, bool HAS_DA, bool NEED_BC> int launch_bwd_h(const b200_simpscan_args &a, cudaStream_t st) {
+  return launch_bwd_h_t<DM, HAS_DA, NEED_BC, 128>(a, st);
+}
 template <int DM, bool HAS_DA> int launch_bwd(const b200_simpscan_args &a, cudaStream_t st) {
+  if (a.dstate == 1 && a.out)   // the forward output is the state sequence: no recomputation
+    return a.dB ? launch_bwd_h<DM, HAS_DA, true>(a, st) : launch_bwd_h<DM, HAS_DA, false>(a, st);
   if (a.dstate != 1) return launch_bwd_s<DM, HAS_DA, false, true>(a, st);
   return a.dB ? launch_bwd_s<DM, HAS_DA, true, true>(a, st) : launch_bwd_s<DM, HAS_DA, true, false>(a, st);
 }

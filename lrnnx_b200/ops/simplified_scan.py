@@ -55,7 +55,7 @@ class SimplifiedScanFn(torch.autograd.Function):
         if dx_out.stride(-1) != 1:
             dx_out = dx_out.contiguous()
         res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dx_out, xs, ctx.discretization,
-                                      need_dB_dC=False)
+                                      need_dB_dC=False, out_=out if out.stride(-1) == 1 else None)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du = torch.einsum("ph,bpl->bhl", B.conj(), dBu)
@@ -111,7 +111,7 @@ class S5InnerFn(torch.autograd.Function):
         if dscan.stride(-1) != 1:
             dscan = dscan.contiguous()
         res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dscan, xs, ctx.discretization,
-                                      need_dB_dC=False)
+                                      need_dB_dC=False, out_=scan_out if scan_out.stride(-1) == 1 else None)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du_scan = torch.einsum("ph,bpl->bhl", B.conj(), dBu)

@@ -73,10 +73,12 @@ def fwd(u, delta, A, B, C, deltaA_, discretization_method_str):
     return [out, x]
 
 
-def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str, need_dB_dC=True):
+def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str, need_dB_dC=True, out_=None):
     """Returns ``[du, ddelta, dA, dB, dC]`` plus ``ddeltaA`` when deltaA was given
-    (simplified_scan_cpu.cpp:328-330).  ``need_dB_dC=False`` (an addition to the reference
-    signature, single-state rows only) skips the dB / dC sums and returns None in their place."""
+    (simplified_scan_cpu.cpp:328-330).  Two additions to the reference signature, for single-state
+    rows: ``need_dB_dC=False`` skips the dB / dC sums and returns None in their place; ``out_``, the
+    output of ``fwd`` for the same arguments, lets the kernel take the states from it instead of
+    recomputing them (B C must be non-zero)."""
     a, (batch, dim, seqlen, dstate) = _common(u, delta, A, B, C, deltaA_, discretization_method_str)
     _check(dout.dtype == torch.complex64 and dout.is_cuda, "dout must be a complex64 CUDA tensor")
     _check(dout.stride(-1) == 1 or dout.size(-1) == 1, "dout must be contiguous in the last dimension")
@@ -100,6 +102,12 @@ def bwd(u, delta, A, B, C, deltaA_, dout, x_, discretization_method_str, need_dB
         _check(dA.stride() == A.stride() and dB.stride() == B.stride() and dC.stride() == C.stride(),
                "A, B, C must be dense")
         a.x = None if x_ is None else x_.data_ptr()
+        if out_ is not None and dstate == 1:
+            _check(out_.dtype == torch.complex64 and out_.is_cuda and tuple(out_.shape) == (batch, dim, seqlen),
+                   "out must be a complex64 CUDA tensor of shape (batch, dim, seqlen)")
+            _check(out_.stride(-1) == 1 or out_.size(-1) == 1, "out must be contiguous in the last dimension")
+            a.out = out_.data_ptr()
+            a.out_bs, a.out_ds = out_.stride(0), out_.stride(1)
         a.dout, a.du, a.ddelta = dout.data_ptr(), du.data_ptr(), ddelta.data_ptr()
         a.ddeltaA = None if ddeltaA is None else ddeltaA.data_ptr()
         a.dA = dA.data_ptr()

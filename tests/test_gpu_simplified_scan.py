@@ -77,16 +77,19 @@ def test_kernel_vs_oracle(disc, L, with_dA):
     gout = c(batch, P, L)
     names = [k for k in ("u", "delta", "A", "deltaA") if cpu[k] is not None]
     gc = torch.autograd.grad(out_c, [cpu[k] for k in names], gout, allow_unused=True)
-    res = simplified_scan_cuda.bwd(cu["u"], cu["delta"], cu["A"], one.cuda(), one.cuda(), cu["deltaA"], gout.cuda(),
-                                   x_g, disc)
-    got = dict(u=res[0], delta=res[1], A=res[2])
-    if with_dA:
-        got["deltaA"] = res[5]
-    for k, want in zip(names, gc):
-        if want is None:
-            assert float(got[k].abs().max()) == 0.0
-            continue
-        assert_close(got[k].cpu(), want, rtol=GRTOL, atol_scale=GATOL, name=f"d{k}")
+    # both backward kernels: the one that recomputes the states from the checkpoints, and the one
+    # that takes them from the forward output
+    for out_arg in (None, out_g):
+        res = simplified_scan_cuda.bwd(cu["u"], cu["delta"], cu["A"], one.cuda(), one.cuda(), cu["deltaA"],
+                                       gout.cuda(), x_g, disc, out_=out_arg)
+        got = dict(u=res[0], delta=res[1], A=res[2])
+        if with_dA:
+            got["deltaA"] = res[5]
+        for k, want in zip(names, gc):
+            if want is None:
+                assert float(got[k].abs().max()) == 0.0
+                continue
+            assert_close(got[k].cpu(), want, rtol=GRTOL, atol_scale=GATOL, name=f"d{k}")
 
 
 @pytest.mark.parametrize("disc", ["bilinear", "zoh", "dirac"])
@@ -111,9 +114,9 @@ def test_kernel_constant_step(disc, L, with_dA):
     gout = c(batch, P, L)
     names = [k for k in ("u", "delta", "A", "deltaA") if cpu[k] is not None]
     gc = torch.autograd.grad(out_c, [cpu[k] for k in names], gout, allow_unused=True)
-    for need in (True, False):
+    for need, out_arg in ((True, None), (False, None), (True, out_g), (False, out_g)):
         res = simplified_scan_cuda.bwd(cu["u"], cu["delta"], cu["A"], one.cuda(), one.cuda(), cu["deltaA"],
-                                       gout.cuda(), x_g, disc, need_dB_dC=need)
+                                       gout.cuda(), x_g, disc, need_dB_dC=need, out_=out_arg)
         assert (res[3] is None) == (not need) and (res[4] is None) == (not need)
         got = dict(u=res[0], delta=res[1], A=res[2])
         if with_dA:
