@@ -27,6 +27,8 @@
 // double-buffered bulk loads on per-warp mbarriers (a slice is refilled as
 // soon as the warp holds it in registers) and bulk stores from a per-warp
 // staging slice, so the one block barrier per chunk is the scan exchange.
+#include <cuda.h>   // CUtensorMap and its enums (types only: the encoder is looked up at run time)
+
 #include "common.cuh"
 #include "dispatch.h"
 
@@ -731,6 +733,29 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
 // traffic than the recomputing kernel, a third fewer instructions.
 constexpr int HSL = 32 * BI;          // 256 timesteps per warp slice
 
+// Tensor maps of the activation tensors viewed as rows of 128 bytes, with the 128-byte swizzle:
+// the TMA engine XORs the 16-byte chunk index of every row with the row index (mod 8) on the way
+// into shared memory, which spreads a lane's 64-byte (32-byte) run over all bank groups, so the
+// lane-blocked 128-bit shared loads and stores of a warp are conflict-free.  (With linear bulk
+// copies the 64-byte lane stride gives 4-way conflicts, and the shared-memory pipe, not the
+// issue slots, bounded this kernel.)
+struct TmaMaps {
+  CUtensorMap u, dout, h, d, dA, du, dd, ddA;
+};
+__device__ __forceinline__ int swz128(int byte_off) { return byte_off ^ (((byte_off >> 7) & 7) << 4); }
+__device__ __forceinline__ void tensor_g2s(void *dst, const CUtensorMap *map, int row, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tensor_s2g(const CUtensorMap *map, int row, const void *src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(0), "r"(row), "r"(smem_u32(src))
+               : "memory");
+}
+
 template <int HWARPS> struct __align__(16) BwdHShared {
   cf rtot_q[2][HWARPS];     // per-warp aggregates of the reverse scan (double-buffered by tile parity)
   cf rtot_g[2][HWARPS];
@@ -740,13 +765,16 @@ template <int HWARPS> struct __align__(16) BwdHShared {
   uint64_t full_ro[HWARPS];      // dout / h slices (single: refilled as soon as they sit in registers)
 };
 
-template <int DM, bool HAS_DA, bool NEED_BC, int HT>
-__global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200_simpscan_args p) {
+template <int DM, bool HAS_DA, bool NEED_BC, int HT, bool SWZ>
+__global__ void __launch_bounds__(HT, 512 / HT)
+simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps maps) {
   constexpr int HWARPS = HT / 32, HTILE = HT * BI;   // warps per CTA, timesteps per tile
   constexpr int WU = HSL * 8, WD = HSL * 4;
   constexpr int ROB = 2 * WU;                             // dout | h of one warp slice (read-only)
   constexpr int RWB = WU + WD * (HAS_DA ? 2 : 1);         // u | delta (| deltaA): overwritten by du | ddelta (| ddeltaA)
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_dyn[];
+  // the swizzle pattern repeats every 1024 bytes: slices start on 1024-byte boundaries
+  unsigned char *smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   BwdHShared<HWARPS> &sh = *reinterpret_cast<BwdHShared<HWARPS> *>(smem_raw + HWARPS * (ROB + 2 * RWB));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int L = p.seqlen;
@@ -785,19 +813,33 @@ __global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200
     const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x);
     if (!r.tma) return;
     const int64_t t0 = (int64_t)c * HTILE + warp * HSL;
+    // row of 128 bytes at which the slice starts in a contiguous (batch, dim, seqlen) tensor
+    const int64_t e0 = (blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x) * L + t0;
+    const int rc = (int)(e0 / 16), rf = (int)(e0 / 32);   // complex64 / float32 tensors
     if (which & 1) {
       uint64_t *bar = &sh.full_ro[warp];
       mbar_expect_tx(bar, ROB);
-      bulk_g2s(ro, r.dout + t0, WU, bar);
-      bulk_g2s(ro + WU, r.h + t0, WU, bar);
+      if (SWZ) {
+        tensor_g2s(ro, &maps.dout, rc, bar);
+        tensor_g2s(ro + WU, &maps.h, rc, bar);
+      } else {
+        bulk_g2s(ro, r.dout + t0, WU, bar);
+        bulk_g2s(ro + WU, r.h + t0, WU, bar);
+      }
     }
     if (which & 2) {
       unsigned char *s = rwbuf(f & 1);
       uint64_t *bar = &sh.full_rw[f & 1][warp];
       mbar_expect_tx(bar, RWB);
-      bulk_g2s(s, r.u + t0, WU, bar);
-      bulk_g2s(s + WU, r.d + t0, WD, bar);
-      if (HAS_DA) bulk_g2s(s + WU + WD, r.dA + t0, WD, bar);
+      if (SWZ) {
+        tensor_g2s(s, &maps.u, rc, bar);
+        tensor_g2s(s + WU, &maps.d, rf, bar);
+        if (HAS_DA) tensor_g2s(s + WU + WD, &maps.dA, rf, bar);
+      } else {
+        bulk_g2s(s, r.u + t0, WU, bar);
+        bulk_g2s(s + WU, r.d + t0, WD, bar);
+        if (HAS_DA) bulk_g2s(s + WU + WD, r.dA + t0, WD, bar);
+      }
     }
   };
 
@@ -812,7 +854,7 @@ __global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200
 
   bool failed = false;
   auto wait = [&](uint64_t *bar, uint32_t parity) {
-    if (!failed && !mbar_wait(bar, parity)) failed = true;
+    if (!failed && !mbar_wait(bar, parity, 1u << 21)) failed = true;
   };
   uint32_t full_phase = 0;   // bits 0, 1: the two overwritten buffers; bit 2: the read-only slices
   bool stores_pending = false;
@@ -862,13 +904,18 @@ __global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200
     }
     cf u[BI], dy[BI], h[BI];
     float dl[BI], dAv[BI];
+    const bool sw = SWZ && async_tile;      // swizzled (tensor copy) or linear (plain loads) slice layout
+    auto off_c = [&](int q) { const int o = lane * 64 + q * 16; return sw ? swz128(o) : o; };   // complex slices
+    auto off_f = [&](int q) { const int o = lane * 32 + q * 16; return sw ? swz128(o) : o; };   // float slices
     {
-      const float4 *s4 = reinterpret_cast<const float4 *>(su + lane * BI);
-      const float4 *o4 = reinterpret_cast<const float4 *>(sdo + lane * BI);
-      const float4 *h4 = reinterpret_cast<const float4 *>(shh + lane * BI);
+      const unsigned char *s4 = reinterpret_cast<const unsigned char *>(su);
+      const unsigned char *o4 = reinterpret_cast<const unsigned char *>(sdo);
+      const unsigned char *h4 = reinterpret_cast<const unsigned char *>(shh);
 #pragma unroll
       for (int q = 0; q < BI / 2; ++q) {
-        const float4 v = s4[q], w = o4[q], x = h4[q];
+        const int o = off_c(q);
+        const float4 v = *reinterpret_cast<const float4 *>(s4 + o), w = *reinterpret_cast<const float4 *>(o4 + o),
+                     x = *reinterpret_cast<const float4 *>(h4 + o);
         u[2 * q] = cf(v.x, v.y);
         u[2 * q + 1] = cf(v.z, v.w);
         dy[2 * q] = cf(w.x, w.y);
@@ -876,14 +923,15 @@ __global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200
         h[2 * q] = cf(x.x, x.y);
         h[2 * q + 1] = cf(x.z, x.w);
       }
-      const float4 *d4 = reinterpret_cast<const float4 *>(sd + lane * BI);
-      const float4 *dA4 = reinterpret_cast<const float4 *>(sdA + lane * BI);
+      const unsigned char *d4 = reinterpret_cast<const unsigned char *>(sd);
+      const unsigned char *dA4 = reinterpret_cast<const unsigned char *>(sdA);
 #pragma unroll
       for (int q = 0; q < BI / 4; ++q) {
-        const float4 v = d4[q];
+        const int o = off_f(q);
+        const float4 v = *reinterpret_cast<const float4 *>(d4 + o);
         dl[4 * q] = v.x; dl[4 * q + 1] = v.y; dl[4 * q + 2] = v.z; dl[4 * q + 3] = v.w;
         if (HAS_DA) {
-          const float4 w = dA4[q];
+          const float4 w = *reinterpret_cast<const float4 *>(dA4 + o);
           dAv[4 * q] = w.x; dAv[4 * q + 1] = w.y; dAv[4 * q + 2] = w.z; dAv[4 * q + 3] = w.w;
         }
       }
@@ -1003,24 +1051,34 @@ __global__ void __launch_bounds__(HT, 512 / HT) simpscan_bwd_h_kernel(const b200
     dC_acc = dC_acc + dC_l;
     // ---- du / ddelta (/ ddeltaA): over the u / delta (/ deltaA) slices, then bulk stores
     if (async_tile) {
-      float4 *s4 = reinterpret_cast<float4 *>(su + lane * BI);
+      unsigned char *s4 = reinterpret_cast<unsigned char *>(su);
 #pragma unroll
       for (int qq = 0; qq < BI / 2; ++qq)
-        s4[qq] = make_float4(du[2 * qq].re, du[2 * qq].im, du[2 * qq + 1].re, du[2 * qq + 1].im);
-      float4 *d4 = reinterpret_cast<float4 *>(sd + lane * BI);
+        *reinterpret_cast<float4 *>(s4 + off_c(qq)) =
+            make_float4(du[2 * qq].re, du[2 * qq].im, du[2 * qq + 1].re, du[2 * qq + 1].im);
+      unsigned char *d4 = reinterpret_cast<unsigned char *>(sd);
 #pragma unroll
-      for (int qq = 0; qq < BI / 4; ++qq) d4[qq] = make_float4(ddl[4 * qq], ddl[4 * qq + 1], ddl[4 * qq + 2], ddl[4 * qq + 3]);
+      for (int qq = 0; qq < BI / 4; ++qq)
+        *reinterpret_cast<float4 *>(d4 + off_f(qq)) = make_float4(ddl[4 * qq], ddl[4 * qq + 1], ddl[4 * qq + 2], ddl[4 * qq + 3]);
       if (HAS_DA) {
-        float4 *dA4 = reinterpret_cast<float4 *>(sdA + lane * BI);
+        unsigned char *dA4 = reinterpret_cast<unsigned char *>(sdA);
 #pragma unroll
-        for (int qq = 0; qq < BI / 4; ++qq) dA4[qq] = make_float4(ddA[4 * qq], ddA[4 * qq + 1], ddA[4 * qq + 2], ddA[4 * qq + 3]);
+        for (int qq = 0; qq < BI / 4; ++qq)
+          *reinterpret_cast<float4 *>(dA4 + off_f(qq)) = make_float4(ddA[4 * qq], ddA[4 * qq + 1], ddA[4 * qq + 2], ddA[4 * qq + 3]);
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        bulk_s2g(rp.du + tw, su, WU);
-        bulk_s2g(rp.dd + tw, sd, WD);
-        if (HAS_DA) bulk_s2g(rp.ddA + tw, sdA, WD);
+        if (SWZ) {
+          const int64_t e0 = row * L + tw;
+          tensor_s2g(&maps.du, (int)(e0 / 16), su);
+          tensor_s2g(&maps.dd, (int)(e0 / 32), sd);
+          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 / 32), sdA);
+        } else {
+          bulk_s2g(rp.du + tw, su, WU);
+          bulk_s2g(rp.dd + tw, sd, WD);
+          if (HAS_DA) bulk_s2g(rp.ddA + tw, sdA, WD);
+        }
         bulk_commit();
       }
       stores_pending = true;
@@ -1109,19 +1167,67 @@ template <int DM, bool HAS_DA, bool S1, bool NEED_BC> int launch_bwd_s(const b20
   k<<<(unsigned)grid, BT, smem, st>>>(a);
   return launch_status();
 }
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    tried = true;
+  }
+  return fn;
+}
+// A contiguous tensor of `bytes` bytes as rows of 128 bytes (32 floats), boxes of `box_rows` rows, 128-byte swizzle.
+bool make_row_map(CUtensorMap *m, const void *base, uint64_t bytes, uint32_t box_rows) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc || !base) return false;
+  const cuuint64_t dims[2] = {32, bytes / 128};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {32, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int DM, bool HAS_DA, bool NEED_BC, int HT> int launch_bwd_h_t(const b200_simpscan_args &a, cudaStream_t st) {
   constexpr int HWARPS = HT / 32;
   constexpr int ROB = 2 * HSL * 8, RWB = HSL * 8 + HSL * 4 * (HAS_DA ? 2 : 1);
   const int64_t rows = (int64_t)a.batch * a.dim;
-  const size_t smem = (size_t)HWARPS * (ROB + 2 * RWB) + sizeof(BwdHShared<HWARPS>);
-  auto k = simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT>;
+  const size_t smem = (size_t)HWARPS * (ROB + 2 * RWB) + sizeof(BwdHShared<HWARPS>) + 1024;
+  // swizzled tensor copies need contiguous (batch, dim, seqlen) tensors made of whole 128-byte rows
+  const int64_t L = a.seqlen, DL = (int64_t)a.dim * L;
+  auto dense = [&](int64_t bs, int64_t ds) { return ds == L && bs == DL; };
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  bool swz = L % 32 == 0 && rows * L / 16 < (int64_t(1) << 31) && dense(a.u_bs, a.u_ds) && dense(a.dout_bs, a.dout_ds) &&
+             dense(a.out_bs, a.out_ds) && dense(a.delta_bs, a.delta_ds) && dense(a.du_bs, a.du_ds) &&
+             dense(a.ddelta_bs, a.ddelta_ds) && al16(a.u) && al16(a.dout) && al16(a.out) && al16(a.delta) && al16(a.du) &&
+             al16(a.ddelta);
+  if (HAS_DA) swz = swz && dense(a.deltaA_bs, a.deltaA_ds) && dense(a.ddeltaA_bs, a.ddeltaA_ds) && al16(a.deltaA) && al16(a.ddeltaA);
+  TmaMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (swz) {
+    const uint64_t cb = (uint64_t)rows * L * 8, fb = (uint64_t)rows * L * 4;
+    swz = make_row_map(&maps.u, a.u, cb, 16) && make_row_map(&maps.dout, a.dout, cb, 16) &&
+          make_row_map(&maps.h, a.out, cb, 16) && make_row_map(&maps.d, a.delta, fb, 8) &&
+          make_row_map(&maps.du, a.du, cb, 16) && make_row_map(&maps.dd, a.ddelta, fb, 8);
+    if (HAS_DA) swz = swz && make_row_map(&maps.dA, a.deltaA, fb, 8) && make_row_map(&maps.ddA, a.ddeltaA, fb, 8);
+  }
+  auto k = swz ? simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT, true> : simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT, false>;
   if (int e = set_smem(k, smem)) return e;
   int per_sm = (int)((227 * 1024) / (smem + 1024));
   per_sm = per_sm > 512 / HT ? 512 / HT : (per_sm < 1 ? 1 : per_sm);
   int64_t grid = rows;
   const int64_t resident = (int64_t)sm_count() * per_sm;
   if (grid > resident) grid = resident;
-  k<<<(unsigned)grid, HT, smem, st>>>(a);
+  k<<<(unsigned)grid, HT, smem, st>>>(a, maps);
   return launch_status();
 }
 template <int DM, bool HAS_DA, bool NEED_BC> int launch_bwd_h(const b200_simpscan_args &a, cudaStream_t st) {

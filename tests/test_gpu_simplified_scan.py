@@ -57,10 +57,12 @@ def _kernel_inputs(batch, P, L, S, seed, with_dA):
 
 @pytest.mark.parametrize("disc", ["bilinear", "zoh", "dirac"])
 @pytest.mark.parametrize("L,with_dA", [(1, False), (7, True), (320, False), (321, True), (1000, False),
-                                       (2048, False), (2050, True), (4096, False), (4097, False), (6403, False)])
+                                       (2048, False), (2050, True), (3072, True), (4096, False), (4097, False),
+                                       (6403, False)])
 def test_kernel_vs_oracle(disc, L, with_dA):
     """fwd/bwd of the raw kernel entry points (identity B/C, dstate 1) against the oracle; ragged
-    lengths exercise the 320-step stage, the 2048-step chunk and the unaligned (plain-load) paths."""
+    lengths exercise the 320-step stage, the 2048-step chunk and the unaligned (plain-load) paths;
+    lengths that are multiples of 32 take the swizzled tensor-copy path of the backward."""
     from lrnnx_b200 import simplified_scan_cuda
     batch, P, S = 2, 5, 1
     t, g, c = _kernel_inputs(batch, P, L, S, seed=L, with_dA=with_dA)
