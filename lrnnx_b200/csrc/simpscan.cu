@@ -112,19 +112,23 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
   auto slot_dA = [&](int k) {
     return reinterpret_cast<float *>(wbase + (size_t)k * SLOT_BYTES + F_U_BYTES + F_D_BYTES);
   };
-  // stage f of the stream: bulk (TMA) copies when the row is 16-byte aligned and the stage is full
+  // stage f of the stream: bulk (TMA) copies when the row is 16-byte aligned and the stage is
+  // full, or is the last one of a row whose length is a multiple of 4 (the copies then cover the
+  // valid part only and the lanes past it substitute the neutral operands in registers)
+  const bool partial_ok = (L % 4) == 0;
   auto issue = [&](int f) {   // lane 0 only
     if (f >= total) return;
     const int s = f % nst;
-    if ((s + 1) * FSTAGE > L) return;
+    const int valid = min(FSTAGE, L - s * FSTAGE);
+    if (valid < FSTAGE && !partial_ok) return;
     const RowPtrs r = row_ptrs(gw + (int64_t)(f / nst) * W);
     if (!r.tma) return;
     const int k = f % FNS;
     const int64_t t0 = (int64_t)s * FSTAGE;
-    mbar_expect_tx(&bars[k], SLOT_BYTES);
-    bulk_g2s(slot_u(k), r.u + t0, F_U_BYTES, &bars[k]);
-    bulk_g2s(slot_d(k), r.d + t0, F_D_BYTES, &bars[k]);
-    if (HAS_DA) bulk_g2s(slot_dA(k), r.dA + t0, F_D_BYTES, &bars[k]);
+    mbar_expect_tx(&bars[k], valid * (8 + (HAS_DA ? 8 : 4)));
+    bulk_g2s(slot_u(k), r.u + t0, valid * 8, &bars[k]);
+    bulk_g2s(slot_d(k), r.d + t0, valid * 4, &bars[k]);
+    if (HAS_DA) bulk_g2s(slot_dA(k), r.dA + t0, valid * 4, &bars[k]);
   };
   if (lane == 0) { issue(0); issue(1); }
 
@@ -154,7 +158,8 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
     }
     const int k = f % FNS;
     const int t0 = s * FSTAGE;
-    const bool async_stage = rp.tma && (s + 1) * FSTAGE <= L;
+    const int valid = min(FSTAGE, L - t0);
+    const bool async_stage = rp.tma && (valid == FSTAGE || partial_ok);
     cf *su = slot_u(k);
     float *sd = slot_d(k), *sdA = slot_dA(k);
     if (async_stage) {
@@ -198,6 +203,12 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
           dAv[2 * j] = v.x;
           dAv[2 * j + 1] = v.y;
         }
+      }
+    }
+    if (valid < FSTAGE && async_stage) {   // partial bulk copy: the slot's tail holds stale data
+#pragma unroll
+      for (int i = 0; i < FI; ++i) {
+        if (lane * FI + i >= valid) { u[i] = cf(0.f, 0.f); dl[i] = 0.f; dAv[i] = 0.f; }
       }
     }
     cf out[FI];
@@ -306,7 +317,7 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        bulk_s2g(rp.o + t0, su, F_U_BYTES);
+        bulk_s2g(rp.o + t0, su, valid * 8);
         bulk_commit();
       }
     } else {
