@@ -316,6 +316,7 @@ class S6Scan:
         self.t = {k: v.to(dev) for k, v in h.items()}
         self.ev = []
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
+        self.copy_stream = torch.cuda.Stream(device=dev)
         self.g_fwd = self.g_bwd = None
         if not self.sp and self.L < 4 * 2048:      # (long rows run segmented: host-side stitching, not captured)
             # the extension calls are captured once as CUDA graphs (after a warm-up on a side stream);
@@ -390,6 +391,8 @@ class S6Scan:
         return res
 
     def e2e_step(self):
+        if not self.sp and self.batch % 4 == 0:
+            return self.e2e_step_micro(4)
         t = {k: (self.t[k].copy_(self.h[k], non_blocking=True)) for k in ("u", "delta", "B", "C", "z")}
         if self.sp:
             y, _ = self.sp_fwd(t["u"], t["delta"], self.t["A"], t["B"], t["C"], self.t["D"], t["z"],
@@ -403,6 +406,36 @@ class S6Scan:
         if self.backward:
             loss.backward()
         return float(loss.item())
+
+    def e2e_step_micro(self, n):
+        """The same step with the batch cut into n micro-batches: the copies of micro-batch i+1
+        (copy stream) overlap the compute of micro-batch i; parameter gradients accumulate."""
+        cur = torch.cuda.current_stream()
+        mb = self.batch // n
+        names = ("u", "delta", "B", "C", "z")
+        self.copy_stream.wait_stream(cur)
+        evs = []
+        with torch.cuda.stream(self.copy_stream):
+            for i in range(n):
+                sl = slice(i * mb, (i + 1) * mb)
+                for k in names:
+                    self.t[k][sl].copy_(self.h[k][sl], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+                evs.append(ev)
+        A, D, bias = (self.t[k].detach().requires_grad_(self.backward) for k in ("A", "D", "delta_bias"))
+        total = torch.zeros((), device=self.dev)
+        for i in range(n):
+            sl = slice(i * mb, (i + 1) * mb)
+            cur.wait_event(evs[i])
+            lv = {k: self.t[k][sl].detach().requires_grad_(self.backward) for k in names}
+            y = self.op(lv["u"], lv["delta"], A, lv["B"], lv["C"], D, lv["z"], bias, delta_softplus=True,
+                        discretization="mamba")
+            loss = (y.float() * self.t["gout"][sl].float()).sum()
+            if self.backward:
+                loss.backward()
+            total += loss.detach()
+        return float(total.item())
 
     def e2e_bytes(self):
         return sum(self.h[k].numel() * self.h[k].element_size() for k in ("u", "delta", "B", "C", "z")), 4
