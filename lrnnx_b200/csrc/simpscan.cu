@@ -334,6 +334,29 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
 }
 
 // ----------------------------------------------------------------- backward
+// Tensor maps of the activation tensors viewed as rows of 128 bytes, with the 128-byte swizzle:
+// the TMA engine XORs the 16-byte chunk index of every row with the row index (mod 8) on the way
+// into shared memory, which spreads a lane's 64-byte (32-byte) run over all bank groups, so the
+// lane-blocked 128-bit shared loads and stores of a warp are conflict-free.  (With linear bulk
+// copies the 64-byte lane stride gives 4-way conflicts, and the shared-memory pipe, not the
+// issue slots, bounded this kernel.)
+struct TmaMaps {
+  CUtensorMap u, dout, h, d, dA, du, dd, ddA;
+};
+__device__ __forceinline__ int swz128(int byte_off) { return byte_off ^ (((byte_off >> 7) & 7) << 4); }
+__device__ __forceinline__ void tensor_g2s(void *dst, const CUtensorMap *map, int row, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tensor_s2g(const CUtensorMap *map, int row, const void *src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(0), "r"(row), "r"(smem_u32(src))
+               : "memory");
+}
+
 constexpr int BT = 256;               // threads per CTA
 constexpr int BI = 8;                 // timesteps per thread (BT*BI = 2048 = one checkpoint chunk)
 constexpr int BWARPS = BT / 32;
@@ -351,12 +374,15 @@ struct __align__(16) BwdShared {
 
 // NEED_BC = false skips dB / dC (the host passes null pointers: the caller scans B u with
 // identity B and C and has no use for them).
-template <int DM, bool HAS_DA, bool S1, bool NEED_BC>
-__global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan_args p) {
+template <int DM, bool HAS_DA, bool S1, bool NEED_BC, bool SWZ>
+__global__ void __launch_bounds__(BT, 2)
+simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps maps) {
   constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);   // u, dout, delta (, deltaA)
   constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);       // du, ddelta (, ddeltaA)
   constexpr int SL = 32 * BI;                       // timesteps per warp slice
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_dyn[];
+  // the swizzle pattern of the tensor copies repeats every 1024 bytes: slices start on such boundaries
+  unsigned char *smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   // layout: buf[2] | out staging | BwdShared | per-state: gcar[2], accA, accB, accC (cf each)
   unsigned char *out_stage = smem_raw + 2 * (size_t)BUF_BYTES;
   BwdShared &sh = *reinterpret_cast<BwdShared *>(out_stage + OUT_BYTES);
@@ -409,10 +435,19 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
     const int64_t t0 = (int64_t)c * kChunk + warp * SL;
     uint64_t *bar = &sh.full[k][warp];
     mbar_expect_tx(bar, BUF_BYTES / BWARPS);
-    bulk_g2s(buf_u(k) + warp * SL, r.u + t0, B_U_BYTES / BWARPS, bar);
-    bulk_g2s(buf_do(k) + warp * SL, r.dout + t0, B_U_BYTES / BWARPS, bar);
-    bulk_g2s(buf_d(k) + warp * SL, r.d + t0, B_D_BYTES / BWARPS, bar);
-    if (HAS_DA) bulk_g2s(buf_dA(k) + warp * SL, r.dA + t0, B_D_BYTES / BWARPS, bar);
+    if (SWZ) {   // rows of 128 bytes of the contiguous (batch, dim, seqlen) tensors
+      const int64_t e0 = (blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x) * L + t0;
+      const int rc = (int)(e0 / 16), rf = (int)(e0 / 32);
+      tensor_g2s(buf_u(k) + warp * SL, &maps.u, rc, bar);
+      tensor_g2s(buf_do(k) + warp * SL, &maps.dout, rc, bar);
+      tensor_g2s(buf_d(k) + warp * SL, &maps.d, rf, bar);
+      if (HAS_DA) tensor_g2s(buf_dA(k) + warp * SL, &maps.dA, rf, bar);
+    } else {
+      bulk_g2s(buf_u(k) + warp * SL, r.u + t0, B_U_BYTES / BWARPS, bar);
+      bulk_g2s(buf_do(k) + warp * SL, r.dout + t0, B_U_BYTES / BWARPS, bar);
+      bulk_g2s(buf_d(k) + warp * SL, r.d + t0, B_D_BYTES / BWARPS, bar);
+      if (HAS_DA) bulk_g2s(buf_dA(k) + warp * SL, r.dA + t0, B_D_BYTES / BWARPS, bar);
+    }
   };
 
   if (tid == 0) {
@@ -428,7 +463,7 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
   // block barriers, so the CTA always terminates.
   bool failed = false;
   auto wait = [&](uint64_t *bar, uint32_t parity) {
-    if (!failed && !mbar_wait(bar, parity)) failed = true;
+    if (!failed && !mbar_wait(bar, parity, 1u << 21)) failed = true;
   };
   uint32_t full_phase = 0;
   uint32_t iter = 0;          // (chunk, state) iterations so far: parity of the exchange arrays
@@ -479,25 +514,31 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
 
     cf u[BI], dy[BI];
     float dl[BI], dAv[BI];
+    // slice layout: swizzled by the tensor copies, linear after plain loads
+    const bool sw = SWZ && async_chunk;
+    auto off_c = [&](int q) { const int o = lane * 64 + q * 16; return sw ? swz128(o) : o; };   // complex slices
+    auto off_f = [&](int q) { const int o = lane * 32 + q * 16; return sw ? swz128(o) : o; };   // float slices
     {
-      const float4 *s4 = reinterpret_cast<const float4 *>(su + tid * BI);
-      const float4 *o4 = reinterpret_cast<const float4 *>(sdo + tid * BI);
+      const unsigned char *s4 = reinterpret_cast<const unsigned char *>(su + warp * SL);
+      const unsigned char *o4 = reinterpret_cast<const unsigned char *>(sdo + warp * SL);
 #pragma unroll
       for (int q = 0; q < BI / 2; ++q) {
-        const float4 v = s4[q], w = o4[q];
+        const int o = off_c(q);
+        const float4 v = *reinterpret_cast<const float4 *>(s4 + o), w = *reinterpret_cast<const float4 *>(o4 + o);
         u[2 * q] = cf(v.x, v.y);
         u[2 * q + 1] = cf(v.z, v.w);
         dy[2 * q] = cf(w.x, w.y);
         dy[2 * q + 1] = cf(w.z, w.w);
       }
-      const float4 *d4 = reinterpret_cast<const float4 *>(sd + tid * BI);
-      const float4 *dA4 = reinterpret_cast<const float4 *>(sdA + tid * BI);
+      const unsigned char *d4 = reinterpret_cast<const unsigned char *>(sd + warp * SL);
+      const unsigned char *dA4 = reinterpret_cast<const unsigned char *>(sdA + warp * SL);
 #pragma unroll
       for (int q = 0; q < BI / 4; ++q) {
-        const float4 v = d4[q];
+        const int o = off_f(q);
+        const float4 v = *reinterpret_cast<const float4 *>(d4 + o);
         dl[4 * q] = v.x; dl[4 * q + 1] = v.y; dl[4 * q + 2] = v.z; dl[4 * q + 3] = v.w;
         if (HAS_DA) {
-          const float4 w = dA4[q];
+          const float4 w = *reinterpret_cast<const float4 *>(dA4 + o);
           dAv[4 * q] = w.x; dAv[4 * q + 1] = w.y; dAv[4 * q + 2] = w.z; dAv[4 * q + 3] = w.w;
         }
       }
@@ -661,24 +702,34 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
       cf *so = reinterpret_cast<cf *>(out_stage);
       float *sod = reinterpret_cast<float *>(out_stage + B_U_BYTES);
       float *sodA = reinterpret_cast<float *>(out_stage + B_U_BYTES + B_D_BYTES);
-      float4 *s4 = reinterpret_cast<float4 *>(so + tid * BI);
+      unsigned char *s4 = reinterpret_cast<unsigned char *>(so + warp * SL);
 #pragma unroll
-      for (int q = 0; q < BI / 2; ++q) s4[q] = make_float4(du[2 * q].re, du[2 * q].im, du[2 * q + 1].re, du[2 * q + 1].im);
-      float4 *d4 = reinterpret_cast<float4 *>(sod + tid * BI);
+      for (int q = 0; q < BI / 2; ++q)
+        *reinterpret_cast<float4 *>(s4 + off_c(q)) = make_float4(du[2 * q].re, du[2 * q].im, du[2 * q + 1].re, du[2 * q + 1].im);
+      unsigned char *d4 = reinterpret_cast<unsigned char *>(sod + warp * SL);
 #pragma unroll
-      for (int q = 0; q < BI / 4; ++q) d4[q] = make_float4(ddl[4 * q], ddl[4 * q + 1], ddl[4 * q + 2], ddl[4 * q + 3]);
+      for (int q = 0; q < BI / 4; ++q)
+        *reinterpret_cast<float4 *>(d4 + off_f(q)) = make_float4(ddl[4 * q], ddl[4 * q + 1], ddl[4 * q + 2], ddl[4 * q + 3]);
       if (HAS_DA) {
-        float4 *dA4 = reinterpret_cast<float4 *>(sodA + tid * BI);
+        unsigned char *dA4 = reinterpret_cast<unsigned char *>(sodA + warp * SL);
 #pragma unroll
-        for (int q = 0; q < BI / 4; ++q) dA4[q] = make_float4(ddA[4 * q], ddA[4 * q + 1], ddA[4 * q + 2], ddA[4 * q + 3]);
+        for (int q = 0; q < BI / 4; ++q)
+          *reinterpret_cast<float4 *>(dA4 + off_f(q)) = make_float4(ddA[4 * q], ddA[4 * q + 1], ddA[4 * q + 2], ddA[4 * q + 3]);
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
         const int w0 = warp * SL;
-        bulk_s2g(rp.du + t0 + w0, so + w0, B_U_BYTES / BWARPS);
-        bulk_s2g(rp.dd + t0 + w0, sod + w0, B_D_BYTES / BWARPS);
-        if (HAS_DA) bulk_s2g(rp.ddA + t0 + w0, sodA + w0, B_D_BYTES / BWARPS);
+        if (SWZ) {
+          const int64_t e0 = row * L + t0 + w0;
+          tensor_s2g(&maps.du, (int)(e0 / 16), so + w0);
+          tensor_s2g(&maps.dd, (int)(e0 / 32), sod + w0);
+          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 / 32), sodA + w0);
+        } else {
+          bulk_s2g(rp.du + t0 + w0, so + w0, B_U_BYTES / BWARPS);
+          bulk_s2g(rp.dd + t0 + w0, sod + w0, B_D_BYTES / BWARPS);
+          if (HAS_DA) bulk_s2g(rp.ddA + t0 + w0, sodA + w0, B_D_BYTES / BWARPS);
+        }
         bulk_commit();
       }
       stores_pending = true;
@@ -743,29 +794,6 @@ __global__ void __launch_bounds__(BT, 2) simpscan_bwd_kernel(const b200_simpscan
 // the u / delta slices in shared memory and leave through bulk stores.  8 bytes per element more
 // traffic than the recomputing kernel, a third fewer instructions.
 constexpr int HSL = 32 * BI;          // 256 timesteps per warp slice
-
-// Tensor maps of the activation tensors viewed as rows of 128 bytes, with the 128-byte swizzle:
-// the TMA engine XORs the 16-byte chunk index of every row with the row index (mod 8) on the way
-// into shared memory, which spreads a lane's 64-byte (32-byte) run over all bank groups, so the
-// lane-blocked 128-bit shared loads and stores of a warp are conflict-free.  (With linear bulk
-// copies the 64-byte lane stride gives 4-way conflicts, and the shared-memory pipe, not the
-// issue slots, bounded this kernel.)
-struct TmaMaps {
-  CUtensorMap u, dout, h, d, dA, du, dd, ddA;
-};
-__device__ __forceinline__ int swz128(int byte_off) { return byte_off ^ (((byte_off >> 7) & 7) << 4); }
-__device__ __forceinline__ void tensor_g2s(void *dst, const CUtensorMap *map, int row, uint64_t *bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                   smem_u32(dst)),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tensor_s2g(const CUtensorMap *map, int row, const void *src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(0), "r"(row), "r"(smem_u32(src))
-               : "memory");
-}
 
 template <int HWARPS> struct __align__(16) BwdHShared {
   cf rtot_q[2][HWARPS];     // per-warp aggregates of the reverse scan (double-buffered by tile parity)
@@ -1165,19 +1193,6 @@ template <int DM, bool HAS_DA, bool S1> int launch_fwd_s(const b200_simpscan_arg
 template <int DM, bool HAS_DA> int launch_fwd(const b200_simpscan_args &a, cudaStream_t st) {
   return a.dstate == 1 ? launch_fwd_s<DM, HAS_DA, true>(a, st) : launch_fwd_s<DM, HAS_DA, false>(a, st);
 }
-template <int DM, bool HAS_DA, bool S1, bool NEED_BC> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
-  constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
-  constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
-  const int64_t rows = (int64_t)a.batch * a.dim;
-  const size_t smem = 2 * (size_t)BUF_BYTES + OUT_BYTES + sizeof(BwdShared) + (size_t)5 * a.dstate * sizeof(cf);
-  auto k = simpscan_bwd_kernel<DM, HAS_DA, S1, NEED_BC>;
-  if (int e = set_smem(k, smem)) return e;
-  int64_t grid = rows;
-  const int64_t resident = (int64_t)sm_count() * (HAS_DA ? 1 : 2);   // CTAs that fit at once
-  if (grid > resident) grid = resident;
-  k<<<(unsigned)grid, BT, smem, st>>>(a);
-  return launch_status();
-}
 // cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1208,29 +1223,50 @@ bool make_row_map(CUtensorMap *m, const void *base, uint64_t bytes, uint32_t box
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor maps for the backward kernels: possible when every activation tensor is a contiguous
+// (batch, dim, seqlen) array made of whole 128-byte rows.
+bool build_bwd_maps(const b200_simpscan_args &a, bool has_dA, bool with_h, TmaMaps &maps) {
+  memset(&maps, 0, sizeof(maps));
+  const int64_t rows = (int64_t)a.batch * a.dim, L = a.seqlen, DL = (int64_t)a.dim * L;
+  auto dense = [&](int64_t bs, int64_t ds) { return ds == L && bs == DL; };
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  bool ok = L % 32 == 0 && rows * L / 16 < (int64_t(1) << 31) && dense(a.u_bs, a.u_ds) && dense(a.dout_bs, a.dout_ds) &&
+            dense(a.delta_bs, a.delta_ds) && dense(a.du_bs, a.du_ds) && dense(a.ddelta_bs, a.ddelta_ds) && al16(a.u) &&
+            al16(a.dout) && al16(a.delta) && al16(a.du) && al16(a.ddelta);
+  if (with_h) ok = ok && dense(a.out_bs, a.out_ds) && al16(a.out);
+  if (has_dA) ok = ok && dense(a.deltaA_bs, a.deltaA_ds) && dense(a.ddeltaA_bs, a.ddeltaA_ds) && al16(a.deltaA) && al16(a.ddeltaA);
+  if (!ok) return false;
+  const uint64_t cb = (uint64_t)rows * L * 8, fb = (uint64_t)rows * L * 4;
+  ok = make_row_map(&maps.u, a.u, cb, 16) && make_row_map(&maps.dout, a.dout, cb, 16) && make_row_map(&maps.d, a.delta, fb, 8) &&
+       make_row_map(&maps.du, a.du, cb, 16) && make_row_map(&maps.dd, a.ddelta, fb, 8);
+  if (with_h) ok = ok && make_row_map(&maps.h, a.out, cb, 16);
+  if (has_dA) ok = ok && make_row_map(&maps.dA, a.deltaA, fb, 8) && make_row_map(&maps.ddA, a.ddeltaA, fb, 8);
+  return ok;
+}
+
+template <int DM, bool HAS_DA, bool S1, bool NEED_BC> int launch_bwd_s(const b200_simpscan_args &a, cudaStream_t st) {
+  constexpr int BUF_BYTES = 2 * B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
+  constexpr int OUT_BYTES = B_U_BYTES + B_D_BYTES * (HAS_DA ? 2 : 1);
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = 2 * (size_t)BUF_BYTES + OUT_BYTES + sizeof(BwdShared) + (size_t)5 * a.dstate * sizeof(cf) + 1024;
+  TmaMaps maps;
+  const bool swz = build_bwd_maps(a, HAS_DA, false, maps);
+  auto k = swz ? simpscan_bwd_kernel<DM, HAS_DA, S1, NEED_BC, true> : simpscan_bwd_kernel<DM, HAS_DA, S1, NEED_BC, false>;
+  if (int e = set_smem(k, smem)) return e;
+  int64_t grid = rows;
+  const int64_t resident = (int64_t)sm_count() * (HAS_DA ? 1 : 2);   // CTAs that fit at once
+  if (grid > resident) grid = resident;
+  k<<<(unsigned)grid, BT, smem, st>>>(a, maps);
+  return launch_status();
+}
+
 template <int DM, bool HAS_DA, bool NEED_BC, int HT> int launch_bwd_h_t(const b200_simpscan_args &a, cudaStream_t st) {
   constexpr int HWARPS = HT / 32;
   constexpr int ROB = 2 * HSL * 8, RWB = HSL * 8 + HSL * 4 * (HAS_DA ? 2 : 1);
   const int64_t rows = (int64_t)a.batch * a.dim;
   const size_t smem = (size_t)HWARPS * (ROB + 2 * RWB) + sizeof(BwdHShared<HWARPS>) + 1024;
-  // swizzled tensor copies need contiguous (batch, dim, seqlen) tensors made of whole 128-byte rows
-  const int64_t L = a.seqlen, DL = (int64_t)a.dim * L;
-  auto dense = [&](int64_t bs, int64_t ds) { return ds == L && bs == DL; };
-  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  bool swz = L % 32 == 0 && rows * L / 16 < (int64_t(1) << 31) && dense(a.u_bs, a.u_ds) && dense(a.dout_bs, a.dout_ds) &&
-             dense(a.out_bs, a.out_ds) && dense(a.delta_bs, a.delta_ds) && dense(a.du_bs, a.du_ds) &&
-             dense(a.ddelta_bs, a.ddelta_ds) && al16(a.u) && al16(a.dout) && al16(a.out) && al16(a.delta) && al16(a.du) &&
-             al16(a.ddelta);
-  if (HAS_DA) swz = swz && dense(a.deltaA_bs, a.deltaA_ds) && dense(a.ddeltaA_bs, a.ddeltaA_ds) && al16(a.deltaA) && al16(a.ddeltaA);
   TmaMaps maps;
-  memset(&maps, 0, sizeof(maps));
-  if (swz) {
-    const uint64_t cb = (uint64_t)rows * L * 8, fb = (uint64_t)rows * L * 4;
-    swz = make_row_map(&maps.u, a.u, cb, 16) && make_row_map(&maps.dout, a.dout, cb, 16) &&
-          make_row_map(&maps.h, a.out, cb, 16) && make_row_map(&maps.d, a.delta, fb, 8) &&
-          make_row_map(&maps.du, a.du, cb, 16) && make_row_map(&maps.dd, a.ddelta, fb, 8);
-    if (HAS_DA) swz = swz && make_row_map(&maps.dA, a.deltaA, fb, 8) && make_row_map(&maps.ddA, a.ddeltaA, fb, 8);
-  }
+  const bool swz = build_bwd_maps(a, HAS_DA, true, maps);
   auto k = swz ? simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT, true> : simpscan_bwd_h_kernel<DM, HAS_DA, NEED_BC, HT, false>;
   if (int e = set_smem(k, smem)) return e;
   int per_sm = (int)((227 * 1024) / (smem + 1024));
