@@ -116,21 +116,33 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
   // full, or is the last one of a row whose length is a multiple of 4 (the copies then cover the
   // valid part only and the lanes past it substitute the neutral operands in registers)
   const bool partial_ok = (L % 4) == 0;
-  auto issue = [&](int f) {   // lane 0 only
+  // The prefetch position (item pf_f = stage pf_s of row pf_row, slot pf_k) advances without
+  // divisions and the row's pointers are computed once per row: index arithmetic (64-bit
+  // divisions per stage) was a fifth of this kernel's instructions.
+  int pf_f = 0, pf_s = 0, pf_k = 0;
+  int64_t pf_row = gw;
+  RowPtrs pr = row_ptrs(gw);
+  auto issue = [&]() {   // lane 0 only: issues item pf_f and advances
+    const int f = pf_f, s = pf_s, k = pf_k;
     if (f >= total) return;
-    const int s = f % nst;
+    const RowPtrs r = pr;
+    ++pf_f;
+    if (++pf_k == FNS) pf_k = 0;
+    if (++pf_s == nst) {
+      pf_s = 0;
+      pf_row += W;
+      if (pf_f < total) pr = row_ptrs(pf_row);
+    }
     const int valid = min(FSTAGE, L - s * FSTAGE);
     if (valid < FSTAGE && !partial_ok) return;
-    const RowPtrs r = row_ptrs(gw + (int64_t)(f / nst) * W);
     if (!r.tma) return;
-    const int k = f % FNS;
     const int64_t t0 = (int64_t)s * FSTAGE;
     mbar_expect_tx(&bars[k], valid * (8 + (HAS_DA ? 8 : 4)));
     bulk_g2s(slot_u(k), r.u + t0, valid * 8, &bars[k]);
     bulk_g2s(slot_d(k), r.d + t0, valid * 4, &bars[k]);
     if (HAS_DA) bulk_g2s(slot_dA(k), r.dA + t0, valid * 4, &bars[k]);
   };
-  if (lane == 0) { issue(0); issue(1); }
+  if (lane == 0) { issue(); issue(); }
 
   uint32_t phase_bits = 0;   // bit k: parity the next wait on slot k expects
   bool failed = false;
@@ -140,10 +152,12 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
   bool bc_one = false;
   const cf *Ap = nullptr, *Bp = nullptr, *Cp = nullptr;
   cf *xrow = nullptr;
+  int s = -1, k = -1;
   for (int f = 0; f < total; ++f) {
-    const int s = f % nst;
+    if (++s == nst) s = 0;
+    if (++k == FNS) k = 0;
     if (s == 0) {   // new row
-      row = gw + (int64_t)(f / nst) * W;
+      if (f > 0) row += W;
       rp = row_ptrs(row);
       const int d = (int)(row % p.dim);
       Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
@@ -156,7 +170,6 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
       Pc0 = cf(1.f, 0.f);
       hc0 = cf(0.f, 0.f);
     }
-    const int k = f % FNS;
     const int t0 = s * FSTAGE;
     const int valid = min(FSTAGE, L - t0);
     const bool async_stage = rp.tma && (valid == FSTAGE || partial_ok);
@@ -308,7 +321,7 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
     // prefetch stage f+2 into the slot used by stage f-1 (its bulk store must have finished reading)
     if (lane == 0 && f + 2 < total) {
       bulk_wait_read<0>();
-      issue(f + 2);
+      issue();
     }
     if (async_stage) {
       float4 *s4 = reinterpret_cast<float4 *>(su + lane * FI);
@@ -843,18 +856,29 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
   };
   unsigned char *ro = smem_raw + (size_t)warp * ROB;
   auto rwbuf = [&](int k) { return smem_raw + (size_t)HWARPS * ROB + (size_t)(k * HWARPS + warp) * RWB; };
-  // stream item f: row blockIdx.x + (f / n_tiles) * gridDim.x, tile n_tiles - 1 - f % n_tiles;
-  // `which` selects the read-only slices (1), the overwritten ones (2) or both (3)
-  auto issue = [&](int f, int which) {   // lane 0 of a warp
+  // stream item f: row blockIdx.x + (f / n_tiles) * gridDim.x, tile n_tiles - 1 - f % n_tiles.
+  // The prefetch position (item pf_f = row pf_row, tile pf_c) advances without divisions, and the
+  // tensor-copy path needs no row pointers at all: index arithmetic was a fifth of this kernel.
+  int pf_f = 0, pf_c = n_tiles - 1;
+  int64_t pf_row = blockIdx.x;
+  auto advance = [&]() {
+    ++pf_f;
+    if (--pf_c < 0) { pf_c = n_tiles - 1; pf_row += gridDim.x; }
+  };
+  // `which` selects the read-only slices (1), the overwritten ones (2) or both (3) of item pf_f
+  auto issue = [&](int which) {   // lane 0 of a warp
+    const int f = pf_f, c = pf_c;
     if (f >= total) return;
-    const int c = n_tiles - 1 - f % n_tiles;
     if ((c + 1) * HTILE > L) return;
-    const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x);
-    if (!r.tma) return;
+    RowPtrs r = RowPtrs();
+    if (!SWZ) {
+      r = row_ptrs(pf_row);
+      if (!r.tma) return;
+    }
     const int64_t t0 = (int64_t)c * HTILE + warp * HSL;
     // row of 128 bytes at which the slice starts in a contiguous (batch, dim, seqlen) tensor
-    const int64_t e0 = (blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x) * L + t0;
-    const int rc = (int)(e0 / 16), rf = (int)(e0 / 32);   // complex64 / float32 tensors
+    const int64_t e0 = pf_row * L + t0;
+    const int rc = (int)(e0 >> 4), rf = (int)(e0 >> 5);   // complex64 / float32 tensors
     if (which & 1) {
       uint64_t *bar = &sh.full_ro[warp];
       mbar_expect_tx(bar, ROB);
@@ -889,7 +913,8 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
     fence_proxy_async();
   }
   __syncthreads();
-  if (lane == 0) issue(0, 3);
+  if (lane == 0) issue(3);
+  advance();
 
   bool failed = false;
   auto wait = [&](uint64_t *bar, uint32_t parity) {
@@ -902,11 +927,12 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
   cf A0, Cc, inv_bc;
   bool c_one = false, bc_one = false;
   cf dA_acc, dB_acc, dC_acc;
+  int j = -1;
   for (int f = 0; f < total; ++f) {
-    const int j = f % n_tiles;
+    if (++j == n_tiles) j = 0;
     const int c = n_tiles - 1 - j;
     if (j == 0) {   // new row
-      row = blockIdx.x + (int64_t)(f / n_tiles) * gridDim.x;
+      if (f > 0) row += gridDim.x;
       rp = row_ptrs(row);
       const int d = (int)(row % p.dim);
       A0 = reinterpret_cast<const cf *>(p.A)[(int64_t)d * p.A_ds];
@@ -996,10 +1022,11 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
     // first has to be read out by the stores of the previous item
     __syncwarp();
     if (lane == 0) {
-      issue(f + 1, 1);
+      issue(1);
       if (stores_pending) bulk_wait_read<0>();
-      issue(f + 1, 2);
+      issue(2);
     }
+    advance();
     bool same_step = true;
 #pragma unroll
     for (int i = 1; i < BI; ++i) same_step = same_step && dl[i] == dl[0] && dAv[i] == dAv[0];
@@ -1110,9 +1137,9 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
       if (lane == 0) {
         if (SWZ) {
           const int64_t e0 = row * L + tw;
-          tensor_s2g(&maps.du, (int)(e0 / 16), su);
-          tensor_s2g(&maps.dd, (int)(e0 / 32), sd);
-          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 / 32), sdA);
+          tensor_s2g(&maps.du, (int)(e0 >> 4), su);
+          tensor_s2g(&maps.dd, (int)(e0 >> 5), sd);
+          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 >> 5), sdA);
         } else {
           bulk_s2g(rp.du + tw, su, WU);
           bulk_s2g(rp.dd + tw, sd, WD);
