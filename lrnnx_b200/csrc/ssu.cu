@@ -346,21 +346,38 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
   const int my = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
   const int es = (int)sizeof(ST);
 
+  // A CTA's tiles are blockIdx.x + it * gridDim.x; a position in that sequence is kept as
+  // (batch*heads index, tile inside it) and advanced by the decomposed grid stride, so that the
+  // per-tile index arithmetic needs no division (it was a quarter of the kernel's instructions).
+  struct Pos { uint32_t bh, mt; };
+  const uint32_t step_bh = gridDim.x / (uint32_t)tiles_per_bh, step_mt = gridDim.x % (uint32_t)tiles_per_bh;
+  auto first_pos = [&]() { Pos q; q.bh = blockIdx.x / (uint32_t)tiles_per_bh; q.mt = blockIdx.x % (uint32_t)tiles_per_bh; return q; };
+  auto advance = [&](Pos &q) {
+    q.bh += step_bh;
+    q.mt += step_mt;
+    if (q.mt >= (uint32_t)tiles_per_bh) { q.mt -= (uint32_t)tiles_per_bh; q.bh += 1; }
+  };
   struct Tile { int b, h, m0, sb, g; };
-  auto tile_of = [&](int it, bool need_sb) {
-    const uint32_t tile = blockIdx.x + (uint32_t)it * gridDim.x;
+  auto tile_of = [&](const Pos &q, bool need_sb) {
     Tile t;
-    const uint32_t bh = tile / (uint32_t)tiles_per_bh;
-    t.m0 = (int)(tile - bh * (uint32_t)tiles_per_bh) * TR;
-    t.b = (int)(bh / (uint32_t)p.nheads);
-    t.h = (int)(bh - (uint32_t)t.b * (uint32_t)p.nheads);
+    t.m0 = (int)q.mt * TR;
+    if (p.nheads == 1) { t.b = (int)q.bh; t.h = 0; t.g = 0; }
+    else {
+      t.b = (int)(q.bh / (uint32_t)p.nheads);
+      t.h = (int)(q.bh - (uint32_t)t.b * (uint32_t)p.nheads);
+      t.g = t.h / (p.nheads / p.ngroups);
+    }
     t.sb = (need_sb && p.state_batch_indices) ? p.state_batch_indices[t.b] : t.b;
-    t.g = t.h / (p.nheads / p.ngroups);
     return t;
   };
-  auto issue = [&](int it) {   // one thread
+  Pos pf = first_pos();        // position of the next tile to load (used by the issuing thread)
+  int pf_it = 0;
+  auto issue = [&]() {   // one thread: loads tile pf_it and advances
+    const int it = pf_it;
     if (it >= my) return;
-    const Tile t = tile_of(it, true);
+    const Tile t = tile_of(pf, true);
+    ++pf_it;
+    advance(pf);
     unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
     uint64_t *bar = &full[it % TNS];
     uint32_t bytes = SL::ST_B + 2 * SL::X_B + 2 * SL::BC_B;
@@ -394,13 +411,14 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
   }
   __syncthreads();
   if (tid == 0) {
-    for (int i = 0; i < TNS - 1; ++i) issue(i);
+    for (int i = 0; i < TNS - 1; ++i) issue();
   }
+  Pos cur = first_pos();
   const bool plain_exp = p.method == B200_DISC_MAMBA || p.method == B200_DISC_DIRAC;
   bool failed = false;
   for (int it = 0; it < my; ++it) {
     unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
-    const Tile t = tile_of(it, false);
+    const Tile t = tile_of(cur, false);
     // A rows of this thread's passes: plain 16-byte loads, issued before the wait for the tile
     float Av[PASSES][VEC];
 #pragma unroll
@@ -471,7 +489,7 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
     fence_proxy_async();
     __syncthreads();
     if (tid == 0) {
-      const Tile ts = tile_of(it, true);
+      const Tile ts = tile_of(cur, true);
       bulk_s2g(reinterpret_cast<unsigned char *>(p.state) +
                    ((int64_t)ts.sb * p.state_bs + (int64_t)ts.h * p.state_hs + (int64_t)ts.m0 * p.state_ds) * es,
                s + SL::OFF_S, SL::ST_B);
@@ -480,8 +498,9 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
       bulk_commit();
       // the slot refilled next held tile it-1: its stores (the group before this one) must have been read out
       bulk_wait_read<1>();
-      issue(it + TNS - 1);
+      issue();
     }
+    advance(cur);
   }
   if (tid == 0) bulk_wait<0>();
   if (failed) atomicExch(&g_ssu_status, 3);
