@@ -438,19 +438,29 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
   // Every warp runs its own pipeline on its 256-step slice of the chunk: lane 0 issues the
   // slice's bulk loads and stores, the warp alone reads and writes the slice, so loads and
   // stores need no block-wide synchronisation.
-  auto issue = [&](int f) {   // lane 0 of a warp
+  // the prefetch position (item pf_f = row pf_row, chunk pf_c) advances without divisions and the
+  // tensor-copy path needs no row pointers
+  int pf_f = 0, pf_c = n_chunks - 1;
+  int64_t pf_row = blockIdx.x;
+  auto issue = [&]() {   // lane 0 of a warp: issues item pf_f and advances
+    const int f = pf_f, c = pf_c;
+    const int64_t frow = pf_row;
     if (f >= total) return;
-    const int c = n_chunks - 1 - f % n_chunks;
+    ++pf_f;
+    if (--pf_c < 0) { pf_c = n_chunks - 1; pf_row += gridDim.x; }
     if ((c + 1) * kChunk > L) return;
-    const RowPtrs r = row_ptrs(blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x);
-    if (!r.tma) return;
+    RowPtrs r = RowPtrs();
+    if (!SWZ) {
+      r = row_ptrs(frow);
+      if (!r.tma) return;
+    }
     const int k = f & 1;
     const int64_t t0 = (int64_t)c * kChunk + warp * SL;
     uint64_t *bar = &sh.full[k][warp];
     mbar_expect_tx(bar, BUF_BYTES / BWARPS);
     if (SWZ) {   // rows of 128 bytes of the contiguous (batch, dim, seqlen) tensors
-      const int64_t e0 = (blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x) * L + t0;
-      const int rc = (int)(e0 / 16), rf = (int)(e0 / 32);
+      const int64_t e0 = frow * L + t0;
+      const int rc = (int)(e0 >> 4), rf = (int)(e0 >> 5);
       tensor_g2s(buf_u(k) + warp * SL, &maps.u, rc, bar);
       tensor_g2s(buf_do(k) + warp * SL, &maps.dout, rc, bar);
       tensor_g2s(buf_d(k) + warp * SL, &maps.d, rf, bar);
@@ -469,7 +479,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
     fence_proxy_async();
   }
   __syncthreads();
-  if (lane == 0) { issue(0); issue(1); }
+  if (lane == 0) { issue(); issue(); }
 
   // A bounded wait that expires marks the thread as failed; a failed thread skips every later
   // wait (results are then garbage and the status word says so) but keeps taking part in the
@@ -487,11 +497,12 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
   cf A0, C0;
   bool c_one = false;
   cf dA_acc, dB_acc, dC_acc;   // per-thread partial sums over the row (single-state rows)
+  int j = -1;
   for (int f = 0; f < total; ++f) {
-    const int j = f % n_chunks;
+    if (++j == n_chunks) j = 0;
     const int c = n_chunks - 1 - j;
     if (j == 0) {   // new row
-      row = blockIdx.x + (int64_t)(f / n_chunks) * gridDim.x;
+      if (f > 0) row += gridDim.x;
       rp = row_ptrs(row);
       const int d = (int)(row % p.dim);
       Ap = reinterpret_cast<const cf *>(p.A) + (int64_t)d * p.A_ds;
@@ -562,7 +573,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
     }
     // the warp's slice now lives in registers: refill it with the stream item two steps ahead
     __syncwarp();
-    if (lane == 0) issue(f + 2);
+    if (lane == 0) issue();
     bool same_step = true;
 #pragma unroll
     for (int i = 1; i < BI; ++i) same_step = same_step && dl[i] == dl[0] && dAv[i] == dAv[0];
@@ -735,9 +746,9 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
         const int w0 = warp * SL;
         if (SWZ) {
           const int64_t e0 = row * L + t0 + w0;
-          tensor_s2g(&maps.du, (int)(e0 / 16), so + w0);
-          tensor_s2g(&maps.dd, (int)(e0 / 32), sod + w0);
-          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 / 32), sodA + w0);
+          tensor_s2g(&maps.du, (int)(e0 >> 4), so + w0);
+          tensor_s2g(&maps.dd, (int)(e0 >> 5), sod + w0);
+          if (HAS_DA) tensor_s2g(&maps.ddA, (int)(e0 >> 5), sodA + w0);
         } else {
           bulk_s2g(rp.du + t0 + w0, so + w0, B_U_BYTES / BWARPS);
           bulk_s2g(rp.dd + t0 + w0, sod + w0, B_D_BYTES / BWARPS);
