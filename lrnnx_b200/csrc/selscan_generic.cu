@@ -14,8 +14,8 @@
 // as a reverse warp scan and emits all gradients.
 //
 // Behaviour follows csrc/selective_scan/selective_scan.cuh:73-382 and
-// csrc/selective_scan/selective_scan_backward.cuh:86-845 of lrnnx (math
-// restated in include/lrnnx_b200.h and DESIGN.md, not the code structure).
+// csrc/selective_scan/selective_scan_backward.cuh:86-845 of lrnnx (the math is
+// restated in include/lrnnx_b200.h; the code structure is not lrnnx's).
 #include "common.cuh"
 #include <type_traits>
 
