@@ -331,7 +331,7 @@ class S6Scan:
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
         self.copy_stream = torch.cuda.Stream(device=dev)
         self.g_fwd = self.g_bwd = None
-        if not self.sp and self.L < 4 * 2048:      # (long rows run segmented: host-side stitching, not captured)
+        if not self.sp:
             # the extension calls are captured once as CUDA graphs (after a warm-up on a side stream);
             # a step replays them, so the timed region holds the kernels and not the Python launch path
             side = torch.cuda.Stream(device=dev)

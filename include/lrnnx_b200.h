@@ -165,6 +165,13 @@ typedef struct b200_selscan_fixup_args {
 
 int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream);
 
+/* Folds the zero-start summaries of the n_segments > 1 segments of one forward call (the last
+ * checkpoint entry of each segment in f.x) into the state and product entering every segment:
+ *   h_in[0] = 0, p_in[0] = 1,  h_in[s] = P[s-1] h_in[s-1] + h[s-1],  p_in[s] = p_in[s-1] P[s-1].
+ * Writes h_in and p_in (same layout as above; the pointers are outputs here); uses f.x, f.batch,
+ * f.dim, f.dstate, f.seqlen, n_segments and seg_len only. */
+int b200_selscan_fold(const b200_selscan_fixup_args *args, void *stream);
+
 /* ------------------------------------------------------------------------
  * Simplified (diagonal, complex-input) scan used by LTV-S5.
  * Replaces simplified_scan_fwd/bwd (csrc/simplified_scan/simplified_scan_cpu.cpp:160-331)

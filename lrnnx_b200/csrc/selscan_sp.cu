@@ -301,6 +301,26 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_vec_kernel(const b200_
   }
 }
 
+// One thread per (batch, channel, state): sequential fold of the segments' (product, state)
+// summaries, read from the last checkpoint entry of every segment.
+__global__ void selscan_fold_kernel(const float *__restrict__ x, float *__restrict__ h_in, float *__restrict__ p_in,
+                                    int64_t rows, int N, int n_chunks, int chunks_per_seg, int n_seg) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * N) return;
+  const int64_t row = i / N;
+  const int n = (int)(i % N);
+  float h = 0.f, pr = 1.f;
+  for (int s = 0; s < n_seg; ++s) {
+    h_in[((int64_t)s * rows + row) * N + n] = h;
+    p_in[((int64_t)s * rows + row) * N + n] = pr;
+    const int last = min((s + 1) * chunks_per_seg, n_chunks) - 1;
+    const float P = x[(row * n_chunks + last) * 2 * N + 2 * n];
+    const float hs = x[(row * n_chunks + last) * 2 * N + 2 * n + 1];
+    h = fmaf(P, h, hs);
+    pr *= P;
+  }
+}
+
 bool fixup_vec_ok(const b200_selscan_fixup_args &q) {
   const b200_selscan_fwd_args &a = q.f;
   const int es = a.dtype == B200_F32 ? 4 : 2;
@@ -345,5 +365,23 @@ extern "C" int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *str
   } else {
     selscan_fixup_kernel<<<grid, SPW * 32, smem, st>>>(*args);
   }
+  return launch_status();
+}
+
+extern "C" int b200_selscan_fold(const b200_selscan_fixup_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "selscan_fold: null argument block");
+  const b200_selscan_fwd_args &a = args->f;
+  B200_REQUIRE(a.x && args->h_in && args->p_in, B200_ERR_NULL, "selscan_fold: x, h_in, p_in must be non-null");
+  B200_REQUIRE(!a.is_complex, B200_ERR_UNSUPPORTED, "selscan_fold supports real A");
+  B200_REQUIRE(a.batch > 0 && a.dim > 0 && a.seqlen > 0 && a.dstate > 0, B200_ERR_SHAPE, "selscan_fold: bad sizes");
+  B200_REQUIRE(args->n_segments > 1 && args->seg_len > 0 && args->seg_len % kChunk == 0, B200_ERR_SHAPE,
+               "selscan_fold: n_segments > 1 and a seg_len that is a positive multiple of 2048 are required");
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const int n_chunks = (a.seqlen + kChunk - 1) / kChunk;
+  const int64_t total = rows * a.dstate;
+  selscan_fold_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float *>(a.x), reinterpret_cast<float *>(const_cast<void *>(args->h_in)),
+      reinterpret_cast<float *>(const_cast<void *>(args->p_in)), rows, a.dstate, n_chunks, args->seg_len / kChunk,
+      args->n_segments);
   return launch_status();
 }

@@ -179,23 +179,17 @@ def _stage_states_of(x_, batch, dim, seqlen, dstate):
 
 
 def _stitch_segments(a, x, S, seqlen, u):
-    """Fold the zero-start summaries of the segments and run the fix-up kernel on segments >= 1."""
-    n_chunks = x.shape[2]
+    """Fold the zero-start summaries of the segments (one kernel) and run the fix-up kernel on segments >= 1."""
     seg_len = -(-(-(-seqlen // S)) // CHUNK) * CHUNK
-    cps = seg_len // CHUNK
-    last = [min((s + 1) * cps, n_chunks) - 1 for s in range(S)]
-    P = x[:, :, last, 0::2].permute(2, 0, 1, 3).contiguous()      # (S, batch, dim, dstate) zero-start products
-    h = x[:, :, last, 1::2].permute(2, 0, 1, 3).contiguous()
-    h_in = torch.zeros_like(h)
-    p_in = torch.ones_like(P)
-    for s in range(1, S):
-        h_in[s] = P[s - 1] * h_in[s - 1] + h[s - 1]
-        p_in[s] = p_in[s - 1] * P[s - 1]
+    batch, dim, _, two_n = x.shape
+    h_in = torch.empty((S, batch, dim, two_n // 2), dtype=torch.float32, device=x.device)
+    p_in = torch.empty_like(h_in)
     q = _lib.struct("b200_selscan_fixup_args")()
     a.l_segments = 0
     q.f = a
     q.h_in, q.p_in = h_in.data_ptr(), p_in.data_ptr()
     q.n_segments, q.seg_len = S, seg_len
+    _lib.call("b200_selscan_fold", q, _stream(u))
     _lib.call("b200_selscan_fixup", q, _stream(u))
 
 
