@@ -21,7 +21,8 @@ namespace b200 {
 namespace {
 
 constexpr int FT = 256;       // forward threads
-constexpr int FL = 2;         // output positions per thread
+constexpr int FL = 2;         // output positions per thread (Cauchy)
+constexpr int VFL = 8;        // output positions per thread (Vandermonde), FT apart
 constexpr int NMAX_SMEM = 1024;
 constexpr int BTT = 256;      // backward threads
 constexpr int TN = 4;         // poles per backward CTA
@@ -74,33 +75,41 @@ __global__ void __launch_bounds__(FT) cauchy_fwd_kernel(const cf *__restrict__ v
 
 __global__ void __launch_bounds__(FT) vand_fwd_kernel(const cf *__restrict__ v, const cf *__restrict__ x,
                                                       float *__restrict__ out, int n, int L) {
+  // A thread owns VFL positions l0, l0 + FT, ...: exp(x l) is evaluated exactly at l0 and advanced
+  // by the per-pole constant exp(x FT) (a complex multiply instead of an exp and a sin/cos per term).
   __shared__ float4 vx[NMAX_SMEM];
+  __shared__ float2 wstep[NMAX_SMEM];
   const int b = blockIdx.y;
-  const int l0 = blockIdx.x * FT * FL + threadIdx.x;
-  float acc[FL];
+  const int l0 = blockIdx.x * FT * VFL + threadIdx.x;
+  const float lf = (float)l0;
+  float acc[VFL];
 #pragma unroll
-  for (int j = 0; j < FL; ++j) acc[j] = 0.f;
+  for (int j = 0; j < VFL; ++j) acc[j] = 0.f;
   for (int nb = 0; nb < n; nb += NMAX_SMEM) {
     const int cnt = min(NMAX_SMEM, n - nb);
     __syncthreads();
     for (int i = threadIdx.x; i < cnt; i += FT) {
       const cf vv = v[(int64_t)b * n + nb + i], xx = x[(int64_t)b * n + nb + i];
       vx[i] = make_float4(vv.re, vv.im, xx.re, xx.im);
+      const cf w = cexp(xx * (float)FT);
+      wstep[i] = make_float2(w.re, w.im);
     }
     __syncthreads();
 #pragma unroll 2
     for (int i = 0; i < cnt; ++i) {
       const float4 t = vx[i];
-      const cf vv(t.x, t.y), xx(t.z, t.w);
+      const float2 ws = wstep[i];
+      const cf xx(t.z, t.w), W(ws.x, ws.y);
+      cf E = cexp(xx * lf) * cf(t.x, t.y);      // v exp(x l0)
 #pragma unroll
-      for (int j = 0; j < FL; ++j) {
-        const float lf = (float)(l0 + j * FT);
-        acc[j] += (cexp(xx * lf) * vv).re;
+      for (int j = 0; j < VFL; ++j) {
+        acc[j] += E.re;
+        E = E * W;
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < FL; ++j) {
+  for (int j = 0; j < VFL; ++j) {
     const int l = l0 + j * FT;
     if (l < L) out[(int64_t)b * L + l] = 2.f * acc[j];
   }
@@ -122,7 +131,15 @@ __global__ void __launch_bounds__(BTT) s4_bwd_partial_kernel(const cf *__restric
 #pragma unroll
   for (int k = 0; k < TN; ++k) { a1[k] = cf(0.f, 0.f); a2[k] = cf(0.f, 0.f); }
   const int lbeg = chunk * l_chunk, lend = min(L, lbeg + l_chunk);
-  for (int l = lbeg + threadIdx.x; l < lend; l += BTT) {
+  // Vandermonde: exp(w l) advanced by the per-pole constant exp(w BTT) between the positions of
+  // a thread (BTT apart), re-evaluated exactly every 16 positions
+  cf Ek[TN], Wk[TN];
+  if constexpr (VAND) {
+#pragma unroll
+    for (int k = 0; k < TN; ++k) Wk[k] = cexp(wn[k] * (float)BTT);
+  }
+  int iter = 0;
+  for (int l = lbeg + threadIdx.x; l < lend; l += BTT, ++iter) {
     if constexpr (!VAND) {
       const cf d = reinterpret_cast<const cf *>(dout_)[(int64_t)b * L + l];
       const cf zl = z[l];
@@ -136,9 +153,11 @@ __global__ void __launch_bounds__(BTT) s4_bwd_partial_kernel(const cf *__restric
     } else {
       const float d = reinterpret_cast<const float *>(dout_)[(int64_t)b * L + l];
       const float lf = (float)l;
+      const bool exact = (iter & 15) == 0;
 #pragma unroll
       for (int k = 0; k < TN; ++k) {
-        const cf e = conj(cexp(wn[k] * lf)) * d;
+        Ek[k] = exact ? cexp(wn[k] * lf) : Ek[k] * Wk[k];
+        const cf e = conj(Ek[k]) * d;
         a1[k] = a1[k] + e;
         a2[k] = a2[k] + e * lf;
       }
@@ -301,7 +320,7 @@ int b200_cauchy_bwd_static(const b200_s4_args *args, void *stream) {
 int b200_vand_fwd(const b200_s4_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "vand_fwd: null argument block");
   if (int e = check(*args, false, true)) return e;
-  dim3 grid((args->seqlen + FT * FL - 1) / (FT * FL), args->batch);
+  dim3 grid((args->seqlen + FT * VFL - 1) / (FT * VFL), args->batch);
   vand_fwd_kernel<<<grid, FT, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const cf *>(args->v), reinterpret_cast<const cf *>(args->w),
       reinterpret_cast<float *>(args->out), args->n, args->seqlen);
