@@ -276,6 +276,9 @@ class S5Scan:
 
 class S6Scan:
     """Selective scan (S6/Mamba) forward(+backward); shapes of BASELINE configs 0, 2 (one layer) and 3."""
+    roofline_note = ("with dstate 16 the scan needs one ex2 and ~7 fp32 operations per (timestep, state, channel) "
+                     "for 4-10 bytes: it is bound by fp32 / SFU instruction issue, not by HBM (ncu: 62 % of the issue "
+                     "slots busy in the forward, DRAM below 10 %)")
     metric, unit = "scan tokens/s (selective scan)", "tokens/s"
 
     def __init__(self, name, batch, dim, L, N, dtype, backward=True):
@@ -571,6 +574,7 @@ class CauchyKernel:
     frequency).  The kernel is bound by the fp32 pipe (two complex reciprocals per
     (row, frequency, pole)), not by HBM; the HBM fraction is reported for completeness."""
     name = "cauchy_s4"
+    roofline_note = "bound by the fp32 pipe (two complex reciprocals per (row, frequency, pole)), not by HBM"
     dtype = "c64"
     metric, unit = "Cauchy output elements/s (fwd+bwd)", "elements/s"
     launches_per_step = 3      # forward, backward partials, backward fold
@@ -745,6 +749,9 @@ def run_ours(args, wl):
                             "traffic": NCU_TRAFFIC.get((wl.name, kname)), "algorithmic_bytes": nbytes,
                             "ms_per_launch": ms,
                             "peak_source": peak_kind}
+            note = getattr(wl, "roofline_note", None)
+            if note:
+                roofs[kname]["note"] = note
         dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
         cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
         h2d, d2h = wl.e2e_bytes()
