@@ -30,6 +30,19 @@ inline int launch_status() {
   return 0;
 }
 
+// Number of SMs of the current device (cached per device ordinal; 148 if the query fails).
+inline int sm_count_current() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cache[dev];
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev] = n;     // benign race: every writer stores the same value
+  }
+  return n;
+}
+
 constexpr int kChunk = 2048;   // checkpoint spacing of the x tensor (timesteps)
 constexpr int kMaxDState = 256;
 constexpr float kLog2e = 1.4426950408889634f;

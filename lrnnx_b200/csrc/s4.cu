@@ -15,6 +15,7 @@
 // the sequence); threads stride over the chunk with TN complex accumulators each; CTA
 // partials go to a scratch buffer and a second kernel folds the chunks in order.
 #include "common.cuh"
+#include <atomic>
 #include "dispatch.h"
 
 namespace b200 {
@@ -196,7 +197,7 @@ __global__ void s4_bwd_fold_kernel(const cf *__restrict__ v, const cf *__restric
 
 int chunking(int batch, int n, int L, int &l_chunk) {
   const int64_t tiles = (int64_t)batch * ((n + TN - 1) / TN);
-  int want = (int)((148 * 4 + tiles - 1) / tiles);          // enough CTAs to fill the GPU
+  int want = (int)((sm_count_current() * 4 + tiles - 1) / tiles);          // enough CTAs to fill the GPU
   const int max_chunks = (L + 1023) / 1024;                 // at least 1024 positions per CTA
   if (want > max_chunks) want = max_chunks;
   if (want < 1) want = 1;
@@ -279,23 +280,23 @@ static __device__ __align__(256) unsigned char g_cauchy_static_scratch[B200_CAUC
 
 // In host code the array's name is only a handle; the device address has to be
 // asked for, per device, with that device current.
-static void *g_static_scratch_ptr[64] = {};
+static std::atomic<void *> g_static_scratch_ptr[64];
 
 static int static_scratch_for_current_device(void **out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { set_error("cudaGetDevice: %s", cudaGetErrorString(e)); return (int)e; }
   B200_REQUIRE(dev >= 0 && dev < 64, B200_ERR_UNSUPPORTED, "cauchy_bwd_static: device ordinal %d not supported", dev);
-  if (!g_static_scratch_ptr[dev]) {
-    void *ptr = nullptr;
+  void *ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     e = cudaGetSymbolAddress(&ptr, g_cauchy_static_scratch);
     if (e != cudaSuccess || !ptr) {
       set_error("cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
       return e != cudaSuccess ? (int)e : B200_ERR_UNSUPPORTED;
     }
-    g_static_scratch_ptr[dev] = ptr;
+    g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);   // same value from every thread
   }
-  *out = g_static_scratch_ptr[dev];
+  *out = ptr;
   return 0;
 }
 

@@ -45,13 +45,16 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   const float *psrc = reinterpret_cast<const float *>(q.p_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
   float amax = -INFINITY;            // slowest decay of the row
   float hmax = 0.f;
+  bool bad = false;                  // a non-finite incoming state: fmaxf drops NaN, so it is tracked apart
   for (int n = lane; n < N; n += 32) {
     const float a = A[(int64_t)n * p.A_ns];
     A2[n] = a * kLog2e;
     hin[n] = hsrc[n];
     amax = fmaxf(amax, a * kLog2e);
     hmax = fmaxf(hmax, fabsf(hsrc[n]));
+    bad |= !(fabsf(hsrc[n]) <= 3.4e38f);
   }
+  bad = __any_sync(0xffffffffu, bad);
   hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 16));
   hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 8));
   hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, 4));
@@ -76,8 +79,9 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_kernel(const b200_sels
   const int64_t c_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
   const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
   float carry = 0.f;                 // sum of delta' over the steps already processed
-  const float cutoff = dt == B200_F32 ? -32.f : -14.f;
-  if (hmax == 0.f) return;           // nothing enters this segment (first segment of the first rank)
+  // a NaN or infinite state reaches every later step of the unsplit scan: no early exit then
+  const float cutoff = bad ? -INFINITY : (dt == B200_F32 ? -32.f : -14.f);
+  if (hmax == 0.f && !bad) return;   // nothing enters this segment (first segment of the first rank)
   const int L = t_end;
   constexpr int K = 4;               // 32-step sub-blocks per iteration (independent loads and scans in flight)
   for (int t0 = t_begin; t0 < L; t0 += 32 * K) {
@@ -205,13 +209,16 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_vec_kernel(const b200_
   const float *hsrc = reinterpret_cast<const float *>(q.h_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
   const float *psrc = reinterpret_cast<const float *>(q.p_in) + ((int64_t)seg * p.batch * p.dim + row) * N;
   float amax = -INFINITY, hmax = 0.f;
+  bool bad = false;                  // a non-finite incoming state: fmaxf drops NaN, so it is tracked apart
   for (int n = lane; n < N; n += 32) {
     const float a = A[(int64_t)n * p.A_ns];
     A2[n] = a * kLog2e;
     hin[n] = hsrc[n];
     amax = fmaxf(amax, a * kLog2e);
     hmax = fmaxf(hmax, fabsf(hsrc[n]));
+    bad |= !(fabsf(hsrc[n]) <= 3.4e38f);
   }
+  bad = __any_sync(0xffffffffu, bad);
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) {
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
@@ -226,14 +233,15 @@ __global__ void __launch_bounds__(SPW * 32) selscan_fixup_vec_kernel(const b200_
     xrow[(int64_t)c * 2 * N + 2 * n + 1] += P * hin[n];
     xrow[(int64_t)c * 2 * N + 2 * n] = P * psrc[n];
   }
-  if (hmax == 0.f) return;           // nothing enters this segment
+  if (hmax == 0.f && !bad) return;   // nothing enters this segment
   const T *dl = reinterpret_cast<const T *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
   const T *Cg = reinterpret_cast<const T *>(p.C) + (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
   T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
   const T *zr = p.z ? reinterpret_cast<const T *>(p.z) + (int64_t)b * p.z_bs + (int64_t)d * p.z_ds : nullptr;
   T *oz = p.z ? reinterpret_cast<T *>(p.out_z) + (int64_t)b * p.out_z_bs + (int64_t)d * p.out_z_ds : nullptr;
   const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
-  const float cutoff = sizeof(T) == 4 ? -32.f : -14.f;
+  // a NaN or infinite state reaches every later step of the unsplit scan: no early exit then
+  const float cutoff = bad ? -INFINITY : (sizeof(T) == 4 ? -32.f : -14.f);
   float carry = 0.f;                 // sum of delta' over the steps already processed (warp-uniform)
   for (int t0 = t_begin; t0 < L; t0 += 256) {
     if (amax * carry < cutoff) break;   // every state has decayed away

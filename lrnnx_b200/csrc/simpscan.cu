@@ -1198,15 +1198,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
   if (failed) atomicExch(&g_simpscan_status, 4);
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return sm_count_current(); }
 
 template <typename K> int set_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) {

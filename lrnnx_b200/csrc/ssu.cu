@@ -416,6 +416,7 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
   Pos cur = first_pos();
   const bool plain_exp = p.method == B200_DISC_MAMBA || p.method == B200_DISC_DIRAC;
   bool failed = false;
+  int fail_it = 0;
   for (int it = 0; it < my; ++it) {
     unsigned char *s = smem + (size_t)(it % TNS) * SL::SIZE;
     const Tile t = tile_of(cur, false);
@@ -487,7 +488,13 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
       stt<XT>(s + SL::OFF_OUT, rowA, out);
     }
     fence_proxy_async();
-    __syncthreads();
+    // A tile whose loads did not arrive holds garbage: nothing of it may reach the caller's state
+    // (updated in place) or out.  Every thread leaves the loop together; no store, no new load.
+    if (__syncthreads_or(failed ? 1 : 0)) {
+      failed = true;
+      fail_it = it;
+      break;
+    }
     if (tid == 0) {
       const Tile ts = tile_of(cur, true);
       bulk_s2g(reinterpret_cast<unsigned char *>(p.state) +
@@ -502,19 +509,19 @@ __global__ void __launch_bounds__(TT, 4) ssu_tma_kernel(const b200_ssu_args p, i
     }
     advance(cur);
   }
-  if (tid == 0) bulk_wait<0>();
-  if (failed) atomicExch(&g_ssu_status, 3);
+  if (tid == 0) {
+    bulk_wait<0>();      // stores of the tiles completed before a failure, or of the last tiles
+    if (failed) {
+      // loads still in flight into this CTA's slots: give each a last bounded wait before the CTA
+      // (and its shared memory) goes away
+      for (int k = fail_it + 1; k < my && k < fail_it + TNS - 1; ++k)
+        mbar_wait(&full[k % TNS], (uint32_t)(k / TNS) & 1u, 1u << 20);
+      atomicExch(&g_ssu_status, 3);
+    }
+  }
 }
 
-int ssu_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+int ssu_sm_count() { return sm_count_current(); }
 
 template <typename ST, typename XT, int LPR> int launch_tma_l(const b200_ssu_args &a, cudaStream_t st) {
   using SL = TmaSlot<ST, XT, LPR>;
@@ -595,6 +602,11 @@ extern "C" int b200_ssu_step(const b200_ssu_args *args, void *stream) {
                "ssu_step: sizes must be positive");
   B200_REQUIRE(a.nheads % a.ngroups == 0, B200_ERR_SHAPE, "nheads must be divisible by ngroups");
   B200_REQUIRE(a.method >= B200_DISC_ZOH && a.method <= B200_DISC_S7, B200_ERR_DTYPE, "ssu_step: unknown discretization");
+  // lrnnx's Triton kernel (selective_state_update.py:168-176) and its selective_state_update_ref
+  // (:551-553) give different transitions for "s7" with deltaA (exp(A deltaA) against the S7
+  // formula of dt), and no lrnnx layer passes both: the combination is refused.
+  B200_REQUIRE(!(a.method == B200_DISC_S7 && a.deltaA), B200_ERR_UNSUPPORTED,
+               "ssu_step: deltaA is not defined for the s7 discretization");
   B200_REQUIRE(dtype_ok(a.state_dtype) && dtype_ok(a.x_dtype) && dtype_ok(a.dt_dtype) && dtype_ok(a.A_dtype) &&
                    dtype_ok(a.bc_dtype),
                B200_ERR_DTYPE, "ssu_step: unknown dtype");

@@ -111,15 +111,20 @@ def selective_scan_oracle(u, delta, A, B, C, D=None, z=None, delta_bias=None, de
     h = torch.zeros(batch, dim, N, dtype=wdt)          # state without a constant B
     prod = torch.ones(batch, dim, N, dtype=wdt)
     ys, ckpt = [], []
+    # per-timestep views taken once (unbind has a single stacked backward; indexing inside the
+    # loop would materialise a full-size zero tensor per step under autograd)
+    dl_t, dlA_t, u_t = dl.unbind(-1), dlA.unbind(-1), uf.unbind(-1)
+    B_t = Bw.unbind(-1) if var_B else None
+    C_t = Cw.unbind(-1) if var_C else None
     for t in range(L):
-        a, k = _discretize(discretization, Aw, dl[:, :, t], dlA[:, :, t])
-        beta = k * uf[:, :, t].unsqueeze(-1)
+        a, k = _discretize(discretization, Aw, dl_t[t], dlA_t[t])
+        beta = k * u_t[t].unsqueeze(-1)
         if var_B and not ignore_B:
-            beta = beta * Bw[:, :, :, t]
+            beta = beta * B_t[t]
         h = a * h + beta
         if return_checkpoints:
             prod = prod * a
-        cfac = Cw[:, :, :, t] if var_C else Cw
+        cfac = C_t[t] if var_C else Cw
         if not var_B:
             cfac = cfac * Bw
         y = (h * cfac).sum(-1)

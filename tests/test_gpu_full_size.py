@@ -53,6 +53,37 @@ def test_config1_full_size_linearity_and_rows():
         assert_close(y1[bb:bb + 1, pp:pp + 1].cpu(), yo, rtol=1e-3, atol_scale=2e-4, name=f"row {bb},{pp}")
 
 
+def test_config1_full_size_backward_rows_vs_float64():
+    """Rows of the full-size backward against float64 autograd through the oracle (rows are
+    independent; dA[p] sums the batch, so all 8 rows of one state index are evaluated for it).
+    Both backward kernels: recomputing from the checkpoints, and from the forward output."""
+    from lrnnx_b200 import simplified_scan_cuda as ext
+    t = _cfg1()
+    g = torch.Generator().manual_seed(2)
+    dout = torch.complex(torch.randn(t["u"].shape, generator=g), torch.randn(t["u"].shape, generator=g)).cuda()
+    out, x = ext.fwd(t["u"], t["delta"], t["A"], t["one"], t["one"], None, "dirac")
+    cd = torch.complex128
+    one = torch.ones(1, 1, dtype=cd)
+
+    def rows64(bs, pp):
+        u = t["u"][bs, pp:pp + 1].cpu().to(cd).requires_grad_(True)
+        d = t["delta"][bs, pp:pp + 1].cpu().double().requires_grad_(True)
+        A = t["A"][pp:pp + 1].cpu().to(cd).requires_grad_(True)
+        y = O.simplified_kernel_oracle(u, d, A, one, one, None, "dirac", compute_dtype=torch.float64)
+        return torch.autograd.grad(y, [u, d, A], dout[bs, pp:pp + 1].cpu().to(cd))
+
+    for out_arg in (None, out):
+        du, ddelta, dA = ext.bwd(t["u"], t["delta"], t["A"], t["one"], t["one"], None, dout, x, "dirac", out_=out_arg)[:3]
+        for bb, pp in [(0, 0), (3, 117), (7, 255)]:
+            du64, dd64, _ = rows64(slice(bb, bb + 1), pp)
+            assert_close(du[bb:bb + 1, pp:pp + 1].cpu(), du64.to(torch.complex64), rtol=1e-3, atol_scale=2e-4,
+                         name=f"du row {bb},{pp}")
+            assert_close(ddelta[bb:bb + 1, pp:pp + 1].cpu(), dd64.float(), rtol=1e-3, atol_scale=2e-4,
+                         name=f"ddelta row {bb},{pp}")
+        _, _, dA64 = rows64(slice(0, 8), 117)
+        assert_close(dA[117:118].cpu(), dA64.to(torch.complex64), rtol=1e-3, atol_scale=2e-4, name="dA[117]")
+
+
 def test_config1_full_size_time_shift():
     from lrnnx_b200 import simplified_scan_cuda as ext
     t = _cfg1(batch=2)

@@ -208,3 +208,16 @@ def test_s5_step_shapes(H, P):
     out_g = simplified_state_update(st, **{k: v.cuda() for k, v in t.items()}, discretization="zoh")
     assert_close(out_g.cpu(), out_c, rtol=1e-4, atol_scale=2e-5, name="out")
     assert_close(st.cpu(), ref_state, rtol=1e-4, atol_scale=1e-5, name="state")
+
+
+def test_s7_with_deltaA_is_refused():
+    """lrnnx's Triton kernel and its selective_state_update_ref disagree on "s7" + deltaA
+    (selective_state_update.py:168-176 against :551-553); the combination is rejected."""
+    from lrnnx_b200.ops import selective_state_update
+    t = _inputs(2, 128, 16, seed=1, itype=torch.float32, stype=torch.float32, heads=None, ngroups=1)
+    args = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items() if k != "state"}
+    state = t["state"].cuda()
+    before = state.clone()
+    with pytest.raises(RuntimeError, match="deltaA is not defined for the s7"):
+        selective_state_update(state, **args, deltaA=torch.rand_like(args["x"]), discretization="s7")
+    assert torch.equal(state, before)
