@@ -23,8 +23,17 @@ x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
   cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch scan) timed on the
              host cores on a bounded sample of the same workload.
 
+  workloads  the default run adds one sub-record per further workload of the hot path, each with
+             its own ms_per_step, value, roofline, kernels, e2e and cpu_baseline (fewer steps each,
+             so that the whole run stays within a few minutes): s6_cfg0 (configs[0]), s6_layer and
+             s6_layer_f32 (one Mamba layer's scan at the configs[2] shape), s6_long (configs[3];
+             sequence-parallel with a correctness check of the stitched output when N > 1),
+             ssu_step (configs[4] state-update kernels), cauchy, s5_scan_zoh (configs[1] with a
+             time-varying step size) and, when N > 1, s5_strong (configs[1] with its batch of 8
+             split over the ranks: fixed total work).
+
 ``--impl reference`` times that CPU implementation alone (rank 0 only).
-Other workloads (``--workload``): s6_cfg0, s6_layer, s6_layer_f32, s6_long (sequence-parallel when N > 1), ssu_step, cauchy.
+``--workload NAME`` runs one workload alone as the top-level line (no ``workloads`` key).
 """
 from __future__ import annotations
 
@@ -118,19 +127,26 @@ def cn(g, *shape):
 
 # --------------------------------------------------------------------------- workloads
 class S5Scan:
-    """BASELINE config 1."""
-    name = "s5_scan_cfg1"
+    """BASELINE config 1 (and its variants: time-varying step size, batch split over the ranks)."""
     dtype = "c64"
     metric, unit = "scan tokens/s (simplified scan fwd+bwd)", "tokens/s"
 
-    def __init__(self, batch=8, P=256, H=512, L=4096):
-        self.batch, self.P, self.H, self.L = batch, P, H, L
+    def __init__(self, batch=8, P=256, H=512, L=4096, disc="dirac", name="s5_scan_cfg1", strong=False, cpu_full=True):
+        self.batch, self.P, self.H, self.L, self.disc, self.name = batch, P, H, L, disc, name
+        self.strong, self.cpu_full = strong, cpu_full
+        self._set_sizes()
+
+    def _set_sizes(self):
+        batch, P, H, L = self.batch, self.P, self.H, self.L
         self.tokens = batch * L
         self.fwd_bytes = 20 * batch * P * L          # u 8 + delta 4 read, out 8 written per (b,p,l)
         self.bwd_bytes = 32 * batch * P * L          # u 8, delta 4, dout 8 read; du 8, ddelta 4 written
-        self.describe = {"workload": f"{self.name}: B={batch} P={P} H={H} L={L} complex64 dirac fwd+bwd",
+        step = "delta = 1" if self.disc == "dirac" else "time-varying delta"
+        self.describe = {"workload": f"{self.name}: B={batch} P={P} H={H} L={L} complex64 {self.disc} ({step}) fwd+bwd",
                          "global_batch": batch, "seq_len": L, "states": P, "channels": H,
-                         "l2": "operands of every kernel exceed the 126 MB L2 (fwd 168 MB, bwd 268 MB)"}
+                         "l2": "operands of every kernel exceed the 126 MB L2 (fwd 168 MB, bwd 268 MB)"
+                         if self.fwd_bytes > 1.3e8 else "L2 flushed by a 256 MB write between timed iterations"}
+        self.flush = self.fwd_bytes <= 1.3e8
 
     def host_inputs(self, seed=0, batch=None, L=None):
         g = torch.Generator().manual_seed(seed)
@@ -140,7 +156,10 @@ class S5Scan:
         B = cn(g, self.P, self.H) / math.sqrt(self.H)
         C = cn(g, self.H, self.P) / math.sqrt(self.P)
         u = torch.randn(batch, L, self.H, generator=g).transpose(1, 2).to(torch.complex64).contiguous()
-        delta = torch.ones(batch, self.P, L)
+        if self.disc == "dirac":
+            delta = torch.ones(batch, self.P, L)
+        else:      # the time-varying step sizes an LTV-S5 layer feeds (lrnnx/models/ltv/s5.py:113-115)
+            delta = 0.5 + torch.rand(batch, self.P, L, generator=g)
         gout = cn(g, batch, self.H, L)
         return dict(u=u, delta=delta, A=A, B=B, C=C, gout=gout)
 
@@ -148,7 +167,16 @@ class S5Scan:
         from lrnnx_b200 import simplified_scan_cuda
         from lrnnx_b200.ops import simplified_scan_fn
         self.dev, self.pg = dev, pg
+        if self.strong and pg is not None:
+            # fixed total work: the batch of 8 rows is split over the ranks (batch x state rows are
+            # independent recurrences; only dA is reduced)
+            w = torch.distributed.get_world_size()
+            self.batch = max(1, self.batch // w)
+            self._set_sizes()
+            self.scaling = "strong"
+            self.describe["parallelism"] = f"batch of {self.batch * w} split over {w} GPUs ({self.batch} per GPU)"
         h = self.host_inputs()
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
         self.h_x = h["u"].real.transpose(1, 2).contiguous().pin_memory()      # (batch, L, H) float32: the layer's input
         self.h_delta, self.h_gout = h["delta"].pin_memory(), h["gout"].pin_memory()
         self.A, self.B, self.C = (h[k].to(dev) for k in ("A", "B", "C"))
@@ -173,20 +201,22 @@ class S5Scan:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                out, x = self.ext.fwd(*args, "dirac")
-                self.ext.bwd(*args, self.dBu_in, x, "dirac", need_dB_dC=False, out_=out)
+                out, x = self.ext.fwd(*args, self.disc)
+                self.ext.bwd(*args, self.dBu_in, x, self.disc, need_dB_dC=False, out_=out)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.g_fwd, self.g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.g_fwd):
-            self.out, self.x = self.ext.fwd(*args, "dirac")
+            self.out, self.x = self.ext.fwd(*args, self.disc)
         with torch.cuda.graph(self.g_bwd):
             # as SimplifiedScanFn.backward calls it (identity B and C: dB / dC are not needed, and the
             # forward output, which is the state sequence, is handed back)
-            self.res = self.ext.bwd(*args, self.dBu_in, self.x, "dirac", need_dB_dC=False, out_=self.out)
+            self.res = self.ext.bwd(*args, self.dBu_in, self.x, self.disc, need_dB_dC=False, out_=self.out)
 
     def step(self, record=False):
         """forward + backward scan kernels through the extension entry points (graph replay)."""
+        if self.flush_buf is not None:
+            self.flush_buf.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
@@ -242,7 +272,7 @@ class S5Scan:
             cur.wait_event(evs[i])
             u = self.d_x[sl].transpose(1, 2).contiguous().to(torch.complex64).requires_grad_(True)
             delta = self.d_delta[sl].detach().requires_grad_(True)
-            y = self.op(u, delta, A, B, C, discretization="dirac")
+            y = self.op(u, delta, A, B, C, discretization=self.disc)
             loss = (y * self.gout[sl].conj()).real.sum()
             loss.backward()
             total += loss.detach()
@@ -260,18 +290,24 @@ class S5Scan:
         return {"simpscan_fwd_kernel": (self.fwd_bytes, statistics.mean(f)),
                 "simpscan_bwd_kernel": (self.bwd_bytes, statistics.mean(b))}
 
-    # CPU arm: batch 1, first 1024 steps, same P and H (per-token work unchanged)
-    cpu_sample = "the full workload: batch 8, 4096 timesteps, P=256, H=512"
+    # CPU arm: the full workload for the headline line; batch 1 and the first 1024 steps (same P
+    # and H: the work per token is unchanged) for the sub-records
+    @property
+    def cpu_sample(self):
+        if self.cpu_full:
+            return f"the full workload: batch {self.batch}, {self.L} timesteps, P={self.P}, H={self.H}"
+        return f"batch 1, first 1024 of {self.L} timesteps, P={self.P}, H={self.H}"
 
     def cpu_step(self):
         from oracle import scan_oracle as O
+        cb, cl = (self.batch, self.L) if self.cpu_full else (1, min(self.L, 1024))
         if not hasattr(self, "_cpu"):
-            self._cpu = self.host_inputs()
+            self._cpu = self.host_inputs(batch=cb, L=cl)
         h = self._cpu
         leaves = [h[k].clone().requires_grad_(True) for k in ("u", "delta", "A", "B", "C")]
-        y = O.simplified_scan_oracle(*leaves, discretization="dirac")
+        y = O.simplified_scan_oracle(*leaves, discretization=self.disc)
         torch.autograd.grad(y, leaves, h["gout"])
-        return self.batch * self.L
+        return cb * cl
 
 
 class S6Scan:
@@ -325,6 +361,9 @@ class S6Scan:
             self.scaling = "strong"
             r, w = dist.get_rank(), dist.get_world_size()
             lo, hi = (r * self.L // w) // 8 * 8, ((r + 1) * self.L // w) // 8 * 8 if r + 1 < w else self.L
+            if r == 0:   # 16 channels over the full sequence, for the check of the stitched result
+                self._chk = {k: (v[:, :16].clone() if v.dim() == 3 else (v.clone() if v.dim() == 4 else v[:16].clone()))
+                             for k, v in h.items()}
             h = {k: (v[..., lo:hi].contiguous() if v.dim() >= 3 else v) for k, v in h.items()}
             self.describe["parallelism"] = f"sequence-parallel over {w} GPUs: chunk-state all-gather + fix-up"
             self.fwd_bytes //= w
@@ -405,6 +444,28 @@ class S6Scan:
         if self.pg is not None and res is not None:
             torch.distributed.all_reduce(res[2], group=self.pg)
         return res
+
+    def sp_check(self):
+        """Sequence-parallel run only: the stitched gated output of 16 channels, gathered from all
+        ranks, against the unsplit forward of those channels on rank 0.  Returns the record on
+        rank 0 (None elsewhere)."""
+        import torch.distributed as dist
+        t = self.t
+        y, _ = self.sp_fwd(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["z"], t["delta_bias"], True, self.pg)
+        mine = y[:, :16].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(parts, mine, group=self.pg)
+        if dist.get_rank() != 0:
+            return None
+        c = {k: v.to(self.dev) for k, v in self._chk.items()}
+        ref = self.ext.fwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"], None, True,
+                           "mamba")[2].float()
+        got = torch.cat(parts, dim=-1).float()
+        scale = float(ref.abs().max())
+        err = (got - ref).abs()
+        ok = bool((err <= 1e-2 * scale + 3e-2 * ref.abs()).all())
+        return {"channels": 16, "max_abs_err": float(err.max()), "max_rel_err": float(err.max()) / scale, "ok": ok,
+                "tolerance": "|d| <= 1e-2 max|ref| + 3e-2 |ref| (bf16 outputs)"}
 
     def e2e_step(self):
         if not self.sp and self.batch % 4 == 0:
@@ -627,10 +688,17 @@ class CauchyKernel:
     def e2e_bytes(self):
         return sum(self.h[k].numel() * 8 for k in ("v", "w", "z")), 4
 
+    # fp32 operations per (row, frequency, pole pair): two terms v / (z - w), each a complex
+    # subtraction (2), |d|^2 (3), a reciprocal (1), two scalings (2), a complex product (6) and a
+    # complex accumulation (2); the backward evaluates 1/d and 1/d^2 terms for dv and dw: twice that
+    FLOP_FWD, FLOP_BWD = 32, 64
+
     def kernel_rooflines(self):
         f = [a[0].elapsed_time(a[1]) for a in self.ev]
         b = [a[1].elapsed_time(a[2]) for a in self.ev]
-        return {"cauchy_fwd": (self.fwd_bytes, statistics.mean(f)), "cauchy_bwd": (self.bwd_bytes, statistics.mean(b))}
+        terms = self.rows * self.L * self.n
+        return {"cauchy_fwd": (self.fwd_bytes, statistics.mean(f), {"flops": self.FLOP_FWD * terms}),
+                "cauchy_bwd": (self.bwd_bytes, statistics.mean(b), {"flops": self.FLOP_BWD * terms})}
 
     cpu_sample = "64 of 1024 rows, all 16384 frequencies"
 
@@ -645,9 +713,14 @@ class CauchyKernel:
         return 64 * self.L
 
 
-def make_workload(name):
+def make_workload(name, sub=False):
+    """``sub``: the workload is a sub-record of the default run (bounded CPU sample)."""
     if name in ("s5_scan", "s5_scan_cfg1", "default"):
-        return S5Scan()
+        return S5Scan(cpu_full=not sub)
+    if name == "s5_scan_zoh":
+        return S5Scan(disc="zoh", name="s5_scan_zoh", cpu_full=False)
+    if name == "s5_strong":
+        return S5Scan(name="s5_strong_cfg1", strong=True, cpu_full=False)
     if name == "s6_cfg0":
         return S6Scan("s6_cfg0", 2, 256, 512, 16, torch.float32)
     if name == "s6_layer":
@@ -661,6 +734,12 @@ def make_workload(name):
     if name in ("cauchy", "cauchy_s4"):
         return CauchyKernel()
     raise SystemExit(f"unknown workload {name}")
+
+
+SUB_WORKLOADS = ("s6_cfg0", "s6_layer", "s6_layer_f32", "s6_long", "ssu_step", "cauchy", "s5_scan_zoh")
+
+# nominal fp32 rate of one B200: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz (no measured figure exists)
+FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 # --------------------------------------------------------------------------- arms
@@ -692,18 +771,8 @@ def run_reference(args, wl):
     print(json.dumps(line))
 
 
-def run_ours(args, wl):
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    pg = None
-    if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=dev)
-        pg = torch.distributed.group.WORLD
+def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
+    """Set up one workload and time it; returns its record on rank 0 (None on the other ranks)."""
     wl.setup(dev, pg)
 
     def barrier():
@@ -711,13 +780,13 @@ def run_ours(args, wl):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, record=False):
-        for _ in range(warmup):
+    def timed(fn, n, w, record=False):
+        for _ in range(w):
             fn()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(n):
             fn(record=True) if record else fn()
         drain = getattr(wl, "drain", None)
         if drain is not None:
@@ -729,49 +798,107 @@ def run_ours(args, wl):
             t = torch.tensor([ms], device=dev)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             ms = float(t.item())
-        return ms / steps
+        return ms / n
 
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(local) if (rank == 0 and sample_clocks) else None
     if sampler:
         sampler.start()
-    ms_step = timed(wl.step, args.steps, args.warmup, record=True)
-    # separate pass without per-kernel events inside the loop is not needed: events cost ~1 us
+    ms_step = timed(wl.step, steps, warmup, record=True)
     clocks = sampler.stop() if sampler else None
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(steps, 10))
     ms_e2e = timed(wl.e2e_step, e2e_steps, 3)
+    check = wl.sp_check() if getattr(wl, "sp", False) else None
+    if rank != 0:
+        return None
 
+    peak, peak_kind = measured_peaks()
+    roofs = {}
+    for kname, item in wl.kernel_rooflines().items():
+        nbytes, ms = item[0], item[1]
+        extra = item[2] if len(item) > 2 else {}
+        ach = nbytes / (ms * 1e-3) / 1e9
+        roofs[kname] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                        "traffic": NCU_TRAFFIC.get((wl.name, kname)), "algorithmic_bytes": nbytes,
+                        "ms_per_launch": ms, "peak_source": peak_kind}
+        if "flops" in extra:     # a kernel bound by the fp32 pipe: the fraction is of the fp32 rate
+            tf = extra["flops"] / (ms * 1e-3) / 1e12
+            roofs[kname].update({"bound": "fp32", "achieved": tf, "peak": FP32_PEAK_TFLOPS, "unit": "TFLOP/s",
+                                 "frac": tf / FP32_PEAK_TFLOPS, "algorithmic_flops": extra["flops"],
+                                 "peak_source": "nominal: 148 SMs x 128 lanes x 2 x 1.965 GHz", "hbm_frac": ach / peak})
+        note = getattr(wl, "roofline_note", None)
+        if note:
+            roofs[kname]["note"] = note
+    dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
+    cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
+    h2d, d2h = wl.e2e_bytes()
+    strong = getattr(wl, "scaling", "weak") == "strong"
+    total_tokens = wl.tokens * (1 if (strong and getattr(wl, "sp", False)) else world)
+    describe = dict(wl.describe)
+    if "global_batch" in describe and not getattr(wl, "sp", False):
+        describe["global_batch"] = describe["global_batch"] * world     # every rank runs its own batch shard
+    rec = {"metric": wl.metric, "value": total_tokens / (ms_step * 1e-3), "unit": wl.unit,
+           "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+           "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+           "dtype": wl.dtype,
+           "data": "synthetic (seeded CPU generator, copied to the GPU)", "config": describe,
+           "clocks": clocks,
+           "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": wl.unit, "ms_per_step": ms_e2e,
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+           "gpu_launches": wl.launches_per_step * steps,
+           "roofline": dict(roofs[dominant], kernel=dominant),
+           "kernels": roofs,
+           "cpu_baseline": {"value": cpu_tps, "unit": wl.unit, "cores": torch.get_num_threads(),
+                            "kind": "port", "sample": wl.cpu_sample, "seconds": cpu_sec}}
+    if check is not None:
+        rec["sp_check"] = check
+    return rec
+
+
+def run_ours(args, wl, with_subs):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    pg = None
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+        pg = torch.distributed.group.WORLD
+    line = measure(wl, args.steps, args.warmup, world, rank, local, dev, pg)
+    failed = False
+    if with_subs:
+        subs = {}
+        names = SUB_WORKLOADS + (("s5_strong",) if world > 1 else ())
+        del wl
+        for name in names:
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            sub = make_workload(name, sub=True)
+            rec = measure(sub, max(3, min(args.steps, 10)), 3, world, rank, local, dev, pg, sample_clocks=True)
+            if rec is not None:
+                # a sub-record keeps what differs from the top-level line
+                for k in ("higher_is_better", "vs_baseline", "data", "n_gpus"):
+                    rec.pop(k, None)
+                subs[name] = rec
+                if rec.get("sp_check") is not None and not rec["sp_check"]["ok"]:
+                    failed = True
+            del sub
+        if rank == 0:
+            line["workloads"] = subs
+    elif rank == 0 and line.get("sp_check") is not None and not line["sp_check"]["ok"]:
+        failed = True
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        roofs = {}
-        for kname, (nbytes, ms) in wl.kernel_rooflines().items():
-            ach = nbytes / (ms * 1e-3) / 1e9
-            roofs[kname] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                            "traffic": NCU_TRAFFIC.get((wl.name, kname)), "algorithmic_bytes": nbytes,
-                            "ms_per_launch": ms,
-                            "peak_source": peak_kind}
-            note = getattr(wl, "roofline_note", None)
-            if note:
-                roofs[kname]["note"] = note
-        dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
-        cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
-        h2d, d2h = wl.e2e_bytes()
-        total_tokens = wl.tokens if getattr(wl, "scaling", "weak") == "strong" else world * wl.tokens
-        line = {"metric": wl.metric, "value": total_tokens / (ms_step * 1e-3), "unit": wl.unit,
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-                "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
-                "dtype": wl.dtype,
-                "data": "synthetic (seeded CPU generator, copied to the GPU)", "config": wl.describe,
-                "clocks": clocks,
-                "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": wl.unit, "ms_per_step": ms_e2e,
-                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-                "gpu_launches": wl.launches_per_step * args.steps,
-                "roofline": dict(roofs[dominant], kernel=dominant),
-                "kernels": roofs,
-                "cpu_baseline": {"value": cpu_tps, "unit": wl.unit, "cores": torch.get_num_threads(),
-                                 "kind": "port", "sample": wl.cpu_sample, "seconds": cpu_sec}}
         print(json.dumps(line))
     if world > 1:
+        flag = torch.tensor([1 if failed else 0], device=dev)
+        torch.distributed.broadcast(flag, 0)
+        failed = bool(flag.item())
         torch.distributed.destroy_process_group()
+    if failed:
+        raise SystemExit("bench.py: the sequence-parallel output differs from the unsplit forward (sp_check)")
 
 
 def main():
@@ -779,15 +906,15 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="s5_scan_cfg1")
+    ap.add_argument("--workload", default=None, help="run one workload alone (default: configs[1] plus the sub-records)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = make_workload(args.workload)
+    wl = make_workload(args.workload or "s5_scan_cfg1")
     if args.impl == "reference":
         run_reference(args, wl)
     else:
-        run_ours(args, wl)
+        run_ours(args, wl, with_subs=args.workload is None)
 
 
 if __name__ == "__main__":

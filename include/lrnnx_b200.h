@@ -79,19 +79,22 @@ typedef struct b200_selscan_fwd_args {
                                scanned from a zero state by its own thread blocks (more parallelism for
                                long rows); out, out_z and x of segments >= 1 are then zero-start results
                                that the caller must stitch with b200_selscan_fixup (n_segments = S).
-                               Honoured only on the shape class served by the throughput kernel,
+                               Honoured only on the shape class served by the throughput kernels,
                                rejected with B200_ERR_UNSUPPORTED elsewhere. */
+  int32_t stage_len;        /* spacing in steps of the states in stage_h: the value returned by
+                               b200_selscan_stage_states() for this problem (0 when stage_h is NULL) */
+  int32_t reserved0;
   const void *u, *delta, *A, *B, *C;
   const void *D, *z, *delta_bias, *deltaA;      /* nullable */
   void *out;                                    /* (batch, dim, seqlen) */
   void *out_z;                                  /* required iff z != NULL */
   void *x;                                      /* required */
   void *stage_h;                                /* nullable; no counterpart in the reference.  (batch, dim,
-                                                   ceil(seqlen/256), dstate) float32: the state at the end of
-                                                   every 256-step stage.  Written by the forward call and read
-                                                   by the backward call (which then skips its recomputation
-                                                   of these states) only where b200_selscan_stage_states()
-                                                   says so; ignored otherwise. */
+                                                   ceil(seqlen/stage_len), dstate) float32, 16-byte aligned: the
+                                                   state at the end of every stage of stage_len steps.  Written
+                                                   by the forward call and read by the backward call (which then
+                                                   skips its recomputation of these states) only where
+                                                   b200_selscan_stage_states() says so; ignored otherwise. */
   int64_t u_bs, u_ds;
   int64_t delta_bs, delta_ds;
   int64_t z_bs, z_ds;
@@ -105,9 +108,11 @@ typedef struct b200_selscan_fwd_args {
 
 int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream);
 
-/* 1 if b200_selscan_fwd with these arguments (stage_h aside) would write stage_h and
- * b200_selscan_bwd on the same problem would read it, else 0: true on the shape class of the
- * throughput kernels with l_segments <= 1. */
+/* Stage spacing (in steps) with which b200_selscan_fwd with these arguments (stage_h and
+ * stage_len aside) would write stage_h and b200_selscan_bwd on the same problem would read it;
+ * 0 if stage states are not used for this problem.  Non-zero on the shape class of the throughput
+ * kernels with l_segments <= 1: 32 for the streaming kernels (enough rows to fill the GPU with
+ * one warp per 16 channels), 256 for the lane-scan kernels. */
 int b200_selscan_stage_states(const b200_selscan_fwd_args *args);
 
 /* ------------------------------------------------------------------------
@@ -319,6 +324,65 @@ int b200_cauchy_bwd(const b200_s4_args *args, void *stream);
 int b200_cauchy_bwd_static(const b200_s4_args *args, void *stream);
 int b200_vand_fwd(const b200_s4_args *args, void *stream);
 int b200_vand_bwd(const b200_s4_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Depthwise causal convolution of a Mamba block (+ optional SiLU), its backward, and the
+ * one-token update used in decoding.  Replace the nn.Conv1d(groups=d_inner, padding=width-1)
+ * fallback of lrnnx/models/ltv/mamba.py:270-279 (forward), its autograd backward, and the
+ * roll + dot of Mamba.step (lrnnx/models/ltv/mamba.py:394-409); lrnnx's own fast path for them
+ * is the un-vendored causal_conv1d package (mamba.py:24-27).
+ *   x, out, dout, dx : (batch, dim, seqlen) activations dtype, seqlen contiguous (16-byte accesses
+ *                      where a row segment is 16-byte aligned, element accesses otherwise)
+ *   weight (dim, width) and bias (dim, nullable) : activations dtype, dense; width 2..4
+ *   out[b,d,t] = act(bias[d] + sum_k weight[d,k] * x[b,d,t-(width-1)+k]),  x = 0 before t = 0
+ *   dweight (dim, width), dbias (dim) : float32 accumulators, zero-filled by the caller
+ *   update: x, out (batch, dim) with strides x_bs/x_ds, out_bs/out_ds; state (batch, dim, width)
+ *           activations dtype, innermost stride 1, shifted left by one and appended with x in place
+ * ------------------------------------------------------------------------ */
+typedef struct b200_conv1d_args {
+  int32_t batch, dim, seqlen, width;
+  int32_t dtype;              /* B200_F32 / F16 / BF16 */
+  int32_t silu;               /* apply SiLU to the output */
+  const void *x, *weight, *bias;
+  void *out;
+  void *state;                /* update only */
+  const void *dout;           /* backward only */
+  void *dx, *dweight, *dbias; /* backward only */
+  int64_t x_bs, x_ds, out_bs, out_ds, state_bs, state_ds;
+  int64_t dout_bs, dout_ds, dx_bs, dx_ds;
+} b200_conv1d_args;
+
+int b200_conv1d_fwd(const b200_conv1d_args *args, void *stream);
+int b200_conv1d_bwd(const b200_conv1d_args *args, void *stream);
+int b200_conv1d_update(const b200_conv1d_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Fused residual add + RMSNorm, forward and backward.  Replaces rms_norm_fn / layer_norm_fn with
+ * is_rms_norm (lrnnx/ops/triton/layer_norm.py:994-1094) as the LM blocks call it
+ * (lrnnx/layers/block.py:77-87, lrnnx/architectures/language_model.py:374-384):
+ *   z = x + residual (residual nullable);  y = z * rsqrt(mean(z^2) + eps) * weight
+ *   x, y, dy, dx (rows, cols) activations dtype; residual, residual_out, dresidual, dresidual_in
+ *   (rows, cols) in residual_dtype (the activations dtype, or float32 = residual_in_fp32);
+ *   weight (cols) activations dtype; rstd (rows) float32; dweight (cols) float32, zero-filled.
+ *   forward writes y, residual_out (= z, optional) and rstd (optional);
+ *   backward reads dy, residual_out (z), rstd, weight and dresidual (gradient arriving at
+ *   residual_out, nullable), writes dx and (optional) dresidual_in — both equal dz — and adds to dweight.
+ * cols must be a multiple of 8 and at most 4096; every row 16-byte aligned.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_rmsnorm_args {
+  int64_t rows;
+  int32_t cols;
+  int32_t dtype, residual_dtype;
+  float eps;
+  const void *x, *residual, *weight;
+  void *y, *residual_out, *rstd;
+  const void *dy, *dresidual;
+  void *dx, *dresidual_in, *dweight;
+  int64_t x_rs, residual_rs, y_rs, residual_out_rs, dy_rs, dresidual_rs, dx_rs, dresidual_in_rs;
+} b200_rmsnorm_args;
+
+int b200_rmsnorm_fwd(const b200_rmsnorm_args *args, void *stream);
+int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream);
 
 #ifdef __cplusplus
 }

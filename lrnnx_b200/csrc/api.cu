@@ -42,7 +42,7 @@ using namespace b200;
 extern "C" {
 
 const char *b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 3; }
+int b200_abi_version(void) { return 4; }
 
 // size of an argument block as this library was compiled; lets a binding
 // verify its own struct layout before the first call
@@ -55,6 +55,8 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_ssu_args")) return (int)sizeof(b200_ssu_args);
   if (!strcmp(name, "b200_s4_args")) return (int)sizeof(b200_s4_args);
   if (!strcmp(name, "b200_s5_step_args")) return (int)sizeof(b200_s5_step_args);
+  if (!strcmp(name, "b200_conv1d_args")) return (int)sizeof(b200_conv1d_args);
+  if (!strcmp(name, "b200_rmsnorm_args")) return (int)sizeof(b200_rmsnorm_args);
   return -1;
 }
 
@@ -64,15 +66,28 @@ int b200_selscan_fwd(const b200_selscan_fwd_args *args, void *stream) {
   B200_REQUIRE(args->out && args->x, B200_ERR_NULL, "selscan_fwd: out and x must be non-null");
   B200_REQUIRE(!args->z || args->out_z, B200_ERR_NULL, "selscan_fwd: out_z is required when z is given");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (selscan_fwd_fast_supported(*args)) return selscan_fwd_fast(*args, st);
+  // stage states are written only with the spacing the chosen kernel works in
+  b200_selscan_fwd_args a = *args;
+  if (selscan_fwd_sl_supported(a)) {
+    if (a.stage_len != kSlStage) a.stage_h = nullptr;
+    return selscan_fwd_sl(a, st);
+  }
+  if (selscan_fwd_fast_supported(a)) {
+    if (a.stage_len != kFastStage) a.stage_h = nullptr;
+    return selscan_fwd_fast(a, st);
+  }
   B200_REQUIRE(args->l_segments <= 1, B200_ERR_UNSUPPORTED,
                "selscan_fwd: l_segments > 1 is only available on the throughput-kernel shape class");
   return selscan_fwd_generic(*args, st);
 }
 
 int b200_selscan_stage_states(const b200_selscan_fwd_args *args) {
-  if (!args || check_selscan(*args)) return 0;
-  return (args->l_segments <= 1 && selscan_fwd_fast_supported(*args)) ? 1 : 0;
+  if (!args || check_selscan(*args) || args->l_segments > 1) return 0;
+  b200_selscan_fwd_args a = *args;
+  a.stage_h = nullptr;
+  if (selscan_fwd_sl_supported(a)) return kSlStage;
+  if (selscan_fwd_fast_supported(a)) return kFastStage;
+  return 0;
 }
 
 int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream) {
@@ -90,7 +105,12 @@ int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream) {
   B200_REQUIRE(!f.delta_bias || args->ddelta_bias, B200_ERR_NULL,
                "selscan_bwd: ddelta_bias is required when delta_bias is given");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (selscan_bwd_fast_supported(*args)) return selscan_bwd_fast(*args, st);
+  if (selscan_bwd_sl_supported(*args)) return selscan_bwd_sl(*args, st);
+  if (selscan_bwd_fast_supported(*args)) {
+    b200_selscan_bwd_args a = *args;
+    if (a.f.stage_len != kFastStage) a.f.stage_h = nullptr;    // states of another spacing: recompute
+    return selscan_bwd_fast(a, st);
+  }
   return selscan_bwd_generic(*args, st);
 }
 

@@ -1,0 +1,464 @@
+// Elementwise companions of the selective scan inside a Mamba block: the depthwise causal
+// convolution (+ SiLU) before the scan, its one-token update for decoding, and the fused
+// residual-add + RMSNorm before the block.  All three are HBM-bound: every element is read once
+// and written once with 16-byte accesses.
+//   causal conv:  lrnnx/models/ltv/mamba.py:270-279 (nn.Conv1d(groups=d_inner, padding=d_conv-1)
+//                 truncated to L, then SiLU) and :394-409 (roll + dot + SiLU in step());
+//   add + norm:   lrnnx/ops/triton/layer_norm.py:994-1094 (rms_norm_fn with residual, prenorm).
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int CVT = 128;          // threads per CTA of the convolution kernels
+constexpr int CVE = 8;            // timesteps per thread
+constexpr int MAXW = 4;           // widest convolution
+
+template <typename T> __device__ __forceinline__ float tof(T v);
+template <> __device__ __forceinline__ float tof<float>(float v) { return v; }
+template <> __device__ __forceinline__ float tof<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float tof<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T fromf(float v);
+template <> __device__ __forceinline__ float fromf<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 fromf<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half fromf<__half>(float v) { return __float2half_rn(v); }
+
+// 8 consecutive elements of a row starting at t (t a multiple of 8); positions outside [0, L)
+// read as zero.  16-byte accesses where the address allows, element accesses otherwise.
+__device__ __forceinline__ bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+template <typename T> __device__ __forceinline__ void load8(const T *row, int t, int L, float (&v)[CVE]) {
+  if (t >= 0 && t + CVE <= L && al16(row + t)) {
+    if constexpr (sizeof(T) == 2) {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(row + t);
+      const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) v[i] = tof(e[i]);
+    } else {
+      const float4 a = *reinterpret_cast<const float4 *>(row + t), b = *reinterpret_cast<const float4 *>(row + t + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CVE; ++i) v[i] = (t + i >= 0 && t + i < L) ? tof(row[t + i]) : 0.f;
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T *row, int t, int L, const float (&v)[CVE]) {
+  if (t + CVE <= L && al16(row + t)) {
+    if constexpr (sizeof(T) == 2) {
+      uint4 raw;
+      T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) e[i] = fromf<T>(v[i]);
+      *reinterpret_cast<uint4 *>(row + t) = raw;
+    } else {
+      *reinterpret_cast<float4 *>(row + t) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(row + t + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CVE; ++i)
+      if (t + i < L) row[t + i] = fromf<T>(v[i]);
+  }
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoidf_(x); }
+__device__ __forceinline__ float dsilu_f(float x) {
+  const float s = sigmoidf_(x);
+  return s * (1.f + x * (1.f - s));
+}
+
+// out[b, d, t] = act(bias[d] + sum_k w[d, k] x[b, d, t - (W-1) + k])
+template <typename T>
+__global__ void __launch_bounds__(CVT) conv1d_fwd_kernel(const b200_conv1d_args p) {
+  const int row = blockIdx.x;                       // (batch, channel)
+  const int b = row / p.dim, d = row % p.dim;
+  const int t = (blockIdx.y * CVT + threadIdx.x) * CVE;
+  if (t >= p.seqlen) return;
+  const int W = p.width;
+  const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
+  T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  float w[MAXW];
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k) w[k] = k < W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k]) : 0.f;
+  const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
+  float prev[CVE], cur[CVE], y[CVE];
+  load8<T>(x, t - CVE, p.seqlen, prev);
+  load8<T>(x, t, p.seqlen, cur);
+#pragma unroll
+  for (int i = 0; i < CVE; ++i) {
+    float acc = bias;
+#pragma unroll
+    for (int k = 0; k < MAXW; ++k) {
+      if (k < W) {
+        const int j = i - (W - 1) + k;               // offset inside [prev | cur]
+        acc = fmaf(w[k], j >= 0 ? cur[j] : prev[CVE + j], acc);
+      }
+    }
+    y[i] = p.silu ? silu_f(acc) : acc;
+  }
+  store8<T>(out, t, p.seqlen, y);
+}
+
+// dx, and per-thread partial sums of dweight / dbias folded per CTA into float32 accumulators
+template <typename T>
+__global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args p) {
+  const int row = blockIdx.x;
+  const int b = row / p.dim, d = row % p.dim;
+  const int t = (blockIdx.y * CVT + threadIdx.x) * CVE;
+  const int W = p.width, L = p.seqlen;
+  const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
+  const T *dout = reinterpret_cast<const T *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
+  T *dx = reinterpret_cast<T *>(p.dx) + (int64_t)b * p.dx_bs + (int64_t)d * p.dx_ds;
+  float w[MAXW];
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k) w[k] = k < W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k]) : 0.f;
+  const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
+  float dw[MAXW] = {0.f, 0.f, 0.f, 0.f}, db = 0.f;
+  if (t < L) {
+    // x over [t - 8, t + 16), dout over [t, t + 16): the gradient of the pre-activation is needed
+    // for this thread's 8 steps and the W - 1 steps after them
+    float xs[3 * CVE], g[2 * CVE];
+    {
+      float a[CVE];
+      load8<T>(x, t - CVE, L, a);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) xs[i] = a[i];
+      load8<T>(x, t, L, a);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) xs[CVE + i] = a[i];
+      load8<T>(x, t + CVE, L, a);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) xs[2 * CVE + i] = a[i];
+      load8<T>(dout, t, L, a);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) g[i] = a[i];
+      load8<T>(dout, t + CVE, L, a);
+#pragma unroll
+      for (int i = 0; i < CVE; ++i) g[CVE + i] = a[i];
+    }
+    float dpre[CVE + MAXW - 1];
+#pragma unroll
+    for (int i = 0; i < CVE + MAXW - 1; ++i) {
+      float gi = g[i];                                // zero past L
+      if (p.silu) {
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < MAXW; ++k)
+          if (k < W) acc = fmaf(w[k], xs[CVE + i - (W - 1) + k], acc);
+        gi *= dsilu_f(acc);
+      }
+      dpre[i] = gi;
+    }
+    float dxv[CVE];
+#pragma unroll
+    for (int i = 0; i < CVE; ++i) {
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < MAXW; ++k)
+        if (k < W) acc = fmaf(w[k], dpre[i + (W - 1) - k], acc);     // x[t+i] feeds out[t+i+(W-1)-k] through w[k]
+      dxv[i] = acc;
+      db += dpre[i];
+#pragma unroll
+      for (int k = 0; k < MAXW; ++k)
+        if (k < W) dw[k] = fmaf(dpre[i], xs[CVE + i - (W - 1) + k], dw[k]);
+    }
+    store8<T>(dx, t, L, dxv);
+  }
+  // CTA reduction of the parameter gradients, then one atomic per CTA and parameter
+  __shared__ float red[CVT / 32][MAXW + 1];
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k) dw[k] = warp_sum(dw[k]);
+  db = warp_sum(db);
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < MAXW; ++k) red[wp][k] = dw[k];
+    red[wp][MAXW] = db;
+  }
+  __syncthreads();
+  if (threadIdx.x <= MAXW) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < CVT / 32; ++i) s += red[i][threadIdx.x];
+    if (threadIdx.x < W) atomicAdd(reinterpret_cast<float *>(p.dweight) + (int64_t)d * W + threadIdx.x, s);
+    if (threadIdx.x == MAXW && p.dbias) atomicAdd(reinterpret_cast<float *>(p.dbias) + d, s);
+  }
+}
+
+// one token: state <- [state[1:], x]; out = act(bias + sum_k w[k] state[k])
+template <typename T>
+__global__ void __launch_bounds__(256) conv1d_update_kernel(const b200_conv1d_args p) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(i / p.dim), d = (int)(i % p.dim);
+  const int W = p.width;
+  T *st = reinterpret_cast<T *>(p.state) + (int64_t)b * p.state_bs + (int64_t)d * p.state_ds;
+  const float xv = tof(reinterpret_cast<const T *>(p.x)[(int64_t)b * p.x_bs + (int64_t)d * p.x_ds]);
+  float acc = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
+  float s[MAXW];
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k) s[k] = (k + 1 < W) ? tof(st[k + 1]) : 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k) {
+    if (k < W) {
+      const float v = (k == W - 1) ? xv : s[k];
+      st[k] = fromf<T>(v);
+      acc = fmaf(tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k]), v, acc);
+    }
+  }
+  reinterpret_cast<T *>(p.out)[(int64_t)b * p.out_bs + (int64_t)d * p.out_ds] = fromf<T>(p.silu ? silu_f(acc) : acc);
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+constexpr int NT = 256;           // threads per CTA: a CTA walks rows, a thread owns up to NV columns x 8
+constexpr int NV = 2;             // 16-byte vectors per thread: rows up to 256 * 2 * 8 = 4096 columns
+
+template <typename T> __device__ __forceinline__ void ldv(const T *p, float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = tof(e[i]);
+  } else {
+    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+template <typename T> __device__ __forceinline__ void stv(T *p, const float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    uint4 raw;
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = fromf<T>(v[i]);
+    *reinterpret_cast<uint4 *>(p) = raw;
+  } else {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  __syncthreads();                 // red may still be read from the previous use
+  if (lane == 0) red[wp] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) s += red[i];
+  return s;
+}
+
+// z = x + residual (stored as residual_out when asked for); y = z * rstd * w, rstd = rsqrt(mean z^2 + eps)
+template <typename T, typename R>
+__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const b200_rmsnorm_args p) {
+  __shared__ float red[NT / 32];
+  const int H = p.cols;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T *x = reinterpret_cast<const T *>(p.x) + row * p.x_rs;
+    const R *res = p.residual ? reinterpret_cast<const R *>(p.residual) + row * p.residual_rs : nullptr;
+    float z[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * NT + threadIdx.x) * 8;
+      if (c < H) {
+        ldv<T>(x + c, z[j]);
+        if (res) {
+          float r[8];
+          ldv<R>(res + c, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) z[j][i] += r[i];
+        }
+        if (p.residual_out) {
+          // the sum is rounded to the residual dtype first, as the reference stores it before normalising
+          R *ro = reinterpret_cast<R *>(p.residual_out) + row * p.residual_out_rs + c;
+          stv<R>(ro, z[j]);
+          if constexpr (sizeof(R) == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) z[j][i] = tof(fromf<R>(z[j][i]));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(z[j][i], z[j][i], ss);
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / (float)H + p.eps);
+    if (threadIdx.x == 0 && p.rstd) reinterpret_cast<float *>(p.rstd)[row] = rstd;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * NT + threadIdx.x) * 8;
+      if (c < H) {
+        float w[8], y[8];
+        ldv<T>(reinterpret_cast<const T *>(p.weight) + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = z[j][i] * rstd * w[i];
+        stv<T>(reinterpret_cast<T *>(p.y) + row * p.y_rs + c, y);
+      }
+    }
+  }
+}
+
+// dz = (w dy - zhat mean(zhat w dy)) rstd + dresidual;  dw += dy zhat  (per-thread partial, one atomic per CTA column)
+template <typename T, typename R>
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const b200_rmsnorm_args p) {
+  __shared__ float red[NT / 32];
+  const int H = p.cols;
+  float dwacc[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const R *z = reinterpret_cast<const R *>(p.residual_out) + row * p.residual_out_rs;   // the normalised input
+    const T *dy = reinterpret_cast<const T *>(p.dy) + row * p.dy_rs;
+    const float rstd = reinterpret_cast<const float *>(p.rstd)[row];
+    float zh[NV][8], wdy[NV][8];
+    float c1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * NT + threadIdx.x) * 8;
+      if (c < H) {
+        float w[8], g[8];
+        ldv<R>(z + c, zh[j]);
+        ldv<T>(dy + c, g);
+        ldv<T>(reinterpret_cast<const T *>(p.weight) + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          zh[j][i] *= rstd;
+          wdy[j][i] = g[i] * w[i];
+          c1 = fmaf(zh[j][i], wdy[j][i], c1);
+          dwacc[j][i] = fmaf(g[i], zh[j][i], dwacc[j][i]);
+        }
+      }
+    }
+    c1 = block_sum(c1, red) / (float)H;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * NT + threadIdx.x) * 8;
+      if (c < H) {
+        float dz[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dz[i] = (wdy[j][i] - zh[j][i] * c1) * rstd;
+        if (p.dresidual) {
+          float r[8];
+          ldv<R>(reinterpret_cast<const R *>(p.dresidual) + row * p.dresidual_rs + c, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dz[i] += r[i];
+        }
+        // one gradient for both inputs of the add: dx (dtype of x) and, when asked for, dresidual_in
+        stv<T>(reinterpret_cast<T *>(p.dx) + row * p.dx_rs + c, dz);
+        if (p.dresidual_in) stv<R>(reinterpret_cast<R *>(p.dresidual_in) + row * p.dresidual_in_rs + c, dz);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = (j * NT + threadIdx.x) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(reinterpret_cast<float *>(p.dweight) + c + i, dwacc[j][i]);
+    }
+  }
+}
+
+int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
+  B200_REQUIRE(a.x && a.weight && (bwd || a.out), B200_ERR_NULL, "conv1d: x, weight, out must be non-null");
+  B200_REQUIRE(a.batch > 0 && a.dim > 0 && (update || a.seqlen > 0), B200_ERR_SHAPE, "conv1d: sizes must be positive");
+  B200_REQUIRE(a.width >= 2 && a.width <= MAXW, B200_ERR_SHAPE, "conv1d: width must be 2, 3 or 4 (got %d)", a.width);
+  B200_REQUIRE(a.dtype == B200_F32 || a.dtype == B200_F16 || a.dtype == B200_BF16, B200_ERR_DTYPE, "conv1d: unknown dtype");
+  if (update) {
+    B200_REQUIRE(a.state, B200_ERR_NULL, "conv1d_update: state must be non-null");
+    return 0;
+  }
+  if (bwd) {
+    B200_REQUIRE(a.dout && a.dx && a.dweight, B200_ERR_NULL, "conv1d_bwd: dout, dx, dweight must be non-null");
+    B200_REQUIRE(!a.bias || a.dbias, B200_ERR_NULL, "conv1d_bwd: dbias is required when bias is given");
+  }
+  B200_REQUIRE((int64_t)a.batch * a.dim < (int64_t(1) << 31), B200_ERR_SHAPE, "conv1d: too many rows");
+  return 0;
+}
+
+int check_norm(const b200_rmsnorm_args &a, bool bwd) {
+  B200_REQUIRE(a.weight && a.rows > 0 && a.cols > 0, B200_ERR_NULL, "rmsnorm: weight must be non-null, sizes positive");
+  B200_REQUIRE(a.cols % 8 == 0 && a.cols <= NT * NV * 8, B200_ERR_SHAPE,
+               "rmsnorm: the row length must be a multiple of 8 and at most %d (got %d)", NT * NV * 8, a.cols);
+  B200_REQUIRE(a.dtype == B200_F32 || a.dtype == B200_F16 || a.dtype == B200_BF16, B200_ERR_DTYPE, "rmsnorm: unknown dtype");
+  B200_REQUIRE(a.residual_dtype == a.dtype || a.residual_dtype == B200_F32, B200_ERR_DTYPE,
+               "rmsnorm: the residual is kept in the activation dtype or in float32");
+  if (!bwd) {
+    B200_REQUIRE(a.x && a.y, B200_ERR_NULL, "rmsnorm_fwd: x and y must be non-null");
+  } else {
+    B200_REQUIRE(a.dy && a.dx && a.dweight && a.rstd && a.residual_out, B200_ERR_NULL,
+                 "rmsnorm_bwd: dy, dx, dweight, rstd and residual_out (the normalised input) must be non-null");
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+#define DISPATCH_T(dt, CALL)                         \
+  if ((dt) == B200_F32) { using T = float; CALL; }   \
+  else if ((dt) == B200_BF16) { using T = __nv_bfloat16; CALL; } \
+  else { using T = __half; CALL; }
+
+extern "C" {
+
+int b200_conv1d_fwd(const b200_conv1d_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "conv1d_fwd: null argument block");
+  if (int e = check_conv(*args, false, false)) return e;
+  const dim3 grid((unsigned)(args->batch * args->dim), (unsigned)((args->seqlen + CVT * CVE - 1) / (CVT * CVE)));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DISPATCH_T(args->dtype, (conv1d_fwd_kernel<T><<<grid, CVT, 0, st>>>(*args)));
+  return launch_status();
+}
+
+int b200_conv1d_bwd(const b200_conv1d_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "conv1d_bwd: null argument block");
+  if (int e = check_conv(*args, true, false)) return e;
+  const dim3 grid((unsigned)(args->batch * args->dim), (unsigned)((args->seqlen + CVT * CVE - 1) / (CVT * CVE)));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DISPATCH_T(args->dtype, (conv1d_bwd_kernel<T><<<grid, CVT, 0, st>>>(*args)));
+  return launch_status();
+}
+
+int b200_conv1d_update(const b200_conv1d_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "conv1d_update: null argument block");
+  if (int e = check_conv(*args, false, true)) return e;
+  const int64_t n = (int64_t)args->batch * args->dim;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DISPATCH_T(args->dtype, (conv1d_update_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(*args)));
+  return launch_status();
+}
+
+int b200_rmsnorm_fwd(const b200_rmsnorm_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "rmsnorm_fwd: null argument block");
+  if (int e = check_norm(*args, false)) return e;
+  const int64_t grid = args->rows < (int64_t)sm_count_current() * 8 ? args->rows : (int64_t)sm_count_current() * 8;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (args->residual_dtype == B200_F32) {
+    DISPATCH_T(args->dtype, (rmsnorm_fwd_kernel<T, float><<<(unsigned)grid, NT, 0, st>>>(*args)));
+  } else {
+    DISPATCH_T(args->dtype, (rmsnorm_fwd_kernel<T, T><<<(unsigned)grid, NT, 0, st>>>(*args)));
+  }
+  return launch_status();
+}
+
+int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "rmsnorm_bwd: null argument block");
+  if (int e = check_norm(*args, true)) return e;
+  const int64_t grid = args->rows < (int64_t)sm_count_current() * 4 ? args->rows : (int64_t)sm_count_current() * 4;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (args->residual_dtype == B200_F32) {
+    DISPATCH_T(args->dtype, (rmsnorm_bwd_kernel<T, float><<<(unsigned)grid, NT, 0, st>>>(*args)));
+  } else {
+    DISPATCH_T(args->dtype, (rmsnorm_bwd_kernel<T, T><<<(unsigned)grid, NT, 0, st>>>(*args)));
+  }
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,668 @@
+// Streaming kernels of the selective scan for the S6 (Mamba) shape class: real A, "mamba"
+// discretization, variable B and C, dstate 16, 16-byte aligned rows, L a multiple of 8.
+//
+// With 16 states per channel the scan is bound by the SFU (one ex2 per (t, n, channel)) and by
+// instruction issue, not by HBM.  These kernels spend as few issue slots per (t, n, channel) as
+// the recurrence allows by giving up time-parallel scans altogether:
+//   * a lane owns 4 states (two float2 pairs) of 2 channels and walks the sequence serially:
+//     h = a h + b is one packed FMA per state pair per step, there is no cross-lane scan, no
+//     running product, no carry exchange; the four lanes of a channel pair combine their partial
+//     outputs with two shuffles per step;
+//   * a warp owns a tile of 16 channels of one (batch, group) and works on its own: the warp
+//     stages its operands (asynchronous 16-byte copies into shared memory, one stage of 32 steps
+//     ahead), converts the B / C tile once to float32 in [t][n] order, evaluates softplus, delta u,
+//     the z gate per (channel, t) once, and its lanes then read everything with conflict-free
+//     128-bit shared loads.  No block-wide barrier exists in these kernels;
+//   * packing is over state pairs, so B and C pairs come out of shared memory as float2 operands
+//     of the packed instructions without any broadcast moves; only delta and delta u are
+//     broadcast, once per (channel, t) for four states.
+// The backward walks the stages in reverse.  Per stage it recomputes the 32 states of the stage
+// from the state at the stage start (saved by the forward call: stage_h with 32-step spacing)
+// into shared memory, then runs the adjoint g_t = a_{t+1} g_{t+1} + dy_t C_t serially with the
+// adjoint and a_{t+1} carried in registers across stages.  dB / dC contributions of the tile's
+// 16 channels are summed through shared memory (they overwrite the stage's states in place) and
+// leave as one float32 reduction per (n, t) per tile.
+// Results match csrc/selective_scan/selective_scan.cuh:73-382 and
+// csrc/selective_scan/selective_scan_backward.cuh:86-845 of lrnnx for this shape class.
+#include "common.cuh"
+#include "dispatch.h"
+#include <cstdlib>
+
+namespace b200 {
+namespace {
+
+constexpr int ST = 32;            // timesteps per stage
+constexpr int SCH = 16;           // channels per warp tile
+constexpr int SN = 16;            // states
+constexpr int BCROW = 36;         // floats per timestep row of the converted B|C tile (32 + 4 pad)
+constexpr int DDROW = 36;         // floats per timestep row of the per-(channel pair) operand tiles
+constexpr int YROW = 33;          // floats per channel row of the per-(channel, t) result tiles
+constexpr int HROW = 272;         // floats per timestep row of the state tile (2 x 32 lanes x 4 + 16 pad)
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float2 ex2f2(float2 x) { return make_float2(ex2f(x.x), ex2f(x.y)); }
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+
+// softplus with the reference's pass-through above 20 (selective_scan.cuh:172-174) on two SFU
+// operations: e = exp(x); log1p(e) as a degree-5 series for e < 1/32 (relative error < 1e-8) and
+// as log(1 + e) above (the rounding of 1 + e is then below 2e-6 of e).
+__device__ __forceinline__ float softplus_sl(float x) {
+  if (x > 20.f) return x;
+  const float e = ex2f(x * kLog2e);
+  const float series = e * fmaf(e, fmaf(e, fmaf(e, fmaf(e, 0.2f, -0.25f), 0.33333334f), -0.5f), 1.f);
+  const float big = lg2f(1.f + e) * 0.6931471805599453f;
+  return e < 0.03125f ? series : big;
+}
+
+__device__ __forceinline__ void cp16(void *smem_dst, const void *gsrc, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// Asynchronous copy of NR 32-step rows (global row r at src + r * row_stride + t0) into shared rows
+// of ST elements; 16-byte pieces past the end of the sequence are zero-filled.  Warp-wide.
+template <typename T, int NR>
+__device__ __forceinline__ void stage_rows(T *dst, const T *src, int64_t row_stride, int t0, int L, int lane) {
+  constexpr int EPP = 16 / (int)sizeof(T);   // elements per 16-byte piece
+  constexpr int PPR = ST / EPP;              // pieces per row
+#pragma unroll
+  for (int i = 0; i < NR * PPR / 32; ++i) {
+    const int idx = lane + 32 * i;
+    const int r = idx / PPR, q = idx % PPR;
+    const int t = t0 + q * EPP;
+    const bool ok = t < L;
+    cp16(dst + r * ST + q * EPP, src + (int64_t)r * row_stride + (ok ? t : 0), ok ? 16 : 0);
+  }
+}
+// Copy of NR 32-step rows from shared memory to global rows (16-byte pieces, skipped past L).
+template <typename T, int NR>
+__device__ __forceinline__ void store_rows(T *dst, int64_t row_stride, const T *src, int t0, int L, int lane) {
+  constexpr int EPP = 16 / (int)sizeof(T);
+  constexpr int PPR = ST / EPP;
+#pragma unroll
+  for (int i = 0; i < NR * PPR / 32; ++i) {
+    const int idx = lane + 32 * i;
+    const int r = idx / PPR, q = idx % PPR;
+    const int t = t0 + q * EPP;
+    if (t < L) *reinterpret_cast<uint4 *>(dst + (int64_t)r * row_stride + t) = *reinterpret_cast<const uint4 *>(src + r * ST + q * EPP);
+  }
+}
+
+// B | C tile of one stage: raw rows [n][t] of T  ->  float32 rows [t][B0..B15 C0..C15] (lane = t)
+template <typename T>
+__device__ __forceinline__ void convert_bc(float *bc, const T *rawB, const T *rawC, int lane) {
+  float *row = bc + lane * BCROW;
+#pragma unroll
+  for (int n = 0; n < SN; n += 4) {
+    const float4 b = make_float4(to_f(rawB[(n + 0) * ST + lane]), to_f(rawB[(n + 1) * ST + lane]),
+                                 to_f(rawB[(n + 2) * ST + lane]), to_f(rawB[(n + 3) * ST + lane]));
+    const float4 c = make_float4(to_f(rawC[(n + 0) * ST + lane]), to_f(rawC[(n + 1) * ST + lane]),
+                                 to_f(rawC[(n + 2) * ST + lane]), to_f(rawC[(n + 3) * ST + lane]));
+    *reinterpret_cast<float4 *>(row + n) = b;
+    *reinterpret_cast<float4 *>(row + SN + n) = c;
+  }
+}
+
+// ------------------------------------------------------------------------------------ forward
+template <typename T> struct FwdSmem {
+  static constexpr int RAW_ROWS = 5 * SCH;                               // u, delta, z, B, C
+  static constexpr int RAW = RAW_ROWS * ST * (int)sizeof(T);             // one raw stage
+  static constexpr int OFF_BC = 2 * RAW;
+  static constexpr int OFF_DD = OFF_BC + ST * BCROW * 4;
+  static constexpr int OFF_Y = OFF_DD + ST * DDROW * 4;
+  static constexpr int OFF_PAR = OFF_Y + SCH * YROW * 4;                 // bias[16], D[16]
+  static constexpr int TOTAL = ((OFF_PAR + 2 * SCH * 4 + 127) / 128) * 128;
+};
+
+template <typename T, int NW, bool STG>
+__global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_selscan_fwd_args p) {
+  using SM = FwdSmem<T>;
+  extern __shared__ __align__(128) unsigned char smem_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sl = lane & 3, cp = lane >> 2;
+  const int tiles_per_b = p.dim / SCH;
+  const int64_t tile = (int64_t)blockIdx.x * NW + warp;
+  if (tile >= (int64_t)p.batch * tiles_per_b) return;       // warps are independent: no block barrier anywhere
+  unsigned char *smem = smem_all + (size_t)warp * SM::TOTAL;
+  const int b = (int)(tile / tiles_per_b);
+  const int d0 = (int)(tile % tiles_per_b) * SCH;
+  const int g = d0 / (p.dim / p.n_groups);
+  const int n_chunks = (p.seqlen + kChunk - 1) / kChunk;
+  // blockIdx.y = segment of the sequence scanned from a zero state (whole checkpoint chunks)
+  int seg_len = p.seqlen;
+  if (gridDim.y > 1) {
+    const int per = (p.seqlen + (int)gridDim.y - 1) / (int)gridDim.y;
+    seg_len = ((per + kChunk - 1) / kChunk) * kChunk;
+  }
+  const int t_begin = (int)blockIdx.y * seg_len;
+  const int L = min(p.seqlen, t_begin + seg_len);
+  if (t_begin >= L) return;
+  const int nst = (L - t_begin + ST - 1) / ST;
+  const bool has_z = p.z != nullptr;
+
+  const T *Usrc = reinterpret_cast<const T *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d0 * p.u_ds;
+  const T *Dsrc = reinterpret_cast<const T *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d0 * p.delta_ds;
+  const T *Zsrc = has_z ? reinterpret_cast<const T *>(p.z) + (int64_t)b * p.z_bs + (int64_t)d0 * p.z_ds : nullptr;
+  const T *Bsrc = reinterpret_cast<const T *>(p.B) + (int64_t)b * p.B_bs + (int64_t)g * p.B_gs;
+  const T *Csrc = reinterpret_cast<const T *>(p.C) + (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  T *Odst = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d0 * p.out_ds;
+  T *OZdst = has_z ? reinterpret_cast<T *>(p.out_z) + (int64_t)b * p.out_z_bs + (int64_t)d0 * p.out_z_ds : nullptr;
+
+  auto issue = [&](int s) {
+    T *raw = reinterpret_cast<T *>(smem + (size_t)(s & 1) * SM::RAW);
+    const int t0 = t_begin + s * ST;
+    stage_rows<T, SCH>(raw, Usrc, p.u_ds, t0, L, lane);
+    stage_rows<T, SCH>(raw + SCH * ST, Dsrc, p.delta_ds, t0, L, lane);
+    if (has_z) stage_rows<T, SCH>(raw + 2 * SCH * ST, Zsrc, p.z_ds, t0, L, lane);
+    stage_rows<T, SN>(raw + 3 * SCH * ST, Bsrc, p.B_ns, t0, L, lane);
+    stage_rows<T, SN>(raw + 4 * SCH * ST, Csrc, p.C_ns, t0, L, lane);
+  };
+  issue(0);
+  cp_commit();
+
+  float *bc = reinterpret_cast<float *>(smem + SM::OFF_BC);
+  float *dd = reinterpret_cast<float *>(smem + SM::OFF_DD);
+  float *ys = reinterpret_cast<float *>(smem + SM::OFF_Y);
+  float *par = reinterpret_cast<float *>(smem + SM::OFF_PAR);
+  if (lane < SCH) {
+    par[lane] = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d0 + lane] : 0.f;
+    par[SCH + lane] = p.D ? reinterpret_cast<const float *>(p.D)[d0 + lane] : 0.f;
+  }
+  // A * log2(e): this lane's 4 states of its 2 channels
+  const int c0 = d0 + 2 * cp;
+  float2 A2[2][2];
+  {
+    const float *A = reinterpret_cast<const float *>(p.A);
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        A2[c][j] = make_float2(A[(int64_t)(c0 + c) * p.A_ds + (int64_t)(4 * sl + 2 * j) * p.A_ns] * kLog2e,
+                               A[(int64_t)(c0 + c) * p.A_ds + (int64_t)(4 * sl + 2 * j + 1) * p.A_ns] * kLog2e);
+  }
+  float2 h[2][2];
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) h[c][j] = make_float2(0.f, 0.f);
+  float cs0 = 0.f, cs1 = 0.f;      // sum of delta since the start of the segment (channels c0, c0 + 1)
+  float *xrow = reinterpret_cast<float *>(p.x) + ((int64_t)b * p.dim + c0) * n_chunks * 2 * SN;
+  const int n_stages = (p.seqlen + ST - 1) / ST;
+  float *sth = STG ? reinterpret_cast<float *>(p.stage_h) + ((int64_t)b * p.dim + c0) * n_stages * SN : nullptr;
+  __syncwarp();
+
+  for (int s = 0; s < nst; ++s) {
+    if (s + 1 < nst) issue(s + 1);
+    cp_commit();
+    cp_wait<1>();
+    __syncwarp();
+    T *raw = reinterpret_cast<T *>(smem + (size_t)(s & 1) * SM::RAW);
+    const int t0 = t_begin + s * ST;
+    // ---- per-stage preparation (lane = timestep)
+    convert_bc<T>(bc, raw + 3 * SCH * ST, raw + 4 * SCH * ST, lane);
+    {
+      const bool live = t0 + lane < L;
+      float *row = dd + lane * DDROW;
+#pragma unroll
+      for (int q = 0; q < SCH / 2; ++q) {
+        float dv[2], duv[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int ch = 2 * q + c;
+          float d = to_f(raw[(SCH + ch) * ST + lane]) + par[ch];
+          if (p.delta_softplus) d = softplus_sl(d);
+          if (!live) d = 0.f;                                   // past the end: a = 1, b = 0
+          dv[c] = d;
+          duv[c] = d * to_f(raw[ch * ST + lane]);
+        }
+        *reinterpret_cast<float4 *>(row + 4 * q) = make_float4(dv[0], duv[0], dv[1], duv[1]);
+      }
+    }
+    __syncwarp();
+    // ---- the recurrence: 32 serial steps, 4 packed chains per lane
+#pragma unroll 4
+    for (int t = 0; t < ST; ++t) {
+      const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
+      const float4 c4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + SN + 4 * sl);
+      const float4 d4 = *reinterpret_cast<const float4 *>(dd + t * DDROW + 4 * cp);
+      const float2 B01 = make_float2(b4.x, b4.y), B23 = make_float2(b4.z, b4.w);
+      const float2 C01 = make_float2(c4.x, c4.y), C23 = make_float2(c4.z, c4.w);
+      const float2 dl0 = splat(d4.x), du0 = splat(d4.y), dl1 = splat(d4.z), du1 = splat(d4.w);
+      h[0][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][0])), h[0][0], __fmul2_rn(du0, B01));
+      h[0][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][1])), h[0][1], __fmul2_rn(du0, B23));
+      h[1][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][0])), h[1][0], __fmul2_rn(du1, B01));
+      h[1][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][1])), h[1][1], __fmul2_rn(du1, B23));
+      const float2 p0 = __ffma2_rn(h[0][1], C23, __fmul2_rn(h[0][0], C01));
+      const float2 p1 = __ffma2_rn(h[1][1], C23, __fmul2_rn(h[1][0], C01));
+      const float s0 = p0.x + p0.y, s1 = p1.x + p1.y;
+      // sum over the 4 lanes of the channel pair: odd lanes end with channel c0 + 1, even with c0
+      const float send = (sl & 1) ? s0 : s1;
+      float keep = ((sl & 1) ? s1 : s0) + __shfl_xor_sync(0xffffffffu, send, 1);
+      keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+      if (sl < 2) ys[(2 * cp + sl) * YROW + t] = keep;
+      cs0 += d4.x;
+      cs1 += d4.z;
+    }
+    // ---- checkpoints and stage states
+    const bool chunk_end = ((t0 + ST) % kChunk) == 0 || s == nst - 1;
+    if (chunk_end) {
+      const int64_t o = (int64_t)(t0 / kChunk) * 2 * SN + 8 * sl;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float cs = c ? cs1 : cs0;
+        const float2 P0 = ex2f2(__fmul2_rn(splat(cs), A2[c][0])), P1 = ex2f2(__fmul2_rn(splat(cs), A2[c][1]));
+        float *xr = xrow + (int64_t)c * n_chunks * 2 * SN + o;
+        *reinterpret_cast<float4 *>(xr) = make_float4(P0.x, h[c][0].x, P0.y, h[c][0].y);
+        *reinterpret_cast<float4 *>(xr + 4) = make_float4(P1.x, h[c][1].x, P1.y, h[c][1].y);
+      }
+    }
+    if (STG) {
+      float *q = sth + (int64_t)(t0 / ST) * SN + 4 * sl;
+      *reinterpret_cast<float4 *>(q) = make_float4(h[0][0].x, h[0][0].y, h[0][1].x, h[0][1].y);
+      *reinterpret_cast<float4 *>(q + (int64_t)n_stages * SN) = make_float4(h[1][0].x, h[1][0].y, h[1][1].x, h[1][1].y);
+    }
+    __syncwarp();
+    // ---- outputs (lane = timestep): out = y + D u into the delta rows, out * silu(z) into the z rows
+    {
+      T *ot = raw + SCH * ST, *zt = raw + 2 * SCH * ST;
+#pragma unroll 4
+      for (int ch = 0; ch < SCH; ++ch) {
+        const float o = fmaf(par[SCH + ch], to_f(raw[ch * ST + lane]), ys[ch * YROW + lane]);
+        ot[ch * ST + lane] = from_f<T>(o);
+        if (has_z) {
+          const float zv = to_f(zt[ch * ST + lane]);
+          zt[ch * ST + lane] = from_f<T>(o * zv * sigmoidf_(zv));
+        }
+      }
+      __syncwarp();
+      store_rows<T, SCH>(Odst, p.out_ds, ot, t0, L, lane);
+      if (has_z) store_rows<T, SCH>(OZdst, p.out_z_ds, zt, t0, L, lane);
+    }
+    __syncwarp();     // the raw buffer of this stage is refilled by the copies issued two iterations later
+  }
+  cp_wait<0>();
+}
+
+// ------------------------------------------------------------------------------------ backward
+template <typename T> struct BwdSmem {
+  static constexpr int RAW_ROWS = 7 * SCH;                               // u, delta, dout, z, out, B, C
+  static constexpr int RAW = RAW_ROWS * ST * (int)sizeof(T);
+  static constexpr int OFF_BC = RAW;
+  static constexpr int OFF_DA = OFF_BC + ST * BCROW * 4;                 // {delta0, du0, delta1, du1} per (t, pair)
+  static constexpr int OFF_DB = OFF_DA + ST * DDROW * 4;                 // {u0, dy0, u1, dy1}
+  static constexpr int OFF_H = OFF_DB + ST * DDROW * 4;                  // states, then dB | dC partials
+  static constexpr int OFF_SUM = OFF_H + ST * HROW * 4;                  // float2 {sum g B, sum w A2} per (channel, t)
+  static constexpr int OFF_OT = OFF_SUM + SCH * YROW * 8;                // du, ddelta tiles
+  static constexpr int OFF_PAR = OFF_OT + 2 * SCH * ST * (int)sizeof(T);
+  static constexpr int TOTAL = ((OFF_PAR + 2 * SCH * 4 + 127) / 128) * 128;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(32) selscan_sl_bwd_kernel(const b200_selscan_bwd_args q) {
+  using SM = BwdSmem<T>;
+  const b200_selscan_fwd_args &p = q.f;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int lane = threadIdx.x;
+  const int sl = lane & 3, cp = lane >> 2;
+  const int tiles_per_b = p.dim / SCH;
+  const int b = (int)(blockIdx.x / tiles_per_b);
+  const int d0 = (int)(blockIdx.x % tiles_per_b) * SCH;
+  const int g = d0 / (p.dim / p.n_groups);
+  const int L = p.seqlen;
+  const int nst = (L + ST - 1) / ST;
+  const bool has_z = p.z != nullptr;
+
+  const T *Usrc = reinterpret_cast<const T *>(p.u) + (int64_t)b * p.u_bs + (int64_t)d0 * p.u_ds;
+  const T *Dsrc = reinterpret_cast<const T *>(p.delta) + (int64_t)b * p.delta_bs + (int64_t)d0 * p.delta_ds;
+  const T *DOsrc = reinterpret_cast<const T *>(q.dout) + (int64_t)b * q.dout_bs + (int64_t)d0 * q.dout_ds;
+  const T *Zsrc = has_z ? reinterpret_cast<const T *>(p.z) + (int64_t)b * p.z_bs + (int64_t)d0 * p.z_ds : nullptr;
+  const T *Osrc = has_z ? reinterpret_cast<const T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d0 * p.out_ds : nullptr;
+  const T *Bsrc = reinterpret_cast<const T *>(p.B) + (int64_t)b * p.B_bs + (int64_t)g * p.B_gs;
+  const T *Csrc = reinterpret_cast<const T *>(p.C) + (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  T *DUdst = reinterpret_cast<T *>(q.du) + (int64_t)b * q.du_bs + (int64_t)d0 * q.du_ds;
+  T *DDdst = reinterpret_cast<T *>(q.ddelta) + (int64_t)b * q.ddelta_bs + (int64_t)d0 * q.ddelta_ds;
+  T *DZdst = has_z ? reinterpret_cast<T *>(q.dz) + (int64_t)b * q.dz_bs + (int64_t)d0 * q.dz_ds : nullptr;
+  float *dBg = reinterpret_cast<float *>(q.dB) + (int64_t)b * q.dB_bs + (int64_t)g * q.dB_gs;
+  float *dCg = reinterpret_cast<float *>(q.dC) + (int64_t)b * q.dC_bs + (int64_t)g * q.dC_gs;
+
+  T *raw = reinterpret_cast<T *>(smem);
+  auto issue = [&](int s) {
+    const int t0 = s * ST;
+    stage_rows<T, SCH>(raw, Usrc, p.u_ds, t0, L, lane);
+    stage_rows<T, SCH>(raw + SCH * ST, Dsrc, p.delta_ds, t0, L, lane);
+    stage_rows<T, SCH>(raw + 2 * SCH * ST, DOsrc, q.dout_ds, t0, L, lane);
+    if (has_z) {
+      stage_rows<T, SCH>(raw + 3 * SCH * ST, Zsrc, p.z_ds, t0, L, lane);
+      stage_rows<T, SCH>(raw + 4 * SCH * ST, Osrc, p.out_ds, t0, L, lane);
+    }
+    stage_rows<T, SN>(raw + 5 * SCH * ST, Bsrc, p.B_ns, t0, L, lane);
+    stage_rows<T, SN>(raw + 6 * SCH * ST, Csrc, p.C_ns, t0, L, lane);
+  };
+  issue(nst - 1);
+  cp_commit();
+
+  float *bc = reinterpret_cast<float *>(smem + SM::OFF_BC);
+  float *dda = reinterpret_cast<float *>(smem + SM::OFF_DA);
+  float *ddb = reinterpret_cast<float *>(smem + SM::OFF_DB);
+  float *hs = reinterpret_cast<float *>(smem + SM::OFF_H);
+  float2 *sums = reinterpret_cast<float2 *>(smem + SM::OFF_SUM);
+  T *ot = reinterpret_cast<T *>(smem + SM::OFF_OT);
+  float *par = reinterpret_cast<float *>(smem + SM::OFF_PAR);
+  if (lane < SCH) {
+    par[lane] = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d0 + lane] : 0.f;
+    par[SCH + lane] = p.D ? reinterpret_cast<const float *>(p.D)[d0 + lane] : 0.f;
+  }
+  const int c0 = d0 + 2 * cp;
+  float2 A2[2][2];
+  {
+    const float *A = reinterpret_cast<const float *>(p.A);
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        A2[c][j] = make_float2(A[(int64_t)(c0 + c) * p.A_ds + (int64_t)(4 * sl + 2 * j) * p.A_ns] * kLog2e,
+                               A[(int64_t)(c0 + c) * p.A_ds + (int64_t)(4 * sl + 2 * j + 1) * p.A_ns] * kLog2e);
+  }
+  const float *sth = reinterpret_cast<const float *>(p.stage_h) + ((int64_t)b * p.dim + c0) * nst * SN;
+  float2 gadj[2][2], anext[2][2], dAacc[2][2];
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      gadj[c][j] = make_float2(0.f, 0.f);
+      anext[c][j] = make_float2(1.f, 1.f);
+      dAacc[c][j] = make_float2(0.f, 0.f);
+    }
+  float dDacc[SCH], dbacc[SCH];      // lane = timestep partial sums of dD and ddelta_bias
+#pragma unroll
+  for (int ch = 0; ch < SCH; ++ch) { dDacc[ch] = 0.f; dbacc[ch] = 0.f; }
+  __syncwarp();
+
+  for (int s = nst - 1; s >= 0; --s) {
+    const int t0 = s * ST;
+    cp_wait<0>();
+    __syncwarp();
+    // ---- per-stage preparation (lane = timestep)
+    convert_bc<T>(bc, raw + 5 * SCH * ST, raw + 6 * SCH * ST, lane);
+    {
+      const bool live = t0 + lane < L;
+      float *rowa = dda + lane * DDROW, *rowb = ddb + lane * DDROW;
+#pragma unroll
+      for (int qd = 0; qd < SCH / 2; ++qd) {
+        float dv[2], duv[2], uv[2], dyv[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int ch = 2 * qd + c;
+          float d = to_f(raw[(SCH + ch) * ST + lane]) + par[ch];
+          if (p.delta_softplus) d = softplus_sl(d);
+          if (!live) d = 0.f;
+          const float u = to_f(raw[ch * ST + lane]);
+          float dy = to_f(raw[(2 * SCH + ch) * ST + lane]);
+          if (has_z) {
+            const float zv = to_f(raw[(3 * SCH + ch) * ST + lane]);
+            const float ov = to_f(raw[(4 * SCH + ch) * ST + lane]);
+            const float sg = sigmoidf_(zv);
+            // dz = dout * out * d silu(z)/dz  (selective_scan_backward.cuh:214-221); written over z
+            raw[(3 * SCH + ch) * ST + lane] = from_f<T>(dy * ov * sg * (1.f + zv * (1.f - sg)));
+            dy *= zv * sg;
+          }
+          dDacc[ch] = fmaf(dy, u, dDacc[ch]);
+          dv[c] = d; duv[c] = d * u; uv[c] = u; dyv[c] = dy;
+        }
+        *reinterpret_cast<float4 *>(rowa + 4 * qd) = make_float4(dv[0], duv[0], dv[1], duv[1]);
+        *reinterpret_cast<float4 *>(rowb + 4 * qd) = make_float4(uv[0], dyv[0], uv[1], dyv[1]);
+      }
+    }
+    __syncwarp();
+    if (has_z) store_rows<T, SCH>(DZdst, q.dz_ds, raw + 3 * SCH * ST, t0, L, lane);
+    __syncwarp();
+    if (s > 0) issue(s - 1);          // the raw tile is consumed: fetch the next (earlier) stage behind the compute
+    cp_commit();
+    // ---- states of the stage, from the state at its start
+    {
+      float2 h[2][2];
+      if (s > 0) {
+        const float *ps = sth + (int64_t)(s - 1) * SN + 4 * sl;
+        const float4 v0 = *reinterpret_cast<const float4 *>(ps);
+        const float4 v1 = *reinterpret_cast<const float4 *>(ps + (int64_t)nst * SN);
+        h[0][0] = make_float2(v0.x, v0.y); h[0][1] = make_float2(v0.z, v0.w);
+        h[1][0] = make_float2(v1.x, v1.y); h[1][1] = make_float2(v1.z, v1.w);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) h[c][j] = make_float2(0.f, 0.f);
+      }
+#pragma unroll 4
+      for (int t = 0; t < ST; ++t) {
+        const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
+        const float4 d4 = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
+        const float2 B01 = make_float2(b4.x, b4.y), B23 = make_float2(b4.z, b4.w);
+        const float2 dl0 = splat(d4.x), du0 = splat(d4.y), dl1 = splat(d4.z), du1 = splat(d4.w);
+        h[0][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][0])), h[0][0], __fmul2_rn(du0, B01));
+        h[0][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][1])), h[0][1], __fmul2_rn(du0, B23));
+        h[1][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][0])), h[1][0], __fmul2_rn(du1, B01));
+        h[1][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][1])), h[1][1], __fmul2_rn(du1, B23));
+        float *hr = hs + t * HROW + lane * 4;
+        *reinterpret_cast<float4 *>(hr) = make_float4(h[0][0].x, h[0][0].y, h[0][1].x, h[0][1].y);
+        *reinterpret_cast<float4 *>(hr + 128) = make_float4(h[1][0].x, h[1][0].y, h[1][1].x, h[1][1].y);
+      }
+    }
+    // ---- the adjoint, serially in reverse
+#pragma unroll 2
+    for (int t = ST - 1; t >= 0; --t) {
+      const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
+      const float4 c4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + SN + 4 * sl);
+      const float4 da = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
+      const float4 db = *reinterpret_cast<const float4 *>(ddb + t * DDROW + 4 * cp);
+      float *hr = hs + t * HROW + lane * 4;
+      const float4 hv0 = *reinterpret_cast<const float4 *>(hr);
+      const float4 hv1 = *reinterpret_cast<const float4 *>(hr + 128);
+      const float2 Bp[2] = {make_float2(b4.x, b4.y), make_float2(b4.z, b4.w)};
+      const float2 Cp[2] = {make_float2(c4.x, c4.y), make_float2(c4.z, c4.w)};
+      const float2 hh[2][2] = {{make_float2(hv0.x, hv0.y), make_float2(hv0.z, hv0.w)},
+                               {make_float2(hv1.x, hv1.y), make_float2(hv1.z, hv1.w)}};
+      const float dl[2] = {da.x, da.z}, du[2] = {da.y, da.w}, dy[2] = {db.y, db.w};
+      float2 sgB[2], sA[2], dBp[2], dCp[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float2 dl2 = splat(dl[c]), ndu2 = splat(-du[c]), du2 = splat(du[c]), dy2 = splat(dy[c]);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float2 a = ex2f2(__fmul2_rn(dl2, A2[c][j]));
+          const float2 gt = __ffma2_rn(anext[c][j], gadj[c][j], __fmul2_rn(dy2, Cp[j]));
+          gadj[c][j] = gt;
+          anext[c][j] = a;
+          const float2 ah = __ffma2_rn(ndu2, Bp[j], hh[c][j]);          // h_t - b_t = a_t h_{t-1}
+          const float2 w = __fmul2_rn(gt, ah);
+          if (j == 0) { sgB[c] = __fmul2_rn(gt, Bp[j]); sA[c] = __fmul2_rn(w, A2[c][j]); }
+          else { sgB[c] = __ffma2_rn(gt, Bp[j], sgB[c]); sA[c] = __ffma2_rn(w, A2[c][j], sA[c]); }
+          dAacc[c][j] = __ffma2_rn(w, dl2, dAacc[c][j]);
+          if (c == 0) { dBp[j] = __fmul2_rn(gt, du2); dCp[j] = __fmul2_rn(dy2, hh[c][j]); }
+          else { dBp[j] = __ffma2_rn(gt, du2, dBp[j]); dCp[j] = __ffma2_rn(dy2, hh[c][j], dCp[j]); }
+        }
+      }
+      // the states of this step are consumed: their slots take the dB | dC partials of the lane
+      *reinterpret_cast<float4 *>(hr) = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
+      *reinterpret_cast<float4 *>(hr + 128) = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
+      // per-(channel, t) sums over the 16 states: odd lanes end with channel c0 + 1, even with c0
+      const float s1_0 = sgB[0].x + sgB[0].y, s2_0 = sA[0].x + sA[0].y;
+      const float s1_1 = sgB[1].x + sgB[1].y, s2_1 = sA[1].x + sA[1].y;
+      const bool odd = sl & 1;
+      float k1 = (odd ? s1_1 : s1_0) + __shfl_xor_sync(0xffffffffu, odd ? s1_0 : s1_1, 1);
+      float k2 = (odd ? s2_1 : s2_0) + __shfl_xor_sync(0xffffffffu, odd ? s2_0 : s2_1, 1);
+      k1 += __shfl_xor_sync(0xffffffffu, k1, 2);
+      k2 += __shfl_xor_sync(0xffffffffu, k2, 2);
+      if (sl < 2) sums[(2 * cp + sl) * YROW + t] = make_float2(k1, k2);
+    }
+    __syncwarp();
+    // ---- dB / dC: sum the 8 channel pairs of the tile, one reduction per (n, t) to global memory
+    {
+      const int tj = lane >> 2;
+#pragma unroll
+      for (int k = 0; k < ST / 8; ++k) {
+        const int t = 8 * k + tj;
+        const float *base = hs + t * HROW + sl * 4;
+        float4 sb = *reinterpret_cast<const float4 *>(base);
+        float4 sc = *reinterpret_cast<const float4 *>(base + 128);
+#pragma unroll
+        for (int c = 1; c < 8; ++c) {
+          const float4 vb = *reinterpret_cast<const float4 *>(base + c * 16);
+          const float4 vc = *reinterpret_cast<const float4 *>(base + 128 + c * 16);
+          sb.x += vb.x; sb.y += vb.y; sb.z += vb.z; sb.w += vb.w;
+          sc.x += vc.x; sc.y += vc.y; sc.z += vc.z; sc.w += vc.w;
+        }
+        if (t0 + t < L) {
+          float *pb = dBg + (int64_t)(4 * sl) * q.dB_ns + t0 + t;
+          float *pc = dCg + (int64_t)(4 * sl) * q.dC_ns + t0 + t;
+          atomicAdd(pb, sb.x); atomicAdd(pb + q.dB_ns, sb.y); atomicAdd(pb + 2 * q.dB_ns, sb.z); atomicAdd(pb + 3 * q.dB_ns, sb.w);
+          atomicAdd(pc, sc.x); atomicAdd(pc + q.dC_ns, sc.y); atomicAdd(pc + 2 * q.dC_ns, sc.z); atomicAdd(pc + 3 * q.dC_ns, sc.w);
+        }
+      }
+    }
+    // ---- du, ddelta (lane = timestep)
+    {
+#pragma unroll 4
+      for (int ch = 0; ch < SCH; ++ch) {
+        const float2 sm2 = sums[ch * YROW + lane];
+        const float2 a2 = *reinterpret_cast<const float2 *>(dda + lane * DDROW + 2 * ch);   // {delta, delta u}
+        const float2 b2 = *reinterpret_cast<const float2 *>(ddb + lane * DDROW + 2 * ch);   // {u, dy}
+        const float duv = fmaf(a2.x, sm2.x, par[SCH + ch] * b2.y);
+        float ddl = fmaf(b2.x, sm2.x, sm2.y * 0.6931471805599453f);
+        // d softplus(r)/dr = 1 - exp(-softplus(r)); equals 1 in the pass-through range
+        if (p.delta_softplus) ddl *= 1.f - ex2f(-a2.x * kLog2e);
+        dbacc[ch] += ddl;
+        ot[ch * ST + lane] = from_f<T>(duv);
+        ot[(SCH + ch) * ST + lane] = from_f<T>(ddl);
+      }
+      __syncwarp();
+      store_rows<T, SCH>(DUdst, q.du_ds, ot, t0, L, lane);
+      store_rows<T, SCH>(DDdst, q.ddelta_ds, ot + SCH * ST, t0, L, lane);
+    }
+    __syncwarp();
+  }
+  // ---- row-level reductions
+  {
+    float *dA = reinterpret_cast<float *>(q.dA);
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float *pa = dA + (int64_t)(c0 + c) * q.dA_ds + (int64_t)(4 * sl + 2 * j) * q.dA_ns;
+        atomicAdd(pa, dAacc[c][j].x);
+        atomicAdd(pa + q.dA_ns, dAacc[c][j].y);
+      }
+#pragma unroll
+    for (int ch = 0; ch < SCH; ++ch) {
+      const float sD = warp_sum(dDacc[ch]), sb = warp_sum(dbacc[ch]);
+      if (lane == 0) {
+        if (q.dD) atomicAdd(reinterpret_cast<float *>(q.dD) + d0 + ch, sD);
+        if (q.ddelta_bias) atomicAdd(reinterpret_cast<float *>(q.ddelta_bias) + d0 + ch, sb);
+      }
+    }
+  }
+}
+
+inline bool al16(const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+bool shape_ok(const b200_selscan_fwd_args &a) {
+  if (a.is_complex || a.method != B200_DISC_MAMBA || !a.var_B || !a.var_C || a.deltaA) return false;
+  if (a.dstate != SN || a.seqlen % 8 != 0) return false;
+  if (a.dim % SCH != 0 || (a.dim / a.n_groups) % SCH != 0) return false;
+  const int64_t m = 16 / (a.dtype == B200_F32 ? 4 : 2);     // strides must keep every row 16-byte aligned
+  if (!al16(a.u) || !al16(a.delta) || !al16(a.B) || !al16(a.C)) return false;
+  if (a.u_bs % m || a.u_ds % m || a.delta_bs % m || a.delta_ds % m) return false;
+  if (a.B_bs % m || a.B_gs % m || a.B_ns % m || a.C_bs % m || a.C_gs % m || a.C_ns % m) return false;
+  if (a.z && (!al16(a.z) || a.z_bs % m || a.z_ds % m)) return false;
+  return true;
+}
+
+template <typename T, int NW> int launch_fwd(const b200_selscan_fwd_args &a, cudaStream_t st) {
+  using SM = FwdSmem<T>;
+  const bool stg = a.stage_h != nullptr && a.l_segments <= 1;
+  auto k = stg ? selscan_sl_fwd_kernel<T, NW, true> : selscan_sl_fwd_kernel<T, NW, false>;
+  const int smem = NW * SM::TOTAL;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  const int64_t tiles = (int64_t)a.batch * (a.dim / SCH);
+  const dim3 grid((unsigned)((tiles + NW - 1) / NW), (unsigned)(a.l_segments > 1 ? a.l_segments : 1));
+  k<<<grid, NW * 32, smem, st>>>(a);
+  return launch_status();
+}
+
+template <typename T> int launch_bwd(const b200_selscan_bwd_args &a, cudaStream_t st) {
+  using SM = BwdSmem<T>;
+  auto k = selscan_sl_bwd_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  const int64_t tiles = (int64_t)a.f.batch * (a.f.dim / SCH);
+  k<<<(unsigned)tiles, 32, SM::TOTAL, st>>>(a);
+  return launch_status();
+}
+
+}  // namespace
+
+// Few rows leave most of the GPU idle under a serial-in-time kernel (a tile of 16 channels is one
+// warp): below this many warps (tiles times sequence segments) the lane-scan kernels are the
+// better fit.  The environment variable LRNNX_B200_SL_MIN_WARPS overrides the threshold (tests
+// use it to run either kernel family on the same small problem).
+static int64_t min_warps() {
+  if (const char *e = getenv("LRNNX_B200_SL_MIN_WARPS")) return atoll(e);
+  return 2 * (int64_t)sm_count_current();
+}
+
+bool selscan_fwd_sl_supported(const b200_selscan_fwd_args &a) {
+  if (!shape_ok(a)) return false;
+  const int64_t m = 16 / (a.dtype == B200_F32 ? 4 : 2);
+  if (!al16(a.out) || a.out_bs % m || a.out_ds % m || !al16(a.x)) return false;
+  if (a.z && (!al16(a.out_z) || a.out_z_bs % m || a.out_z_ds % m)) return false;
+  if (a.stage_h && !al16(a.stage_h)) return false;
+  const int64_t warps = (int64_t)a.batch * (a.dim / SCH) * (a.l_segments > 1 ? a.l_segments : 1);
+  return warps >= min_warps();
+}
+
+bool selscan_bwd_sl_supported(const b200_selscan_bwd_args &q) {
+  const b200_selscan_fwd_args &a = q.f;
+  if (!shape_ok(a)) return false;
+  if (!a.stage_h || a.stage_len != ST || !al16(a.stage_h)) return false;
+  if (a.out_z) return false;                                   // recomputation of the gated output: lane-scan kernel
+  const int64_t m = 16 / (a.dtype == B200_F32 ? 4 : 2);
+  if (!al16(q.dout) || !al16(q.du) || !al16(q.ddelta)) return false;
+  if (q.dout_bs % m || q.dout_ds % m || q.du_bs % m || q.du_ds % m || q.ddelta_bs % m || q.ddelta_ds % m) return false;
+  if (a.z && (!al16(a.out) || !al16(q.dz) || a.out_bs % m || a.out_ds % m || q.dz_bs % m || q.dz_ds % m)) return false;
+  return true;      // the forward call chose this kernel family when it wrote the 32-step states
+}
+
+int selscan_fwd_sl(const b200_selscan_fwd_args &a, cudaStream_t st) {
+  if (a.dtype == B200_F32) return launch_fwd<float, 3>(a, st);
+  if (a.dtype == B200_BF16) return launch_fwd<__nv_bfloat16, 4>(a, st);
+  return launch_fwd<__half, 4>(a, st);
+}
+
+int selscan_bwd_sl(const b200_selscan_bwd_args &a, cudaStream_t st) {
+  if (a.f.dtype == B200_F32) return launch_bwd<float>(a, st);
+  if (a.f.dtype == B200_BF16) return launch_bwd<__nv_bfloat16>(a, st);
+  return launch_bwd<__half>(a, st);
+}
+
+}  // namespace b200

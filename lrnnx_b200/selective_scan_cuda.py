@@ -141,7 +141,7 @@ def _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, va
     idx = u.device.index if u.device.index is not None else torch.cuda.current_device()
     if idx not in _SM_COUNT:
         _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    slots = 2 * _SM_COUNT[idx]
+    slots = 8 * _SM_COUNT[idx]     # resident 16-channel warp tiles of the streaming kernel
     ctas = batch * dim // 16
     if ctas >= 4 * slots:
         return 1
@@ -161,21 +161,40 @@ def _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, va
     return best
 
 
-STAGE = 256   # steps per stage of the throughput kernels
+# Stage states: the throughput kernels pass the state at every stage boundary from the forward to
+# the backward call (which then skips recomputing them).  They live behind the checkpoints in x's
+# own allocation, so the reference's fwd / bwd signatures stay as they are.  bwd() recognises an x
+# made by fwd() through a registry of weak references to the storages fwd() allocated (a copy, a
+# user-built x or a recycled address never matches) and falls back to recomputation otherwise.
+_STAGE_REGISTRY = {}     # storage impl pointer -> (weak reference to the storage, stage length)
 
 
-def _stage_numel(batch, dim, seqlen, dstate):
-    return batch * dim * (-(-seqlen // STAGE)) * dstate
+def _stage_numel(batch, dim, seqlen, dstate, stage_len):
+    return batch * dim * (-(-seqlen // stage_len)) * dstate
+
+
+def _register_stage_storage(x, stage_len):
+    from torch.multiprocessing.reductions import StorageWeakRef
+    if len(_STAGE_REGISTRY) > 256:
+        for key in [k for k, (ref, _) in _STAGE_REGISTRY.items() if ref.expired()]:
+            del _STAGE_REGISTRY[key]
+    st = x.untyped_storage()
+    _STAGE_REGISTRY[st._cdata] = (StorageWeakRef(st), stage_len)
 
 
 def _stage_states_of(x_, batch, dim, seqlen, dstate):
-    """Device address of the stage states behind the checkpoints of an x made by fwd(), else None."""
+    """(device address, stage length) of the stage states behind the checkpoints of an x made by
+    fwd(), else (None, 0)."""
     if x_ is None or x_.dtype != torch.float32 or x_.storage_offset() != 0 or not x_.is_contiguous():
-        return None
-    need = (x_.numel() + _stage_numel(batch, dim, seqlen, dstate)) * 4
-    if x_.untyped_storage().nbytes() != need:
-        return None
-    return x_.data_ptr() + x_.numel() * 4
+        return None, 0
+    st = x_.untyped_storage()
+    entry = _STAGE_REGISTRY.get(st._cdata)
+    if entry is None or entry[0].expired():
+        return None, 0
+    stage_len = entry[1]
+    if st.nbytes() != (x_.numel() + _stage_numel(batch, dim, seqlen, dstate, stage_len)) * 4:
+        return None, 0
+    return x_.data_ptr() + x_.numel() * 4, stage_len
 
 
 def _stitch_segments(a, x, S, seqlen, u):
@@ -209,16 +228,16 @@ def fwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, delta_softplus, discret
             a.out_z_bs, a.out_z_ds = out_z.stride(0), out_z.stride(1)
         S = _segments_for(u, batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C, deltaA_,
                           discretization_method_str)
-        if S <= 1 and _lib.lib().b200_selscan_stage_states(ctypes.byref(a)) == 1:
-            # The throughput kernels pass the state at every 256-step stage boundary from the forward
-            # to the backward call (which then skips recomputing them).  The states live behind the
-            # checkpoints in x's own allocation, so the reference's call signatures stay as they are;
-            # bwd() recognises the allocation by its size and falls back to recomputation for any other x.
+        stage_len = _lib.lib().b200_selscan_stage_states(ctypes.byref(a)) if S <= 1 else 0
+        if stage_len > 0:
             x_numel = x.numel()
-            flat = torch.empty(x_numel + _stage_numel(batch, dim, seqlen, dstate), dtype=x.dtype, device=u.device)
+            flat = torch.empty(x_numel + _stage_numel(batch, dim, seqlen, dstate, stage_len), dtype=x.dtype,
+                               device=u.device)
             x = flat[:x_numel].view(batch, dim, n_chunks, dstate * 2)
+            _register_stage_storage(x, stage_len)
             a.x = x.data_ptr()
             a.stage_h = x.data_ptr() + x_numel * x.element_size()
+            a.stage_len = stage_len
         if S > 1:
             a.l_segments = S
             try:
@@ -281,7 +300,7 @@ def bwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, dout, x_, out_, dz_, de
         q = _lib.struct("b200_selscan_bwd_args")()
         f.delta_softplus = int(bool(delta_softplus))
         f.x = _ptr(x_)
-        f.stage_h = _stage_states_of(x_, batch, dim, seqlen, dstate)
+        f.stage_h, f.stage_len = _stage_states_of(x_, batch, dim, seqlen, dstate)
         f.out = _ptr(out)
         if out is not None:
             f.out_bs, f.out_ds = out.stride(0), out.stride(1)

@@ -193,6 +193,36 @@ def simplified_kernel_oracle(u, delta, A, B, C, deltaA=None, discretization="bil
     return (out, torch.stack(ckpt, dim=2)) if return_checkpoints else out
 
 
+def simplified_kernel_grads_oracle(u, delta, A, C, dout, deltaA=None, discretization="bilinear",
+                                  compute_dtype=torch.float32):
+    """Gradients as the simplified-scan backward KERNEL of lrnnx defines them
+    (csrc/simplified_scan/simplified_scan_backward.cuh:213,237,296,315,380): the adjoint is seeded
+    with dout * conj(C) and B enters the recurrence as the constant 1 ("B_term = one"), i.e. the
+    gradients of  out' = sum_s C_s h_s,  h = a h + k * Bp * u  at Bp = 1, with dB := d out'/d Bp.
+    For B = 1 (the only way lrnnx calls the kernel) this is the gradient of the forward output;
+    for other B the forward multiplies the output by B as well and the two differ.
+    Returns (du, ddelta, dA, dB, dC, ddeltaA or None)."""
+    cdt = torch.complex64 if compute_dtype == torch.float32 else torch.complex128
+    leaves = [u.detach().to(cdt).requires_grad_(True), delta.detach().to(compute_dtype).requires_grad_(True),
+              A.detach().to(cdt).requires_grad_(True), torch.ones_like(A, dtype=cdt).requires_grad_(True),
+              C.detach().to(cdt).requires_grad_(True)]
+    if deltaA is not None:
+        leaves.append(deltaA.detach().to(compute_dtype).requires_grad_(True))
+    uc, dl, Aw, Bp, Cw = leaves[:5]
+    dlA = leaves[5] if deltaA is not None else dl
+    batch, P, L = u.shape
+    h = torch.zeros(batch, P, A.shape[1], dtype=cdt)
+    outs = []
+    dl_t, dlA_t, u_t = dl.unbind(-1), dlA.unbind(-1), uc.unbind(-1)
+    for t in range(L):
+        a, k = _discretize(discretization, Aw, dl_t[t], dlA_t[t])
+        h = a * h + k * Bp * u_t[t].unsqueeze(-1)
+        outs.append((h * Cw).sum(-1))
+    out = torch.stack(outs, dim=2)
+    grads = torch.autograd.grad(out, leaves, dout.to(cdt), allow_unused=True)
+    return tuple(grads) + ((None,) if deltaA is None else ())
+
+
 def simplified_scan_oracle(u, delta, A, B, C, deltaA=None, return_last_state=False, discretization="bilinear",
                            compute_dtype=torch.float32):
     """simplified_scan_ref (lrnnx/ops/simplified_scan.py:233-340): u (batch, H, L) complex,
@@ -298,3 +328,120 @@ def vandermonde_oracle(v, x, L, compute_dtype=torch.complex128):
     vv, xx = v.to(compute_dtype), x.to(compute_dtype)
     ar = torch.arange(L, dtype=xx.real.dtype)
     return 2 * torch.einsum("bn,bnl->bl", vv, torch.exp(xx.unsqueeze(-1) * ar)).real
+
+
+# ----------------------------------------------------------------------------- Mamba block and LM
+def causal_conv1d_oracle(x, weight, bias=None, activation=None):
+    """The depthwise causal convolution of lrnnx's Mamba without the causal_conv1d package
+    (lrnnx/models/ltv/mamba.py:270-279): nn.Conv1d(groups=dim, padding=width-1) cut to the input
+    length, then SiLU.  x (batch, dim, L); weight (dim, width); bias (dim,)."""
+    L = x.shape[-1]
+    y = F.conv1d(x, weight.unsqueeze(1), bias, padding=weight.shape[-1] - 1, groups=weight.shape[0])[..., :L]
+    return F.silu(y) if activation in ("silu", "swish") else y
+
+
+def causal_conv1d_update_oracle(x, conv_state, weight, bias=None, activation=None):
+    """The convolution step of Mamba.step (lrnnx/models/ltv/mamba.py:394-409): roll the state,
+    append x, dot with the weights.  x (batch, dim); conv_state (batch, dim, width), in place."""
+    conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+    conv_state[:, :, -1] = x
+    y = torch.sum(conv_state * weight, dim=-1)
+    if bias is not None:
+        y = y + bias
+    return (F.silu(y) if activation in ("silu", "swish") else y).to(x.dtype)
+
+
+def rms_norm_oracle(x, weight, residual=None, eps=1e-6, prenorm=False):
+    """rms_norm_ref without bias, dropout and rowscale (lrnnx/ops/triton/layer_norm.py:84-134)."""
+    dtype = x.dtype
+    if residual is not None:
+        x = (x + residual).to(x.dtype)
+    rstd = 1 / torch.sqrt(x.square().mean(dim=-1, keepdim=True) + eps)
+    out = (x * rstd * weight).to(dtype)
+    return (out, x) if prenorm else out
+
+
+def mamba_mixer_oracle(p, hidden, return_states=False):
+    """Mamba.forward in its plain mode (lrnnx/models/ltv/mamba.py:227-353): in_proj, causal
+    conv + SiLU, x_proj -> (dt, B, C), dt_proj, selective scan with D skip, z gate, dt bias and
+    softplus, out_proj.  ``p`` maps the parameter names of lrnnx's Mamba ("in_proj.weight",
+    "conv1d.weight" (dim, 1, width), "conv1d.bias", "x_proj.weight", "dt_proj.weight",
+    "dt_proj.bias", "A_log", "D", "out_proj.weight") to tensors.  hidden (batch, L, d_model).
+    With ``return_states`` also returns (conv_state, ssm_state) as the layer caches them."""
+    batch, L, _ = hidden.shape
+    d_inner, dt_rank = p["dt_proj.weight"].shape
+    N = p["A_log"].shape[1]
+    width = p["conv1d.weight"].shape[-1]
+    xz = (hidden @ p["in_proj.weight"].t()).transpose(1, 2)          # (batch, 2 d_inner, L)
+    x, z = xz.chunk(2, dim=1)
+    conv_state = F.pad(x, (width - L, 0))
+    x = causal_conv1d_oracle(x, p["conv1d.weight"].squeeze(1), p["conv1d.bias"], "silu")
+    x_dbl = x.transpose(1, 2) @ p["x_proj.weight"].t()               # (batch, L, dt_rank + 2N)
+    dt = (x_dbl[..., :dt_rank] @ p["dt_proj.weight"].t()).transpose(1, 2)
+    Bm = x_dbl[..., dt_rank:dt_rank + N].transpose(1, 2).contiguous()
+    Cm = x_dbl[..., dt_rank + N:].transpose(1, 2).contiguous()
+    A = -torch.exp(p["A_log"].float())
+    y, last = selective_scan_oracle(x, dt, A, Bm, Cm, p["D"].float(), z=z, delta_bias=p["dt_proj.bias"].float(),
+                                    delta_softplus=True, return_last_state=True, discretization="mamba")
+    out = y.transpose(1, 2) @ p["out_proj.weight"].t()
+    return (out, conv_state, last) if return_states else out
+
+
+def mamba_mixer_step_oracle(p, hidden, conv_state, ssm_state):
+    """Mamba.step (lrnnx/models/ltv/mamba.py:355-487): hidden (batch, d_model); both states are
+    updated in place."""
+    d_inner, dt_rank = p["dt_proj.weight"].shape
+    N = p["A_log"].shape[1]
+    xz = hidden @ p["in_proj.weight"].t()
+    x, z = xz.chunk(2, dim=-1)
+    x = causal_conv1d_update_oracle(x, conv_state, p["conv1d.weight"].squeeze(1), p["conv1d.bias"], "silu")
+    x_db = x @ p["x_proj.weight"].t()
+    dt = x_db[:, :dt_rank] @ p["dt_proj.weight"].t()
+    A = -torch.exp(p["A_log"].float())
+    y = selective_state_update_oracle(ssm_state, x, dt, A, x_db[:, dt_rank:dt_rank + N], x_db[:, dt_rank + N:],
+                                      p["D"], z=z, dt_bias=p["dt_proj.bias"], dt_softplus=True)
+    return y @ p["out_proj.weight"].t()
+
+
+def _layer_params(sd, i):
+    pre = f"backbone.layers.{i}.mixer."
+    return {k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)}
+
+
+def mamba_lm_oracle(sd, input_ids, n_layer, eps=1e-5):
+    """LRNNLMHeadModel.forward with Mamba mixers and RMSNorm, residuals in the activation dtype
+    (lrnnx/architectures/language_model.py:453-511,683-727; lrnnx/layers/block.py:60-103):
+    embedding, per layer residual add -> norm -> mixer, final add + norm, tied lm_head.
+    ``sd`` is a state dict with lrnnx's parameter names.  Returns the logits (batch, L, vocab)."""
+    hidden = F.embedding(input_ids, sd["backbone.embedding.weight"])
+    residual = None
+    for i in range(n_layer):
+        normed, residual = rms_norm_oracle(hidden, sd[f"backbone.layers.{i}.norm.weight"], residual, eps, prenorm=True)
+        hidden = mamba_mixer_oracle(_layer_params(sd, i), normed)
+    hidden = rms_norm_oracle(hidden, sd["backbone.norm_f.weight"], residual, eps)
+    return hidden @ sd["lm_head.weight"].t()
+
+
+def mamba_lm_prefill_oracle(sd, input_ids, n_layer, eps=1e-5):
+    """The same forward keeping, per layer, the states a decoder continues from.  Returns
+    (logits of the last position, [(conv_state, ssm_state)] per layer)."""
+    hidden = F.embedding(input_ids, sd["backbone.embedding.weight"])
+    residual, states = None, []
+    for i in range(n_layer):
+        normed, residual = rms_norm_oracle(hidden, sd[f"backbone.layers.{i}.norm.weight"], residual, eps, prenorm=True)
+        hidden, cs, ss = mamba_mixer_oracle(_layer_params(sd, i), normed, return_states=True)
+        states.append((cs.clone(), ss.clone()))
+    hidden = rms_norm_oracle(hidden[:, -1], sd["backbone.norm_f.weight"], residual[:, -1], eps)
+    return hidden @ sd["lm_head.weight"].t(), states
+
+
+def mamba_lm_step_oracle(sd, token_ids, states, n_layer, eps=1e-5):
+    """LRNNModel.step + lm_head (lrnnx/architectures/language_model.py:344-451,653-681) for
+    token ids (batch,); ``states`` is updated in place.  Returns logits (batch, vocab)."""
+    hidden = F.embedding(token_ids, sd["backbone.embedding.weight"])
+    residual = None
+    for i in range(n_layer):
+        normed, residual = rms_norm_oracle(hidden, sd[f"backbone.layers.{i}.norm.weight"], residual, eps, prenorm=True)
+        hidden = mamba_mixer_step_oracle(_layer_params(sd, i), normed, states[i][0], states[i][1])
+    hidden = rms_norm_oracle(hidden, sd["backbone.norm_f.weight"], residual, eps)
+    return hidden @ sd["lm_head.weight"].t()

@@ -8,7 +8,7 @@ they are not needed by the *_ref functions), evaluates them on small seeded
 inputs, back-propagates a seeded upstream gradient through them, and stores
 inputs, outputs and gradients as ``<family>.pt`` (a dict of cases).  The
 fixtures pin oracle/scan_oracle.py (tests/test_oracle_golden.py) and are the
-reference side of the GPU parity tests (tests/test_gpu_golden.py).
+reference side of the GPU parity tests (tests/test_gpu_*.py).
 """
 from __future__ import annotations
 
@@ -20,7 +20,9 @@ from pathlib import Path
 
 import torch
 
-REF = os.environ.get("LRNNX_REF", "/root/reference")
+REF = os.environ.get("LRNNX_REF")
+if not REF:
+    raise SystemExit("set LRNNX_REF to the root of the lrnnx source tree")
 for name in ("selective_scan_cuda", "simplified_scan_cuda", "structured_kernels"):
     m = types.ModuleType(name)
     for attr in ("fwd", "bwd", "cauchy_mult_sym_fwd", "cauchy_mult_sym_bwd", "vand_log_mult_sym_fwd",
@@ -248,12 +250,60 @@ def s4_cases():
     return cases
 
 
+def mamba_lm_cases():
+    """lrnnx's own LRNNLMHeadModel with Mamba mixers, run on CPU: the layer's selective_scan_fn and
+    selective_state_update are rebound to the reference's *_ref functions (same signatures) and
+    RMSNorm.forward to rms_norm_ref, fused_add_norm off (the Triton kernels need a GPU).  Stored:
+    the weights, token ids, the logits of forward(), the gradients of the shifted cross-entropy
+    loss for every parameter, and the logits of step() fed the same tokens one by one."""
+    import torch.nn.functional as F
+    import lrnnx.models.ltv.mamba as M
+    import lrnnx.ops.triton.layer_norm as LN
+    from lrnnx.architectures.language_model import LRNNLMHeadModel
+    M.selective_scan_fn = selective_scan_ref
+    M.selective_state_update = selective_state_update_ref
+    LN.RMSNorm.forward = lambda self, x, residual=None, prenorm=False, residual_in_fp32=False: LN.rms_norm_ref(
+        x, self.weight, None, residual=residual, eps=self.eps, prenorm=prenorm)
+    cases = {}
+    for name, (d_model, n_layer, vocab, batch, L) in {"small": (64, 2, 96, 2, 40), "wide": (128, 3, 160, 3, 24)}.items():
+        torch.manual_seed(5)
+        model = LRNNLMHeadModel(d_model=d_model, d_state=16, n_layer=n_layer, vocab_size=vocab,
+                                mixer_types=["Mamba"] * n_layer, mixer_kwargs={"Mamba": {"discretization": "mamba"}},
+                                rms_norm=True, fused_add_norm=False)
+        # the zero-initialised biases and the unit norm weights are moved off their trivial values
+        g = gen(11)
+        with torch.no_grad():
+            for k, prm in model.named_parameters():
+                if k.endswith("norm.weight") or k.endswith("norm_f.weight"):
+                    prm.add_(0.1 * randn(g, *prm.shape))
+                if k.endswith("conv1d.bias"):
+                    prm.add_(0.1 * randn(g, *prm.shape))
+        ids = torch.randint(0, vocab, (batch, L), generator=g)
+        logits = model(ids).logits
+        loss = F.cross_entropy(logits[:, :-1].reshape(-1, vocab), ids[:, 1:].reshape(-1))
+        names = [k for k, _ in model.named_parameters()]
+        grads = torch.autograd.grad(loss, [prm for _, prm in model.named_parameters()], allow_unused=True)
+        caches = model.allocate_inference_cache(batch, L)
+        step_logits = []
+        with torch.no_grad():
+            for t in range(L):
+                step_logits.append(model.step(ids[:, t:t + 1], caches).logits[:, 0])
+        cases[name] = {
+            "config": dict(d_model=d_model, n_layer=n_layer, vocab_size=vocab, d_state=16, d_conv=4, expand=2, eps=1e-5),
+            "state_dict": {k: v.detach().clone() for k, v in model.state_dict().items() if "dtA_proj" not in k},
+            "input_ids": ids, "logits": logits.detach().clone(), "loss": loss.detach().clone(),
+            "grads": {k: (None if gr is None else gr.detach().clone()) for k, gr in zip(names, grads) if "dtA_proj" not in k},
+            "step_logits": torch.stack(step_logits, dim=1),
+        }
+    return cases
+
+
 def main():
     torch.set_num_threads(4)
     only = set(sys.argv[1:])
     for name, fn in (("selective_scan", selective_cases), ("rglru_s7", rglru_s7_cases),
                      ("simplified_scan", simplified_cases), ("state_update", state_update_cases),
-                     ("s5_step", s5_step_cases), ("s4", s4_cases)):
+                     ("s5_step", s5_step_cases), ("s4", s4_cases), ("mamba_lm", mamba_lm_cases)):
         if only and name not in only:
             continue
         cases = fn()

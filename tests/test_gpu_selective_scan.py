@@ -165,13 +165,22 @@ def test_argument_errors():
         selective_scan_cuda.fwd(u.cpu(), u, A, B, B, None, None, None, None, False, "mamba")
 
 
-@pytest.mark.parametrize("L", [8, 264, 2048, 2312, 4104])
+@pytest.fixture(params=["stream", "lanescan"])
+def kernel_family(request, monkeypatch):
+    """Runs a test once on each throughput-kernel family: the library picks the streaming kernels
+    (one warp per 16 channels, serial in time) when a problem has at least
+    LRNNX_B200_SL_MIN_WARPS warps of work and the lane-scan kernels otherwise."""
+    monkeypatch.setenv("LRNNX_B200_SL_MIN_WARPS", "1" if request.param == "stream" else "1000000000")
+    return request.param
+
+
+@pytest.mark.parametrize("L", [8, 40, 264, 2048, 2312, 4104])
 @pytest.mark.parametrize("dtype,groups", [(torch.float32, 1), (torch.float32, 2), (torch.bfloat16, 1),
                                           (torch.float16, 2)])
-def test_throughput_kernel_shape_class(L, dtype, groups):
+def test_throughput_kernel_shape_class(L, dtype, groups, kernel_family):
     """Shapes served by the packed-fp32 throughput kernels (real A, mamba, variable B/C, dstate 16,
-    channel count a multiple of 16 per group, L a multiple of 8): one and several 256-step
-    stages, a ragged last stage, and a 2048-step checkpoint boundary."""
+    channel count a multiple of 16 per group, L a multiple of 8): one and several stages, a ragged
+    last stage, and a 2048-step checkpoint boundary; on both kernel families."""
     t, g = _make_inputs(2, 32 * groups, 16, L, seed=L, dtype=dtype, groups=groups)
     if dtype == torch.float32:
         _oracle_vs_gpu(t, g, "mamba", RTOL32, ATOL32, GRAD_RTOL32, GRAD_ATOL32)
@@ -179,7 +188,43 @@ def test_throughput_kernel_shape_class(L, dtype, groups):
         _oracle_vs_gpu(t, g, "mamba", 3e-2, 1e-2, 3e-2, 2e-2)
 
 
-def test_throughput_kernel_checkpoints():
+@pytest.mark.parametrize("with_z,with_D,with_bias,softplus", [(False, True, True, True), (True, False, False, False),
+                                                             (False, False, True, False)])
+def test_throughput_kernel_optional_operands(with_z, with_D, with_bias, softplus, kernel_family):
+    """z, D, delta_bias absent and delta_softplus off, on both kernel families."""
+    from lrnnx_b200.ops import selective_scan_fn
+    t, g = _make_inputs(2, 32, 16, 296, seed=5, with_z=with_z)
+    if not with_D:
+        t["D"] = None
+    if not with_bias:
+        t["delta_bias"] = None
+    if not softplus:       # raw step sizes must be positive then
+        t["delta"] = 0.5 * torch.rand(t["delta"].shape, generator=g)
+        if with_bias:
+            t["delta_bias"] = 0.1 * torch.rand(t["delta_bias"].shape, generator=g)
+    kw = dict(delta_softplus=softplus, return_last_state=True, discretization="mamba")
+    cpu = {k: (v.clone().requires_grad_(True) if torch.is_tensor(v) else v) for k, v in t.items()}
+    out_c, last_c = O.selective_scan_oracle(**cpu, **kw)
+    gpu = _to_cuda(t)
+    out_g, last_g = selective_scan_fn(**gpu, **kw)
+    assert_close(out_g.detach().cpu(), out_c.detach(), rtol=RTOL32, atol_scale=ATOL32, name="out")
+    assert_close(last_g.detach().cpu(), last_c.detach(), rtol=RTOL32, atol_scale=ATOL32, name="last_state")
+    gout = torch.randn(out_c.shape, generator=g)
+    names = [k for k, v in cpu.items() if torch.is_tensor(v)]
+    gc = torch.autograd.grad(out_c, [cpu[k] for k in names], gout)
+    gg = torch.autograd.grad(out_g, [gpu[k] for k in names], gout.cuda())
+    for k, a, b in zip(names, gg, gc):
+        assert_close(a.cpu(), b, rtol=GRAD_RTOL32, atol_scale=GRAD_ATOL32, name=f"d{k}")
+
+
+def test_streaming_kernel_many_tiles():
+    """Enough rows that the library picks the streaming kernels by itself (at least two warps of
+    work per SM): 4 x 1280 channels in 2 groups, two stages plus a ragged one."""
+    t, g = _make_inputs(4, 1280, 16, 72, seed=12, groups=2)
+    _oracle_vs_gpu(t, g, "mamba", RTOL32, ATOL32, GRAD_RTOL32, GRAD_ATOL32)
+
+
+def test_throughput_kernel_checkpoints(kernel_family):
     from lrnnx_b200 import selective_scan_cuda
     t, g = _make_inputs(1, 16, 16, 4360, seed=8, with_z=False)
     _, _, x_c = O.selective_scan_oracle(**t, delta_softplus=True, return_last_state=True, return_checkpoints=True)
@@ -192,20 +237,25 @@ def test_throughput_kernel_checkpoints():
 
 
 @pytest.mark.parametrize("dtype,L", [(torch.float32, 4360), (torch.bfloat16, 2048), (torch.bfloat16, 520)])
-def test_backward_with_and_without_saved_stage_states(dtype, L):
-    """The forward call of the throughput kernels leaves the state at every 256-step boundary
+def test_backward_with_and_without_saved_stage_states(dtype, L, kernel_family):
+    """The forward call of the throughput kernels leaves the state at every stage boundary
     behind the checkpoints of x; the backward call uses them when it is handed that x and
-    recomputes them (its first sweep) when it is handed a copy.  Both must give the same gradients."""
+    recomputes them when it is handed a copy, or a tensor of the same size that did not come from
+    fwd().  All must give the same gradients."""
     from lrnnx_b200 import selective_scan_cuda as ext
     t, g = _make_inputs(2, 16, 16, L, seed=31, dtype=dtype)
     cu = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in t.items()}
     args = (cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], cu["z"], cu["delta_bias"], None)
     out, x, out_z = ext.fwd(*args, True, "mamba")
-    assert ext._stage_states_of(x, 2, 16, L, 16) is not None
-    assert ext._stage_states_of(x.clone(), 2, 16, L, 16) is None
+    ptr, stage_len = ext._stage_states_of(x, 2, 16, L, 16)
+    assert ptr is not None and stage_len == (32 if kernel_family == "stream" else 256)
+    assert ext._stage_states_of(x.clone(), 2, 16, L, 16) == (None, 0)
+    # a caller-built x whose allocation happens to have the same size is not mistaken for one made by fwd()
+    fake = torch.empty(x.untyped_storage().nbytes() // 4, device="cuda")[: x.numel()].view_as(x).copy_(x)
+    assert ext._stage_states_of(fake, 2, 16, L, 16) == (None, 0)
     dout = torch.randn(out.shape, generator=g).to(dtype).cuda()
     with_states = ext.bwd(*args, dout, x, out, None, True, False, "mamba")
-    recomputed = ext.bwd(*args, dout, x.clone(), out, None, True, False, "mamba")
+    recomputed = ext.bwd(*args, dout, fake, out, None, True, False, "mamba")
     f32 = dtype == torch.float32
     for i, (a, b) in enumerate(zip(with_states, recomputed)):
         if a is None:

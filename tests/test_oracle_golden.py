@@ -131,3 +131,43 @@ def test_s5_step_oracle(name):
     out = O.simplified_state_update_oracle(state, **t, **case["kwargs"])
     assert_close(out, case["outputs"][0], rtol=RTOL, name="out")
     assert_close(state, case["outputs"][1], rtol=RTOL, name="state")
+
+
+# ----------------------------------------------------------------------------- Mamba LM (configs 2 and 4 harness)
+LM = load_golden("mamba_lm")
+
+
+@pytest.mark.parametrize("name", sorted(LM))
+def test_mamba_lm_oracle_matches_reference_model(name):
+    """The oracle's restatement of LRNNLMHeadModel (Mamba mixers, RMSNorm) against the logits,
+    parameter gradients and step() logits recorded from lrnnx's own model."""
+    import torch.nn.functional as F
+    case = LM[name]
+    cfg = case["config"]
+    sd = {k: v.clone().requires_grad_(True) for k, v in case["state_dict"].items()}
+    sd["lm_head.weight"] = sd["backbone.embedding.weight"]          # tied (language_model.py:573,604-613)
+    ids = case["input_ids"]
+    logits = O.mamba_lm_oracle(sd, ids, cfg["n_layer"], cfg["eps"])
+    torch.testing.assert_close(logits, case["logits"], rtol=RTOL, atol=1e-5)
+    loss = F.cross_entropy(logits[:, :-1].reshape(-1, cfg["vocab_size"]), ids[:, 1:].reshape(-1))
+    torch.testing.assert_close(loss, case["loss"], rtol=RTOL, atol=1e-6)
+    names = [k for k, g in case["grads"].items() if g is not None and k != "lm_head.weight"]
+    grads = torch.autograd.grad(loss, [sd[k] for k in names])
+    for k, g in zip(names, grads):
+        want = case["grads"][k]
+        torch.testing.assert_close(g, want, rtol=1e-4, atol=1e-6 + 1e-5 * float(want.abs().max()), msg=lambda m: f"{k}: {m}")
+    # step by step from zero states, and prefill + continue
+    sd = {k: v.detach() for k, v in sd.items()}
+    batch, L = ids.shape
+    d_inner = cfg["expand"] * cfg["d_model"]
+    states = [(torch.zeros(batch, d_inner, cfg["d_conv"]), torch.zeros(batch, d_inner, cfg["d_state"]))
+              for _ in range(cfg["n_layer"])]
+    for t in range(L):
+        lg = O.mamba_lm_step_oracle(sd, ids[:, t], states, cfg["n_layer"], cfg["eps"])
+        torch.testing.assert_close(lg, case["step_logits"][:, t], rtol=1e-4, atol=1e-5)
+    cut = L // 2
+    lg, states = O.mamba_lm_prefill_oracle(sd, ids[:, :cut], cfg["n_layer"], cfg["eps"])
+    torch.testing.assert_close(lg, case["logits"][:, cut - 1], rtol=1e-4, atol=1e-5)
+    for t in range(cut, L):
+        lg = O.mamba_lm_step_oracle(sd, ids[:, t], states, cfg["n_layer"], cfg["eps"])
+        torch.testing.assert_close(lg, case["logits"][:, t], rtol=1e-4, atol=2e-5)
