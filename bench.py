@@ -23,7 +23,8 @@ x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
   cpu_baseline  the CPU oracle (a port of the reference's pure-PyTorch scan) timed on the
              host cores on a bounded sample of the same workload.
 
-  workloads  the default run adds one sub-record per further workload of the hot path, each with
+  workloads  the default run adds one sub-record per further workload (lm_cfg2: configs[2] LM training
+             step; decode_cfg4: configs[4] generation; and the kernel-level ones below), each with
              its own ms_per_step, value, roofline, kernels, e2e and cpu_baseline (fewer steps each,
              so that the whole run stays within a few minutes): s6_cfg0 (configs[0]), s6_layer and
              s6_layer_f32 (one Mamba layer's scan at the configs[2] shape), s6_long (configs[3];
@@ -61,6 +62,14 @@ def measured_peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured (sustained bf16 GEMM)"
+    return 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -175,6 +184,7 @@ class S5Scan:
             self._set_sizes()
             self.scaling = "strong"
             self.describe["parallelism"] = f"batch of {self.batch * w} split over {w} GPUs ({self.batch} per GPU)"
+            self.describe["global_batch"] = self.batch * w
         h = self.host_inputs()
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if self.flush else None
         self.h_x = h["u"].real.transpose(1, 2).contiguous().pin_memory()      # (batch, L, H) float32: the layer's input
@@ -713,6 +723,169 @@ class CauchyKernel:
         return 64 * self.L
 
 
+class LmTrain:
+    """BASELINE configs[2]: Mamba LM, 24 layers, d_model 768 (d_inner 1536, dstate 16, dt_rank 48,
+    conv 4), vocabulary 50280, random-init bf16 weights, token ids uniform in [0, 50280), batch 8 x
+    2048 tokens, forward + backward of the shifted cross-entropy + a fused AdamW step.  The batch
+    is split over the ranks (fixed total work); gradients are all-reduced in buckets overlapped
+    with the backward pass (DistributedDataParallel over NCCL)."""
+    name = "lm_cfg2"
+    dtype = "bf16 weights and activations, f32 scan state"
+    metric, unit = "training tokens/s (LM forward + backward + optimizer step)", "tokens/s"
+    scaling = "strong"
+    roofline_note = ("whole training step against the dense bf16 rate: 6 x parameters x tokens floating-point operations "
+                     "(projections and LM head); the scan, convolution and norm kernels inside it are HBM / SFU bound")
+
+    def __init__(self, batch=8, L=2048, d_model=768, n_layer=24, vocab=50280):
+        self.batch, self.L, self.d_model, self.n_layer, self.vocab = batch, L, d_model, n_layer, vocab
+        self.describe = {"workload": f"{self.name}: Mamba LM {n_layer} layers d_model {d_model} vocab {vocab}, "
+                                     f"batch {batch} x {L} tokens, fwd + bwd + AdamW",
+                         "global_batch": batch, "seq_len": L,
+                         "l2": "weights, activations and logits of a step (several GB) exceed the 126 MB L2"}
+
+    def setup(self, dev, pg):
+        from lrnnx_b200.lm import MambaLMHeadModel
+        self.dev, self.pg = dev, pg
+        w = torch.distributed.get_world_size() if pg is not None else 1
+        r = torch.distributed.get_rank() if pg is not None else 0
+        self.local_batch = max(1, self.batch // w)
+        self.tokens = self.local_batch * self.L
+        self.describe["parallelism"] = f"data parallel: {self.local_batch} of {self.batch} sequences per GPU" if w > 1 else "single GPU"
+        torch.manual_seed(0)
+        model = MambaLMHeadModel(self.d_model, self.n_layer, self.vocab, device=dev, dtype=torch.bfloat16)
+        self.n_params = sum(p.numel() for p in model.parameters())
+        self.model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index]) if pg is not None else model
+        self.opt = torch.optim.AdamW(self.model.parameters(), lr=1e-4, fused=True)
+        g = torch.Generator().manual_seed(r)
+        self.h_ids = torch.randint(0, self.vocab, (self.local_batch, self.L), generator=g).pin_memory()
+        self.ids = self.h_ids.to(dev)
+        self.ev = []
+        self.launches_per_step = self.n_layer * 8          # conv, scan, norm forward and backward per layer (this package's kernels)
+
+    def _train(self, ids):
+        logits = self.model(ids)
+        loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, self.vocab).float(), ids[:, 1:].reshape(-1))
+        self.opt.zero_grad(set_to_none=True)
+        loss.backward()
+        self.opt.step()
+        return loss
+
+    def step(self, record=False):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(2)] if record else None
+        if record:
+            e[0].record()
+        loss = self._train(self.ids)
+        if record:
+            e[1].record()
+            self.ev.append(e)
+        return loss
+
+    def e2e_step(self):
+        self.ids.copy_(self.h_ids, non_blocking=True)
+        return float(self._train(self.ids).item())
+
+    def e2e_bytes(self):
+        return self.h_ids.numel() * 8, 4
+
+    def kernel_rooflines(self):
+        ms = statistics.mean(a[0].elapsed_time(a[1]) for a in self.ev)
+        return {"lm_train_step": (0, ms, {"tensor_flops": 6.0 * self.n_params * self.tokens})}
+
+    cpu_sample = "2 of 24 layers, 1 sequence of 256 tokens, float32 (extrapolated by layers x tokens)"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            from lrnnx_b200.lm import MambaLMHeadModel
+            torch.manual_seed(0)
+            m = MambaLMHeadModel(self.d_model, 2, self.vocab)
+            self._cpu = ({k: v.detach().requires_grad_(True) for k, v in m.state_dict().items()},
+                         torch.randint(0, self.vocab, (1, 256)))
+        sd, ids = self._cpu
+        logits = O.mamba_lm_oracle(sd, ids, 2)
+        loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, self.vocab), ids[:, 1:].reshape(-1))
+        torch.autograd.grad(loss, [v for k, v in sd.items() if k != "lm_head.weight"], allow_unused=True)
+        return 256 * 2 / self.n_layer
+
+
+class LmDecode:
+    """BASELINE configs[4]: Mamba LM at the 1.4B shape (48 layers, d_model 2048, d_inner 4096,
+    dstate 16, dt_rank 128), random-init bf16 weights, batch 64 (split over the ranks), random
+    prompts of 512 tokens prefilled through the scan kernels, then 256 greedy tokens replayed from
+    one captured CUDA graph of the decoding step.  A step of this workload is one whole generation."""
+    name = "decode_cfg4"
+    dtype = "bf16 weights and activations, f32 scan state"
+    metric, unit = "generated tokens/s (prefill 512 + 256 new tokens, CUDA-graph decoding)", "tokens/s"
+    scaling = "strong"
+    roofline_note = ("decoding is bound by reading the weights (2.7 GB) and the recurrent states (1.7 GB, read and "
+                     "written) once per generated token; the fraction is of the measured HBM copy rate")
+
+    def __init__(self, batch=64, prompt=512, new=256, d_model=2048, n_layer=48, vocab=50280):
+        self.batch, self.prompt, self.new = batch, prompt, new
+        self.d_model, self.n_layer, self.vocab = d_model, n_layer, vocab
+        self.describe = {"workload": f"{self.name}: Mamba LM {n_layer} layers d_model {d_model}, batch {batch}, "
+                                     f"prompt {prompt}, {new} generated tokens, CUDA-graph replay",
+                         "global_batch": batch, "seq_len": prompt + new,
+                         "l2": "weights and states read per token (4.4 GB) exceed the 126 MB L2"}
+
+    def setup(self, dev, pg):
+        from lrnnx_b200.lm import MambaLMHeadModel
+        self.dev, self.pg = dev, pg
+        w = torch.distributed.get_world_size() if pg is not None else 1
+        r = torch.distributed.get_rank() if pg is not None else 0
+        self.local_batch = max(1, self.batch // w)
+        self.tokens = self.local_batch * self.new
+        self.describe["parallelism"] = f"batch shards: {self.local_batch} of {self.batch} sequences per GPU" if w > 1 else "single GPU"
+        torch.manual_seed(0)
+        self.model = MambaLMHeadModel(self.d_model, self.n_layer, self.vocab, device=dev, dtype=torch.bfloat16).eval()
+        self.n_params = sum(p.numel() for p in self.model.parameters())
+        g = torch.Generator().manual_seed(r)
+        self.h_prompt = torch.randint(0, self.vocab, (self.local_batch, self.prompt), generator=g).pin_memory()
+        self.d_prompt = self.h_prompt.to(dev)
+        self.t = []
+        self.launches_per_step = self.n_layer * 3 * (self.new - 1) + self.n_layer * 3   # norm, conv update, state update per layer and token; prefill
+
+    def step(self, record=False):
+        tm = {} if record else None
+        out = self.model.generate(self.d_prompt, self.new, use_cuda_graph=True, timings=tm)
+        if record:
+            self.t.append(tm)
+        return out
+
+    def e2e_step(self):
+        self.d_prompt.copy_(self.h_prompt, non_blocking=True)
+        return int(self.step().cpu()[0, -1])
+
+    def e2e_bytes(self):
+        return self.h_prompt.numel() * 8, self.local_batch * self.new * 8
+
+    def kernel_rooflines(self):
+        dec = statistics.mean(t["decode_ms"] for t in self.t) / (self.new - 1)
+        pre = statistics.mean(t["prefill_ms"] for t in self.t)
+        d_inner = 2 * self.d_model
+        state_bytes = self.n_layer * self.local_batch * d_inner * (2 * 16 * 4 + 2 * 4 * 2)     # scan state r+w, conv state r+w
+        per_token = 2 * self.n_params + state_bytes
+        self.describe["prefill_ms"] = pre
+        return {"decode_step_graph": (per_token, dec)}
+
+    cpu_sample = "2 of 48 layers, full batch, one decoding step, float32 (extrapolated by layers)"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            from lrnnx_b200.lm import MambaLMHeadModel
+            torch.manual_seed(0)
+            m = MambaLMHeadModel(self.d_model, 2, self.vocab)
+            sd = {k: v.detach() for k, v in m.state_dict().items()}
+            d_inner = 2 * self.d_model
+            states = [(torch.zeros(self.batch, d_inner, 4), torch.zeros(self.batch, d_inner, 16)) for _ in range(2)]
+            self._cpu = (sd, states, torch.randint(0, self.vocab, (self.batch,)))
+        sd, states, tok = self._cpu
+        with torch.no_grad():
+            O.mamba_lm_step_oracle(sd, tok, states, 2)
+        return self.batch * 2 / self.n_layer
+
+
 def make_workload(name, sub=False):
     """``sub``: the workload is a sub-record of the default run (bounded CPU sample)."""
     if name in ("s5_scan", "s5_scan_cfg1", "default"):
@@ -733,10 +906,15 @@ def make_workload(name, sub=False):
         return SsuStep()
     if name in ("cauchy", "cauchy_s4"):
         return CauchyKernel()
+    if name == "lm_cfg2":
+        return LmTrain()
+    if name == "decode_cfg4":
+        return LmDecode()
     raise SystemExit(f"unknown workload {name}")
 
 
-SUB_WORKLOADS = ("s6_cfg0", "s6_layer", "s6_layer_f32", "s6_long", "ssu_step", "cauchy", "s5_scan_zoh")
+SUB_WORKLOADS = ("s6_cfg0", "s6_layer", "s6_layer_f32", "s6_long", "ssu_step", "cauchy", "s5_scan_zoh", "lm_cfg2",
+                 "decode_cfg4")
 
 # nominal fp32 rate of one B200: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz (no measured figure exists)
 FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
@@ -820,6 +998,12 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
         roofs[kname] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                         "traffic": NCU_TRAFFIC.get((wl.name, kname)), "algorithmic_bytes": nbytes,
                         "ms_per_launch": ms, "peak_source": peak_kind}
+        if "tensor_flops" in extra:     # a step bound by dense bf16 GEMMs: fraction of the measured (sustained) rate
+            tf = extra["tensor_flops"] / (ms * 1e-3) / 1e12
+            tpeak, tkind = measured_tensor_peak()
+            roofs[kname] = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
+                            "traffic": None, "algorithmic_flops": extra["tensor_flops"], "ms_per_launch": ms,
+                            "peak_source": tkind}
         if "flops" in extra:     # a kernel bound by the fp32 pipe: the fraction is of the fp32 rate
             tf = extra["flops"] / (ms * 1e-3) / 1e12
             roofs[kname].update({"bound": "fp32", "achieved": tf, "peak": FP32_PEAK_TFLOPS, "unit": "TFLOP/s",
@@ -834,8 +1018,8 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
     strong = getattr(wl, "scaling", "weak") == "strong"
     total_tokens = wl.tokens * (1 if (strong and getattr(wl, "sp", False)) else world)
     describe = dict(wl.describe)
-    if "global_batch" in describe and not getattr(wl, "sp", False):
-        describe["global_batch"] = describe["global_batch"] * world     # every rank runs its own batch shard
+    if "global_batch" in describe and not strong:
+        describe["global_batch"] = describe["global_batch"] * world     # weak scaling: every rank runs its own full batch
     rec = {"metric": wl.metric, "value": total_tokens / (ms_step * 1e-3), "unit": wl.unit,
            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,

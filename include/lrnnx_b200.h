@@ -384,6 +384,39 @@ typedef struct b200_rmsnorm_args {
 int b200_rmsnorm_fwd(const b200_rmsnorm_args *args, void *stream);
 int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream);
 
+/* ------------------------------------------------------------------------
+ * Complex projection on the tensor cores (tcgen05, 3xTF32: float32-class accuracy):
+ *     out[b] (M x N) = W (M x K) * x[b] (K x N),  complex64.
+ * Replaces the torch.einsum calls (cuBLAS cgemm) around the simplified scan in lrnnx's
+ * SimplifiedScanFn / S5InnerFn (lrnnx/ops/simplified_scan.py:67,87,136,165,401,419,483-524):
+ * Bu = B~ u, y = C~ x and the data gradients du = B~^H dBu, dx = C~^H dy.
+ *   w_planes : float32 (4, M, K), K contiguous: Re(W) rounded to TF32 (low 13 mantissa bits
+ *              zero), the remainder rounded to TF32, and the same two planes of Im(W)
+ *   x        : complex64 (batch, K, N) dense;  out : complex64 (batch, M, N), N contiguous
+ * M a multiple of 128, K of 32, N of 64; all pointers 16-byte aligned.
+ * ------------------------------------------------------------------------ */
+typedef struct b200_cgemm_args {
+  int32_t batch, M, K, N;
+  const void *w_planes, *x;
+  void *out;
+  int64_t x_bs, x_ks;        /* complex elements */
+  int64_t out_bs, out_ms;    /* complex elements */
+} b200_cgemm_args;
+
+int b200_cgemm_wx(const b200_cgemm_args *args, void *stream);
+
+/* Builds the w_planes operand of b200_cgemm_wx from a complex64 matrix W (M, K) given by element
+ * strides (so a transposed view is free), optionally conjugated (conj != 0): planes is float32
+ * (4, M, K), written densely. */
+typedef struct b200_cgemm_planes_args {
+  int32_t M, K, conj, reserved0;
+  const void *w;
+  void *planes;
+  int64_t w_rs, w_cs;        /* complex elements */
+} b200_cgemm_planes_args;
+
+int b200_cgemm_planes(const b200_cgemm_planes_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

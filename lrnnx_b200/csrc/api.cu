@@ -57,6 +57,8 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_s5_step_args")) return (int)sizeof(b200_s5_step_args);
   if (!strcmp(name, "b200_conv1d_args")) return (int)sizeof(b200_conv1d_args);
   if (!strcmp(name, "b200_rmsnorm_args")) return (int)sizeof(b200_rmsnorm_args);
+  if (!strcmp(name, "b200_cgemm_args")) return (int)sizeof(b200_cgemm_args);
+  if (!strcmp(name, "b200_cgemm_planes_args")) return (int)sizeof(b200_cgemm_planes_args);
   return -1;
 }
 

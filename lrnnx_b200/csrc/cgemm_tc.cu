@@ -1,0 +1,410 @@
+// Complex projections around the S5 scan on the 5th-generation tensor cores (tcgen05 + TMEM):
+//     out[b] (M x N) = W (M x K) * X[b] (K x N),      complex64, N contiguous,
+// the shape of  Bu = B~ u,  y = C~ x  and of the two data gradients  du = B~^H dBu,  dx = C~^H dy
+// of lrnnx's simplified_scan_fn / s5_inner_fn (lrnnx/ops/simplified_scan.py:67,87,136,165,401,419,
+// 483-524), which lrnnx evaluates with torch.einsum (cuBLAS SIMT cgemm).
+//
+// Arithmetic.  With X' the (K x 2N) float view of X (re/im interleaved along N),
+//     D1 = Re(W) X',   D2 = Im(W) X'     (two real GEMMs sharing the activation tile)
+//     out_re[n] = D1[2n] - D2[2n+1],   out_im[n] = D1[2n+1] + D2[2n]
+// so the activation is consumed exactly as it lies in memory and only the small weight is split
+// into planes.  fp32-class accuracy on TF32 tensor cores comes from the 3xTF32 split
+//     a b ~= a_hi b_hi + a_lo b_hi + a_hi b_lo,   x_hi = tf32(x), x_lo = tf32(x - x_hi),
+// i.e. six tcgen05.mma per K step.  The weight planes (Re hi, Re lo, Im hi, Im lo) are prepared
+// once per call on the host side; the low part of the activation tile is produced inside the
+// kernel, in shared memory, by the warps that later run the epilogue: it is elementwise, so it is
+// written at the same (swizzled) offsets the TMA used for the tile and no layout knowledge is needed.
+//
+// One CTA per 128 x 64-complex output tile: warp 0 issues the TMA loads (128-byte swizzled
+// tiles, 2-stage ring on mbarriers), warp 1 allocates 256 TMEM columns and issues the MMAs
+// (M = 128, N = 128 floats, K = 8 per instruction; A = weight plane, K-major, 128-byte swizzle;
+// B = activation, MN-major, 128-byte swizzle of 32-byte chunks), warps 2-5 split the activation tile during the main loop and afterwards read the
+// two accumulators with tcgen05.ld, combine them and store complex rows.  Every mbarrier wait is
+// bounded; an expired wait sets the status word, skips the stores and still frees the TMEM.
+#include "common.cuh"
+#include "dispatch.h"
+#include <cuda.h>   // CUtensorMap and its enums (types only: the encoder is looked up at run time)
+#include <cstring>
+
+namespace b200 {
+namespace {
+
+__device__ int g_cgemm_status = 0;
+#ifdef CGEMM_DEBUG
+__device__ float g_dbg[8192];
+#endif
+
+constexpr int GM = 128;               // weight rows per CTA
+constexpr int GN = 128;               // activation floats per CTA (64 complex columns)
+constexpr int GK = 32;                // floats of K per stage: one 128-byte swizzle row
+constexpr int NSTAGE = 2;
+constexpr int TILE = GM * GK * 4;     // 16 KB: a weight-plane tile; an activation tile has the same size
+constexpr int STAGE_BYTES = 6 * TILE; // Re hi, Re lo, Im hi, Im lo, X hi, X lo
+constexpr int TX_BYTES = 5 * TILE;    // what the TMA delivers per stage (X lo is produced in place)
+constexpr int NTHREADS = 192;
+constexpr int TMEM_COLS = 256;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+struct GemmMaps {
+  CUtensorMap w;      // (K, 4 M) float32, box (32, 128)
+  CUtensorMap x;      // (2 N, batch K) float32, box (32, 32)
+};
+
+__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// shared-memory matrix descriptor (descriptor version 1).  layout 2: 128-byte swizzle of 16-byte
+// chunks (the K-major weight tiles); layout 1: 128-byte swizzle of 32-byte chunks, the only
+// layout the tensor core accepts for an MN-major operand of 32-bit elements (the activation tile).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout) {
+  return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (layout << 61);
+}
+// weight-plane tile, K-major: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t a_desc(uint32_t addr) { return smem_desc(addr, 16, 1024, 2); }
+// activation tile, MN-major: 32-float column groups 4096 bytes apart, 4-row K groups 512 bytes apart
+__device__ __forceinline__ uint64_t b_desc(uint32_t addr) { return smem_desc(addr, 4096, 512, 1); }
+// instruction descriptor: D f32, A and B tf32, A K-major, B MN-major, M = 128, N = 128
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((GN >> 3) << 17) | ((GM >> 4) << 24);
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
+                                         uint32_t idesc = kIdesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+// The tensor core truncates a 32-bit operand to TF32, so the high part of x is what it reads from
+// the tile as it is; the low part x - trunc(x) is exact in float32 and is rounded to the nearest
+// TF32 here (the hardware would truncate it, a one-sided error that adds up over K).
+__device__ __forceinline__ float tf32_low(float v) {
+  const float r = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+  return __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xffffe000u);
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive columns of this thread's TMEM lane.  The load is asynchronous: the registers
+// are valid only after tcgen05.wait::ld, so load and wait sit in ONE asm statement; as separate
+// statements the compiler would be free to schedule uses of the outputs before the wait.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // 1024-byte alignment of the tiles (the swizzle atom) is established by hand: the dynamic
+  // shared-memory base is only guaranteed to be 16-byte aligned
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full[NSTAGE], empty[NSTAGE], lo_ready[NSTAGE], acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int fail_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * GN;              // float column of the activation view
+  const int m0 = blockIdx.y * GM;
+  const int b = blockIdx.z;
+  const int nk = p.K / GK;
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&lo_ready[s], 4);            // one arrival per transforming warp
+    }
+    mbar_init(&acc_done, 1);
+    fail_s = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+#ifdef CGEMM_DEBUG
+  if (warp >= 2) {      // fill both accumulators with 7.0: tells "the MMA wrote zeros" from "the MMA wrote nothing"
+    const uint32_t seven = __float_as_uint(7.0f);
+    for (int c = 0; c < TMEM_COLS / 32; ++c) {
+      const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + c * 32;
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+          "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+          "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};\n\t"
+          "tcgen05.wait::st.sync.aligned;" ::"r"(ta), "r"(seven) : "memory");
+    }
+  }
+  if (warp == 4) {
+    float rb[32];
+    tmem_ld32(tmem_base + 0, rb);
+    if (lane < 2) for (int i = 0; i < 8; ++i) g_dbg[4100 + lane * 8 + i] = rb[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0) g_dbg[4000] = __uint_as_float(tmem_base);
+#endif
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int ks = 0; ks < nk; ++ks) {
+        const int s = ks % NSTAGE;
+        if (ks >= NSTAGE && !mbar_wait(&empty[s], ((ks / NSTAGE) - 1) & 1, WAIT_LIMIT)) { atomicExch(&fail_s, 1); break; }
+        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], TX_BYTES);
+        const int k0 = ks * GK;
+#pragma unroll
+        for (int pl = 0; pl < 4; ++pl) tma_2d(st + pl * TILE, &maps.w, k0, pl * p.M + m0, &full[s]);
+#pragma unroll
+        for (int j = 0; j < GN / 32; ++j) tma_2d(st + 4 * TILE + j * 4096, &maps.x, n0 + 32 * j, b * p.K + k0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t d1 = tmem_base, d2 = tmem_base + GN;
+      bool ok = true;
+      for (int ks = 0; ks < nk && ok; ++ks) {
+        const int s = ks % NSTAGE;
+        const uint32_t ph = (ks / NSTAGE) & 1;
+        if (!mbar_wait(&full[s], ph, WAIT_LIMIT)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+#ifdef CGEMM_DEBUG
+        if (ks == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          const uint64_t da = a_desc(st), db = b_desc(st + 4 * TILE);
+          g_dbg[4200] = __uint_as_float(st);
+          g_dbg[4201] = __uint_as_float((uint32_t)da); g_dbg[4202] = __uint_as_float((uint32_t)(da >> 32));
+          g_dbg[4203] = __uint_as_float((uint32_t)db); g_dbg[4204] = __uint_as_float((uint32_t)(db >> 32));
+          g_dbg[4205] = __uint_as_float(kIdesc);
+          g_dbg[4206] = __uint_as_float(smem_u32(smem_raw));
+        }
+#endif
+#ifdef CGEMM_EXP_KK
+        {                        // experiment: D1 = ReHi * ReHi^T with both operands K-major
+          for (int kk = 0; kk < GK / 8; ++kk) {
+            const uint64_t ad = a_desc(st + kk * 32);
+            mma_tf32(d1, ad, ad, kk > 0 ? 1u : 0u, kIdesc & ~(1u << 16));
+          }
+          if (!mbar_wait(&lo_ready[s], ph, WAIT_LIMIT)) { ok = false; break; }
+          mma_commit(&empty[s]);
+          continue;
+        }
+#endif
+        // products with the high part of the activation
+#pragma unroll
+        for (int kk = 0; kk < GK / 8; ++kk) {
+          const uint64_t bh = b_desc(st + 4 * TILE + kk * 1024);
+          const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+          mma_tf32(d1, a_desc(st + 0 * TILE + kk * 32), bh, acc);
+          mma_tf32(d1, a_desc(st + 1 * TILE + kk * 32), bh, 1u);
+          mma_tf32(d2, a_desc(st + 2 * TILE + kk * 32), bh, acc);
+          mma_tf32(d2, a_desc(st + 3 * TILE + kk * 32), bh, 1u);
+        }
+        // products with its low part, once the other warps have written it
+        if (!mbar_wait(&lo_ready[s], ph, WAIT_LIMIT)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < GK / 8; ++kk) {
+          const uint64_t bl = b_desc(st + 5 * TILE + kk * 1024);
+          mma_tf32(d1, a_desc(st + 0 * TILE + kk * 32), bl, 1u);
+          mma_tf32(d2, a_desc(st + 2 * TILE + kk * 32), bl, 1u);
+        }
+        mma_commit(&empty[s]);        // the stage may be refilled once these MMAs have read it
+      }
+      if (!ok) atomicExch(&fail_s, 1);
+      mma_commit(&acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ activation split, then epilogue
+    const int et = tid - 64;                    // 0..127
+    bool ok = true;
+    for (int ks = 0; ks < nk && ok; ++ks) {
+      const int s = ks % NSTAGE;
+      if (!mbar_wait(&full[s], (ks / NSTAGE) & 1, WAIT_LIMIT)) { ok = false; break; }
+      const float4 *hi = reinterpret_cast<const float4 *>(smem + (size_t)s * STAGE_BYTES + 4 * TILE);
+      float4 *lo = reinterpret_cast<float4 *>(smem + (size_t)s * STAGE_BYTES + 5 * TILE);
+#pragma unroll
+      for (int i = 0; i < TILE / 16 / 128; ++i) {
+        const float4 v = hi[i * 128 + et];
+        float4 r;
+        r.x = tf32_low(v.x);
+        r.y = tf32_low(v.y);
+        r.z = tf32_low(v.z);
+        r.w = tf32_low(v.w);
+        lo[i * 128 + et] = r;
+      }
+#ifdef CGEMM_DEBUG
+      if (ks == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        const float *t0 = reinterpret_cast<const float *>(smem + (size_t)s * STAGE_BYTES);
+        for (int i = et; i < 6 * 256; i += 128) g_dbg[i] = t0[(i / 256) * (TILE / 4) + (i % 256)];
+      }
+#endif
+      fence_proxy_async();                      // generic-proxy writes -> visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&lo_ready[s]);
+    }
+    if (!ok) atomicExch(&fail_s, 1);
+    // epilogue: TMEM lane = output row; this warp reads the lane quarter it is allowed to
+    if (ok && mbar_wait(&acc_done, 0, WAIT_LIMIT) && fail_s == 0) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int row = q * 32 + lane;
+      float2 *orow = reinterpret_cast<float2 *>(p.out) + (int64_t)b * p.out_bs + (int64_t)(m0 + row) * p.out_ms + n0 / 2;
+#pragma unroll 1
+      for (int c = 0; c < GN / 32; ++c) {
+        float v1[32], v2[32];
+        const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + c * 32;
+        tmem_ld32(ta, v1);
+        tmem_ld32(ta + GN, v2);
+#ifdef CGEMM_DEBUG
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && c == 0 && row < 4)
+          for (int i = 0; i < 32; ++i) { g_dbg[2048 + row * 64 + i] = v1[i]; g_dbg[2048 + row * 64 + 32 + i] = v2[i]; }
+#endif
+        float4 *dst = reinterpret_cast<float4 *>(orow + c * 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          dst[j] = make_float4(v1[4 * j] - v2[4 * j + 1], v1[4 * j + 1] + v2[4 * j], v1[4 * j + 2] - v2[4 * j + 3],
+                               v1[4 * j + 3] + v2[4 * j + 2]);
+      }
+    } else {
+      atomicExch(&fail_s, 1);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (tid == 0 && fail_s) atomicExch(&g_cgemm_status, 5);
+}
+
+// Weight planes for cgemm_wx_kernel: (4, M, K) float32 = tf32(Re W), tf32(Re W - that), and the same
+// for Im W, from a complex64 matrix addressed by element strides (a transposed view costs nothing)
+// and optionally conjugated.
+__global__ void cgemm_planes_kernel(const float2 *w, int M, int K, int64_t rs, int64_t cs, int conj, float *planes) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)M * K) return;
+  const int m = (int)(i / K), k = (int)(i % K);
+  float2 v = w[(int64_t)m * rs + (int64_t)k * cs];
+  if (conj) v.y = -v.y;
+  const float rh = __uint_as_float((__float_as_uint(v.x) + 0x1000u) & 0xffffe000u);
+  const float ih = __uint_as_float((__float_as_uint(v.y) + 0x1000u) & 0xffffe000u);
+  const float rl = v.x - rh, il = v.y - ih;
+  const int64_t MK = (int64_t)M * K;
+  planes[i] = rh;
+  planes[MK + i] = __uint_as_float((__float_as_uint(rl) + 0x1000u) & 0xffffe000u);
+  planes[2 * MK + i] = ih;
+  planes[3 * MK + i] = __uint_as_float((__float_as_uint(il) + 0x1000u) & 0xffffe000u);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    tried = true;
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap *m, const void *base, uint64_t inner, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+              CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {32, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+int cgemm_status_read() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_cgemm_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#ifdef CGEMM_DEBUG
+extern "C" int b200_cgemm_debug(float *host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_dbg, n * sizeof(float));
+}
+#endif
+
+extern "C" int b200_cgemm_planes(const b200_cgemm_planes_args *args, void *stream) {
+  B200_REQUIRE(args && args->w && args->planes, B200_ERR_NULL, "cgemm_planes: w and planes must be non-null");
+  B200_REQUIRE(args->M > 0 && args->K > 0, B200_ERR_SHAPE, "cgemm_planes: sizes must be positive");
+  const int64_t n = (int64_t)args->M * args->K;
+  cgemm_planes_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float2 *>(args->w), args->M, args->K, args->w_rs, args->w_cs, args->conj,
+      reinterpret_cast<float *>(args->planes));
+  return launch_status();
+}
+
+extern "C" int b200_cgemm_wx(const b200_cgemm_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "cgemm_wx: null argument block");
+  const b200_cgemm_args &a = *args;
+  B200_REQUIRE(a.w_planes && a.x && a.out, B200_ERR_NULL, "cgemm_wx: w_planes, x, out must be non-null");
+  B200_REQUIRE(a.batch > 0 && a.M > 0 && a.K > 0 && a.N > 0, B200_ERR_SHAPE, "cgemm_wx: sizes must be positive");
+  B200_REQUIRE(a.M % GM == 0 && a.K % GK == 0 && (2 * (int64_t)a.N) % GN == 0, B200_ERR_SHAPE,
+               "cgemm_wx: M must be a multiple of %d, K of %d, N of %d (got M=%d K=%d N=%d)", GM, GK, GN / 2, a.M, a.K, a.N);
+  B200_REQUIRE(a.x_ks == a.N && a.x_bs == (int64_t)a.K * a.N, B200_ERR_UNSUPPORTED, "cgemm_wx: x must be a dense (batch, K, N) tensor");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a.w_planes) & 15) == 0 && a.out_ms % 2 == 0 && a.out_bs % 2 == 0,
+               B200_ERR_ALIGN, "cgemm_wx: operands must be 16-byte aligned");
+  B200_REQUIRE((int64_t)a.batch * a.K < (int64_t(1) << 31), B200_ERR_SHAPE, "cgemm_wx: batch * K too large");
+  GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  B200_REQUIRE(make_map(&maps.w, a.w_planes, (uint64_t)a.K, 4ull * a.M, (uint64_t)a.K * 4, GM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                   make_map(&maps.x, a.x, 2ull * a.N, (uint64_t)a.batch * a.K, 8ull * a.N, GK,
+                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B),
+               B200_ERR_UNSUPPORTED, "cgemm_wx: tensor-map encoding failed");
+  const int smem = NSTAGE * STAGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(cgemm_wx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  const dim3 grid((unsigned)(2 * (int64_t)a.N / GN), (unsigned)(a.M / GM), (unsigned)a.batch);
+  cgemm_wx_kernel<<<grid, NTHREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(maps, a);
+  return launch_status();
+}

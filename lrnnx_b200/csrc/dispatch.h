@@ -24,6 +24,9 @@ bool selscan_bwd_sl_supported(const b200_selscan_bwd_args &a);
 int selscan_fwd_sl(const b200_selscan_fwd_args &a, cudaStream_t st);
 int selscan_bwd_sl(const b200_selscan_bwd_args &a, cudaStream_t st);
 
+// status word of the tensor-core projection kernel (cgemm_tc.cu)
+int cgemm_status_read();
+
 // status word of the decode-step pipeline (ssu.cu): non-zero after an expired bounded wait
 int ssu_status_read();
 

@@ -38,6 +38,9 @@ constexpr int BCROW = 36;         // floats per timestep row of the converted B|
 constexpr int DDROW = 36;         // floats per timestep row of the per-(channel pair) operand tiles
 constexpr int YROW = 33;          // floats per channel row of the per-(channel, t) result tiles
 constexpr int HROW = 272;         // floats per timestep row of the state tile (2 x 32 lanes x 4 + 16 pad)
+constexpr int YSROW = 68;         // floats per timestep row of the forward's partial outputs (8 pairs x 4 shares x 2 + 4 pad)
+constexpr int TB = 4;             // steps per block of the forward recurrence (operands loaded a block ahead)
+constexpr int RB = 2;             // steps per block of the reverse recurrence
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
@@ -129,8 +132,7 @@ template <typename T> struct FwdSmem {
   static constexpr int RAW = RAW_ROWS * ST * (int)sizeof(T);             // one raw stage
   static constexpr int OFF_BC = 2 * RAW;
   static constexpr int OFF_DD = OFF_BC + ST * BCROW * 4;
-  static constexpr int OFF_Y = OFF_DD + ST * DDROW * 4;
-  static constexpr int OFF_PAR = OFF_Y + SCH * YROW * 4;                 // bias[16], D[16]
+  static constexpr int OFF_PAR = OFF_DD + ST * DDROW * 4;                // bias[16], D[16]
   static constexpr int TOTAL = ((OFF_PAR + 2 * SCH * 4 + 127) / 128) * 128;
 };
 
@@ -138,6 +140,9 @@ template <typename T, int NW, bool STG>
 __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_selscan_fwd_args p) {
   using SM = FwdSmem<T>;
   extern __shared__ __align__(128) unsigned char smem_all[];
+  // the per-(channel, t) results live in a statically allocated array: a distinct object, so the
+  // compiler may move the operand loads of later steps across the stores into it
+  __shared__ __align__(16) float ys_all[NW][ST * YSROW];      // [t][channel pair][lane share] {c0, c0 + 1}
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sl = lane & 3, cp = lane >> 2;
   const int tiles_per_b = p.dim / SCH;
@@ -182,7 +187,7 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
 
   float *bc = reinterpret_cast<float *>(smem + SM::OFF_BC);
   float *dd = reinterpret_cast<float *>(smem + SM::OFF_DD);
-  float *ys = reinterpret_cast<float *>(smem + SM::OFF_Y);
+  float *ys = ys_all[warp];
   float *par = reinterpret_cast<float *>(smem + SM::OFF_PAR);
   if (lane < SCH) {
     par[lane] = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d0 + lane] : 0.f;
@@ -239,29 +244,78 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
       }
     }
     __syncwarp();
-    // ---- the recurrence: 32 serial steps, 4 packed chains per lane
-#pragma unroll 4
-    for (int t = 0; t < ST; ++t) {
-      const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
-      const float4 c4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + SN + 4 * sl);
-      const float4 d4 = *reinterpret_cast<const float4 *>(dd + t * DDROW + 4 * cp);
-      const float2 B01 = make_float2(b4.x, b4.y), B23 = make_float2(b4.z, b4.w);
-      const float2 C01 = make_float2(c4.x, c4.y), C23 = make_float2(c4.z, c4.w);
-      const float2 dl0 = splat(d4.x), du0 = splat(d4.y), dl1 = splat(d4.z), du1 = splat(d4.w);
-      h[0][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][0])), h[0][0], __fmul2_rn(du0, B01));
-      h[0][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][1])), h[0][1], __fmul2_rn(du0, B23));
-      h[1][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][0])), h[1][0], __fmul2_rn(du1, B01));
-      h[1][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][1])), h[1][1], __fmul2_rn(du1, B23));
-      const float2 p0 = __ffma2_rn(h[0][1], C23, __fmul2_rn(h[0][0], C01));
-      const float2 p1 = __ffma2_rn(h[1][1], C23, __fmul2_rn(h[1][0], C01));
-      const float s0 = p0.x + p0.y, s1 = p1.x + p1.y;
-      // sum over the 4 lanes of the channel pair: odd lanes end with channel c0 + 1, even with c0
-      const float send = (sl & 1) ? s0 : s1;
-      float keep = ((sl & 1) ? s1 : s0) + __shfl_xor_sync(0xffffffffu, send, 1);
-      keep += __shfl_xor_sync(0xffffffffu, keep, 2);
-      if (sl < 2) ys[(2 * cp + sl) * YROW + t] = keep;
-      cs0 += d4.x;
-      cs1 += d4.z;
+    // ---- the recurrence: 32 serial steps, 4 packed chains per lane.  The operands of a block of
+    // TB steps are loaded one block ahead of their use and the block's results are stored after
+    // it, so that neither the shared-memory latency nor the SFU latency sits on the serial chain.
+    {
+      float4 cb[TB], cc[TB], cd[TB];
+#pragma unroll
+      for (int i = 0; i < TB; ++i) {
+        cb[i] = *reinterpret_cast<const float4 *>(bc + i * BCROW + 4 * sl);
+        cc[i] = *reinterpret_cast<const float4 *>(bc + i * BCROW + SN + 4 * sl);
+        cd[i] = *reinterpret_cast<const float4 *>(dd + i * DDROW + 4 * cp);
+      }
+#pragma unroll 2
+      for (int blk = 0; blk < ST / TB; ++blk) {
+        float4 nb[TB], nc[TB], nd[TB];
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const int tn = min((blk + 1) * TB + i, ST - 1);
+          nb[i] = *reinterpret_cast<const float4 *>(bc + tn * BCROW + 4 * sl);
+          nc[i] = *reinterpret_cast<const float4 *>(bc + tn * BCROW + SN + 4 * sl);
+          nd[i] = *reinterpret_cast<const float4 *>(dd + tn * DDROW + 4 * cp);
+        }
+        // transitions and inputs of the block: independent of the state
+        float2 a[TB][4], bb[TB][4];
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const float2 B01 = make_float2(cb[i].x, cb[i].y), B23 = make_float2(cb[i].z, cb[i].w);
+          const float2 dl0 = splat(cd[i].x), du0 = splat(cd[i].y), dl1 = splat(cd[i].z), du1 = splat(cd[i].w);
+          a[i][0] = ex2f2(__fmul2_rn(dl0, A2[0][0]));
+          a[i][1] = ex2f2(__fmul2_rn(dl0, A2[0][1]));
+          a[i][2] = ex2f2(__fmul2_rn(dl1, A2[1][0]));
+          a[i][3] = ex2f2(__fmul2_rn(dl1, A2[1][1]));
+          bb[i][0] = __fmul2_rn(du0, B01);
+          bb[i][1] = __fmul2_rn(du0, B23);
+          bb[i][2] = __fmul2_rn(du1, B01);
+          bb[i][3] = __fmul2_rn(du1, B23);
+        }
+        // the four chains over the block's steps, then the outputs of all steps at once: grouping
+        // the instructions by kind keeps independent work between dependent ones
+        float2 hh[TB][4];
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          h[0][0] = __ffma2_rn(a[i][0], h[0][0], bb[i][0]);
+          h[0][1] = __ffma2_rn(a[i][1], h[0][1], bb[i][1]);
+          h[1][0] = __ffma2_rn(a[i][2], h[1][0], bb[i][2]);
+          h[1][1] = __ffma2_rn(a[i][3], h[1][1], bb[i][3]);
+          hh[i][0] = h[0][0]; hh[i][1] = h[0][1]; hh[i][2] = h[1][0]; hh[i][3] = h[1][1];
+        }
+        float2 p0[TB], p1[TB];
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const float2 C01 = make_float2(cc[i].x, cc[i].y);
+          p0[i] = __fmul2_rn(hh[i][0], C01);
+          p1[i] = __fmul2_rn(hh[i][2], C01);
+        }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const float2 C23 = make_float2(cc[i].z, cc[i].w);
+          p0[i] = __ffma2_rn(hh[i][1], C23, p0[i]);
+          p1[i] = __ffma2_rn(hh[i][3], C23, p1[i]);
+        }
+        // this lane's share (4 of the 16 states) of the two channels' outputs; the four shares are
+        // added up in the output pass
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          *reinterpret_cast<float2 *>(ys + (blk * TB + i) * YSROW + cp * 8 + 2 * sl) =
+              make_float2(p0[i].x + p0[i].y, p1[i].x + p1[i].y);
+          cs0 += cd[i].x;
+          cs1 += cd[i].z;
+        }
+#pragma unroll
+        for (int i = 0; i < TB; ++i) { cb[i] = nb[i]; cc[i] = nc[i]; cd[i] = nd[i]; }
+      }
     }
     // ---- checkpoints and stage states
     const bool chunk_end = ((t0 + ST) % kChunk) == 0 || s == nst - 1;
@@ -287,7 +341,11 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
       T *ot = raw + SCH * ST, *zt = raw + 2 * SCH * ST;
 #pragma unroll 4
       for (int ch = 0; ch < SCH; ++ch) {
-        const float o = fmaf(par[SCH + ch], to_f(raw[ch * ST + lane]), ys[ch * YROW + lane]);
+        // the four lanes' shares of channel ch at timestep `lane`: {c0, c0+1} pairs of shares 0..3
+        const float4 qa = *reinterpret_cast<const float4 *>(ys + lane * YSROW + (ch >> 1) * 8);
+        const float4 qb = *reinterpret_cast<const float4 *>(ys + lane * YSROW + (ch >> 1) * 8 + 4);
+        const float ysum = (ch & 1) ? (qa.y + qa.w) + (qb.y + qb.w) : (qa.x + qa.z) + (qb.x + qb.z);
+        const float o = fmaf(par[SCH + ch], to_f(raw[ch * ST + lane]), ysum);
         ot[ch * ST + lane] = from_f<T>(o);
         if (has_z) {
           const float zv = to_f(zt[ch * ST + lane]);
@@ -304,15 +362,13 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
 }
 
 // ------------------------------------------------------------------------------------ backward
+constexpr int SUMROW = 132;       // floats per timestep row of the backward's partial sums (8 pairs x 4 shares x 4 + 4 pad)
+
 template <typename T> struct BwdSmem {
   static constexpr int RAW_ROWS = 7 * SCH;                               // u, delta, dout, z, out, B, C
   static constexpr int RAW = RAW_ROWS * ST * (int)sizeof(T);
-  static constexpr int OFF_BC = RAW;
-  static constexpr int OFF_DA = OFF_BC + ST * BCROW * 4;                 // {delta0, du0, delta1, du1} per (t, pair)
-  static constexpr int OFF_DB = OFF_DA + ST * DDROW * 4;                 // {u0, dy0, u1, dy1}
-  static constexpr int OFF_H = OFF_DB + ST * DDROW * 4;                  // states, then dB | dC partials
-  static constexpr int OFF_SUM = OFF_H + ST * HROW * 4;                  // float2 {sum g B, sum w A2} per (channel, t)
-  static constexpr int OFF_OT = OFF_SUM + SCH * YROW * 8;                // du, ddelta tiles
+  static constexpr int OFF_SUM = RAW;                                    // float4 partial sums per (t, channel pair, lane share)
+  static constexpr int OFF_OT = OFF_SUM + ST * SUMROW * 4;               // du, ddelta tiles
   static constexpr int OFF_PAR = OFF_OT + 2 * SCH * ST * (int)sizeof(T);
   static constexpr int TOTAL = ((OFF_PAR + 2 * SCH * 4 + 127) / 128) * 128;
 };
@@ -322,6 +378,13 @@ __global__ void __launch_bounds__(32) selscan_sl_bwd_kernel(const b200_selscan_b
   using SM = BwdSmem<T>;
   const b200_selscan_fwd_args &p = q.f;
   extern __shared__ __align__(128) unsigned char smem[];
+  // The stage's states (later its dB | dC partials) and the converted operand tiles are statically
+  // allocated, each a distinct object: the compiler may then move the operand loads of later
+  // steps across the stores of earlier ones (into hs, and into the dynamically allocated sums).
+  __shared__ __align__(16) float hs[ST * HROW];
+  __shared__ __align__(16) float bc[ST * BCROW];       // B | C of the stage, float32, [t][n]
+  __shared__ __align__(16) float dda[ST * DDROW];      // {delta0, delta0 u0, delta1, delta1 u1} per (t, channel pair)
+  __shared__ __align__(16) float ddb[ST * DDROW];      // {u0, dy0, u1, dy1}
   const int lane = threadIdx.x;
   const int sl = lane & 3, cp = lane >> 2;
   const int tiles_per_b = p.dim / SCH;
@@ -361,11 +424,7 @@ __global__ void __launch_bounds__(32) selscan_sl_bwd_kernel(const b200_selscan_b
   issue(nst - 1);
   cp_commit();
 
-  float *bc = reinterpret_cast<float *>(smem + SM::OFF_BC);
-  float *dda = reinterpret_cast<float *>(smem + SM::OFF_DA);
-  float *ddb = reinterpret_cast<float *>(smem + SM::OFF_DB);
-  float *hs = reinterpret_cast<float *>(smem + SM::OFF_H);
-  float2 *sums = reinterpret_cast<float2 *>(smem + SM::OFF_SUM);
+  float *sums = reinterpret_cast<float *>(smem + SM::OFF_SUM);
   T *ot = reinterpret_cast<T *>(smem + SM::OFF_OT);
   float *par = reinterpret_cast<float *>(smem + SM::OFF_PAR);
   if (lane < SCH) {
@@ -453,67 +512,110 @@ __global__ void __launch_bounds__(32) selscan_sl_bwd_kernel(const b200_selscan_b
 #pragma unroll
           for (int j = 0; j < 2; ++j) h[c][j] = make_float2(0.f, 0.f);
       }
-#pragma unroll 4
-      for (int t = 0; t < ST; ++t) {
-        const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
-        const float4 d4 = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
-        const float2 B01 = make_float2(b4.x, b4.y), B23 = make_float2(b4.z, b4.w);
-        const float2 dl0 = splat(d4.x), du0 = splat(d4.y), dl1 = splat(d4.z), du1 = splat(d4.w);
-        h[0][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][0])), h[0][0], __fmul2_rn(du0, B01));
-        h[0][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl0, A2[0][1])), h[0][1], __fmul2_rn(du0, B23));
-        h[1][0] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][0])), h[1][0], __fmul2_rn(du1, B01));
-        h[1][1] = __ffma2_rn(ex2f2(__fmul2_rn(dl1, A2[1][1])), h[1][1], __fmul2_rn(du1, B23));
-        float *hr = hs + t * HROW + lane * 4;
-        *reinterpret_cast<float4 *>(hr) = make_float4(h[0][0].x, h[0][0].y, h[0][1].x, h[0][1].y);
-        *reinterpret_cast<float4 *>(hr + 128) = make_float4(h[1][0].x, h[1][0].y, h[1][1].x, h[1][1].y);
-      }
-    }
-    // ---- the adjoint, serially in reverse
 #pragma unroll 2
-    for (int t = ST - 1; t >= 0; --t) {
-      const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
-      const float4 c4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + SN + 4 * sl);
-      const float4 da = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
-      const float4 db = *reinterpret_cast<const float4 *>(ddb + t * DDROW + 4 * cp);
-      float *hr = hs + t * HROW + lane * 4;
-      const float4 hv0 = *reinterpret_cast<const float4 *>(hr);
-      const float4 hv1 = *reinterpret_cast<const float4 *>(hr + 128);
-      const float2 Bp[2] = {make_float2(b4.x, b4.y), make_float2(b4.z, b4.w)};
-      const float2 Cp[2] = {make_float2(c4.x, c4.y), make_float2(c4.z, c4.w)};
-      const float2 hh[2][2] = {{make_float2(hv0.x, hv0.y), make_float2(hv0.z, hv0.w)},
-                               {make_float2(hv1.x, hv1.y), make_float2(hv1.z, hv1.w)}};
-      const float dl[2] = {da.x, da.z}, du[2] = {da.y, da.w}, dy[2] = {db.y, db.w};
-      float2 sgB[2], sA[2], dBp[2], dCp[2];
+      for (int blk = 0; blk < ST / TB; ++blk) {
+        float2 a[TB][4], bb[TB][4];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float2 dl2 = splat(dl[c]), ndu2 = splat(-du[c]), du2 = splat(du[c]), dy2 = splat(dy[c]);
+        for (int i = 0; i < TB; ++i) {
+          const int t = blk * TB + i;
+          const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
+          const float4 d4 = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
+          const float2 B01 = make_float2(b4.x, b4.y), B23 = make_float2(b4.z, b4.w);
+          const float2 dl0 = splat(d4.x), du0 = splat(d4.y), dl1 = splat(d4.z), du1 = splat(d4.w);
+          a[i][0] = ex2f2(__fmul2_rn(dl0, A2[0][0]));
+          a[i][1] = ex2f2(__fmul2_rn(dl0, A2[0][1]));
+          a[i][2] = ex2f2(__fmul2_rn(dl1, A2[1][0]));
+          a[i][3] = ex2f2(__fmul2_rn(dl1, A2[1][1]));
+          bb[i][0] = __fmul2_rn(du0, B01);
+          bb[i][1] = __fmul2_rn(du0, B23);
+          bb[i][2] = __fmul2_rn(du1, B01);
+          bb[i][3] = __fmul2_rn(du1, B23);
+        }
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const float2 a = ex2f2(__fmul2_rn(dl2, A2[c][j]));
-          const float2 gt = __ffma2_rn(anext[c][j], gadj[c][j], __fmul2_rn(dy2, Cp[j]));
-          gadj[c][j] = gt;
-          anext[c][j] = a;
-          const float2 ah = __ffma2_rn(ndu2, Bp[j], hh[c][j]);          // h_t - b_t = a_t h_{t-1}
-          const float2 w = __fmul2_rn(gt, ah);
-          if (j == 0) { sgB[c] = __fmul2_rn(gt, Bp[j]); sA[c] = __fmul2_rn(w, A2[c][j]); }
-          else { sgB[c] = __ffma2_rn(gt, Bp[j], sgB[c]); sA[c] = __ffma2_rn(w, A2[c][j], sA[c]); }
-          dAacc[c][j] = __ffma2_rn(w, dl2, dAacc[c][j]);
-          if (c == 0) { dBp[j] = __fmul2_rn(gt, du2); dCp[j] = __fmul2_rn(dy2, hh[c][j]); }
-          else { dBp[j] = __ffma2_rn(gt, du2, dBp[j]); dCp[j] = __ffma2_rn(dy2, hh[c][j], dCp[j]); }
+        for (int i = 0; i < TB; ++i) {
+          h[0][0] = __ffma2_rn(a[i][0], h[0][0], bb[i][0]);
+          h[0][1] = __ffma2_rn(a[i][1], h[0][1], bb[i][1]);
+          h[1][0] = __ffma2_rn(a[i][2], h[1][0], bb[i][2]);
+          h[1][1] = __ffma2_rn(a[i][3], h[1][1], bb[i][3]);
+          float *hr = hs + (blk * TB + i) * HROW + lane * 4;
+          *reinterpret_cast<float4 *>(hr) = make_float4(h[0][0].x, h[0][0].y, h[0][1].x, h[0][1].y);
+          *reinterpret_cast<float4 *>(hr + 128) = make_float4(h[1][0].x, h[1][0].y, h[1][1].x, h[1][1].y);
         }
       }
-      // the states of this step are consumed: their slots take the dB | dC partials of the lane
-      *reinterpret_cast<float4 *>(hr) = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
-      *reinterpret_cast<float4 *>(hr + 128) = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
-      // per-(channel, t) sums over the 16 states: odd lanes end with channel c0 + 1, even with c0
-      const float s1_0 = sgB[0].x + sgB[0].y, s2_0 = sA[0].x + sA[0].y;
-      const float s1_1 = sgB[1].x + sgB[1].y, s2_1 = sA[1].x + sA[1].y;
-      const bool odd = sl & 1;
-      float k1 = (odd ? s1_1 : s1_0) + __shfl_xor_sync(0xffffffffu, odd ? s1_0 : s1_1, 1);
-      float k2 = (odd ? s2_1 : s2_0) + __shfl_xor_sync(0xffffffffu, odd ? s2_0 : s2_1, 1);
-      k1 += __shfl_xor_sync(0xffffffffu, k1, 2);
-      k2 += __shfl_xor_sync(0xffffffffu, k2, 2);
-      if (sl < 2) sums[(2 * cp + sl) * YROW + t] = make_float2(k1, k2);
+    }
+    __syncwarp();
+    // ---- the adjoint, serially in reverse.  The states of a block of RB steps are read one block
+    // ahead: their slots are overwritten in place by the block's dB | dC partials.
+    {
+      float4 ch0[RB], ch1[RB];
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const float *hr = hs + (ST - 1 - i) * HROW + lane * 4;
+        ch0[i] = *reinterpret_cast<const float4 *>(hr);
+        ch1[i] = *reinterpret_cast<const float4 *>(hr + 128);
+      }
+#pragma unroll 2
+      for (int blk = 0; blk < ST / RB; ++blk) {
+        float4 nh0[RB], nh1[RB];
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          const int tn = max(ST - 1 - (blk + 1) * RB - i, 0);
+          const float *hr = hs + tn * HROW + lane * 4;
+          nh0[i] = *reinterpret_cast<const float4 *>(hr);
+          nh1[i] = *reinterpret_cast<const float4 *>(hr + 128);
+        }
+        float4 oB[RB], oC[RB];
+        float4 osum[RB];
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          const int t = ST - 1 - blk * RB - i;
+          const float4 b4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + 4 * sl);
+          const float4 c4 = *reinterpret_cast<const float4 *>(bc + t * BCROW + SN + 4 * sl);
+          const float4 da = *reinterpret_cast<const float4 *>(dda + t * DDROW + 4 * cp);
+          const float4 db = *reinterpret_cast<const float4 *>(ddb + t * DDROW + 4 * cp);
+          const float4 hv0 = ch0[i], hv1 = ch1[i];
+          const float2 Bp[2] = {make_float2(b4.x, b4.y), make_float2(b4.z, b4.w)};
+          const float2 Cp[2] = {make_float2(c4.x, c4.y), make_float2(c4.z, c4.w)};
+          const float2 hh[2][2] = {{make_float2(hv0.x, hv0.y), make_float2(hv0.z, hv0.w)},
+                                   {make_float2(hv1.x, hv1.y), make_float2(hv1.z, hv1.w)}};
+          const float dl[2] = {da.x, da.z}, du[2] = {da.y, da.w}, dy[2] = {db.y, db.w};
+          float2 sgB[2], sA[2], dBp[2], dCp[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float2 dl2 = splat(dl[c]), ndu2 = splat(-du[c]), du2 = splat(du[c]), dy2 = splat(dy[c]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float2 a = ex2f2(__fmul2_rn(dl2, A2[c][j]));
+              const float2 gt = __ffma2_rn(anext[c][j], gadj[c][j], __fmul2_rn(dy2, Cp[j]));
+              gadj[c][j] = gt;
+              anext[c][j] = a;
+              const float2 ah = __ffma2_rn(ndu2, Bp[j], hh[c][j]);          // h_t - b_t = a_t h_{t-1}
+              const float2 w = __fmul2_rn(gt, ah);
+              if (j == 0) { sgB[c] = __fmul2_rn(gt, Bp[j]); sA[c] = __fmul2_rn(w, A2[c][j]); }
+              else { sgB[c] = __ffma2_rn(gt, Bp[j], sgB[c]); sA[c] = __ffma2_rn(w, A2[c][j], sA[c]); }
+              dAacc[c][j] = __ffma2_rn(w, dl2, dAacc[c][j]);
+              if (c == 0) { dBp[j] = __fmul2_rn(gt, du2); dCp[j] = __fmul2_rn(dy2, hh[c][j]); }
+              else { dBp[j] = __ffma2_rn(gt, du2, dBp[j]); dCp[j] = __ffma2_rn(dy2, hh[c][j], dCp[j]); }
+            }
+          }
+          oB[i] = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
+          oC[i] = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
+          // this lane's share (4 of the 16 states) of the per-(channel, t) sums; the four shares are
+          // added up in the du / ddelta pass
+          osum[i] = make_float4(sgB[0].x + sgB[0].y, sA[0].x + sA[0].y, sgB[1].x + sgB[1].y, sA[1].x + sA[1].y);
+        }
+        // the states of these steps are consumed: their slots take the dB | dC partials of the lane
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          const int t = ST - 1 - blk * RB - i;
+          float *hr = hs + t * HROW + lane * 4;
+          *reinterpret_cast<float4 *>(hr) = oB[i];
+          *reinterpret_cast<float4 *>(hr + 128) = oC[i];
+          *reinterpret_cast<float4 *>(sums + t * SUMROW + lane * 4) = osum[i];
+        }
+#pragma unroll
+        for (int i = 0; i < RB; ++i) { ch0[i] = nh0[i]; ch1[i] = nh1[i]; }
+      }
     }
     __syncwarp();
     // ---- dB / dC: sum the 8 channel pairs of the tile, one reduction per (n, t) to global memory
@@ -544,7 +646,10 @@ __global__ void __launch_bounds__(32) selscan_sl_bwd_kernel(const b200_selscan_b
     {
 #pragma unroll 4
       for (int ch = 0; ch < SCH; ++ch) {
-        const float2 sm2 = sums[ch * YROW + lane];
+        const float *sp = sums + lane * SUMROW + (ch >> 1) * 16 + (ch & 1) * 2;      // shares 0..3 of {sum g B, sum w A2}
+        const float2 q0 = *reinterpret_cast<const float2 *>(sp), q1 = *reinterpret_cast<const float2 *>(sp + 4);
+        const float2 q2 = *reinterpret_cast<const float2 *>(sp + 8), q3 = *reinterpret_cast<const float2 *>(sp + 12);
+        const float2 sm2 = make_float2((q0.x + q1.x) + (q2.x + q3.x), (q0.y + q1.y) + (q2.y + q3.y));
         const float2 a2 = *reinterpret_cast<const float2 *>(dda + lane * DDROW + 2 * ch);   // {delta, delta u}
         const float2 b2 = *reinterpret_cast<const float2 *>(ddb + lane * DDROW + 2 * ch);   // {u, dy}
         const float duv = fmaf(a2.x, sm2.x, par[SCH + ch] * b2.y);

@@ -1376,7 +1376,9 @@ int b200_device_status(void) {
   if (cudaMemcpyFromSymbol(&v, g_simpscan_status, sizeof(int)) != cudaSuccess) return -1;
   const int w = ssu_status_read();
   if (w < 0) return -1;
-  return v ? v : w;
+  const int g = cgemm_status_read();
+  if (g < 0) return -1;
+  return v ? v : (w ? w : g);
 }
 
 }  // extern "C"

@@ -100,11 +100,8 @@ class Mamba(nn.Module):
         x = causal_conv1d_update(x, cache["conv_state"], self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
         x_db = F.linear(x, self.x_proj.weight)
         dt = F.linear(x_db[:, :R], self.dt_proj.weight)
-        A = cache.get("A")
-        if A is None:
-            A = -torch.exp(self.A_log.float())
-        y = selective_state_update(cache["lrnn_state"], x, dt, A, x_db[:, R:R + N], x_db[:, R + N:], self.D.float(),
-                                   z=z, dt_bias=self.dt_proj.bias.float(), dt_softplus=True)
+        y = selective_state_update(cache["lrnn_state"], x, dt, cache["A"], x_db[:, R:R + N], x_db[:, R + N:], cache["D"],
+                                   z=z, dt_bias=cache["dt_bias"], dt_softplus=True)
         return F.linear(y, self.out_proj.weight)
 
     def allocate_inference_cache(self, batch_size, dtype=None, state_dtype=None):
@@ -112,7 +109,9 @@ class Mamba(nn.Module):
         dtype = dtype or self.conv1d.weight.dtype
         return {"conv_state": torch.zeros(batch_size, self.d_inner, self.d_conv, device=dev, dtype=dtype),
                 "lrnn_state": torch.zeros(batch_size, self.d_inner, self.d_state, device=dev, dtype=state_dtype or dtype),
-                "A": (-torch.exp(self.A_log.float())).contiguous()}
+                # float32 copies of the per-channel parameters, made once instead of once per token
+                "A": (-torch.exp(self.A_log.float())).contiguous(), "D": self.D.float().contiguous(),
+                "dt_bias": self.dt_proj.bias.float().contiguous()}
 
 
 class Block(nn.Module):

@@ -1,8 +1,10 @@
 """``simplified_scan_fn`` and ``s5_inner_fn`` on the sm_100a kernels.
 
 Mirror SimplifiedScanFn / simplified_scan_fn (lrnnx/ops/simplified_scan.py:14-230) and
-S5InnerFn / s5_inner_fn (:343-583): the projections Bu = B u and y = C x are complex
-einsums (cuBLAS) around the diagonal scan kernel, which is called with identity B / C.
+S5InnerFn / s5_inner_fn (:343-583): the projections Bu = B u and y = C x (and their data
+gradients) run on the tensor-core kernel of ``projection`` where its tiling applies, as complex
+einsums (cuBLAS) otherwise, around the diagonal scan kernel, which is called with identity B / C.
+The two weight gradients (sums over batch and time) are einsums.
 
 One deliberate deviation: with ``return_last_state=True`` the reference's CUDA wrapper
 slices its output tensor instead of the state (simplified_scan.py:106-110) and returns a
@@ -14,8 +16,17 @@ from __future__ import annotations
 import torch
 
 from .. import simplified_scan_cuda
+from . import projection
 
 _VALID = ("bilinear", "zoh", "dirac")
+
+
+def _proj(W, x, conj_transpose=False):
+    """W x (or W^H x) per batch: the tensor-core kernel where its tiling applies, einsum otherwise."""
+    Wm = W.conj().transpose(0, 1) if conj_transpose else W
+    if projection.supported(Wm, x if x.is_contiguous() else x.contiguous()):
+        return projection.project(W, x, conj_transpose)
+    return torch.einsum("mk,bkn->bmn", Wm, x)
 
 
 def _kernel_A(A):
@@ -34,10 +45,10 @@ class SimplifiedScanFn(torch.autograd.Function):
         P = A.shape[0]
         A_k = _kernel_A(A).contiguous()
         dstate = A_k.shape[1]
-        Bu = torch.einsum("ph,bhl->bpl", B, u)
+        Bu = _proj(B, u)
         ident = torch.ones(P, dstate, dtype=A.dtype, device=A.device)
         out, xs = simplified_scan_cuda.fwd(Bu, delta, A_k, ident, ident, deltaA, discretization)
-        y = torch.einsum("hp,bpl->bhl", C, out)
+        y = _proj(C, out)
         ctx.discretization = discretization
         ctx.has_deltaA = deltaA is not None
         ctx.A_was_1d = A.dim() == 1
@@ -50,7 +61,7 @@ class SimplifiedScanFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, *args):
         u, delta, A_k, B, C, Bu, out, xs, ident, deltaA = ctx.saved_tensors
-        dx_out = torch.einsum("hp,bhl->bpl", C.conj(), dout)
+        dx_out = _proj(C, dout, conj_transpose=True)
         dC = torch.einsum("bhl,bpl->hp", dout, out.conj())
         if dx_out.stride(-1) != 1:
             dx_out = dx_out.contiguous()
@@ -58,7 +69,7 @@ class SimplifiedScanFn(torch.autograd.Function):
                                       need_dB_dC=False, out_=out if out.stride(-1) == 1 else None)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
-        du = torch.einsum("ph,bpl->bhl", B.conj(), dBu)
+        du = _proj(B, dBu, conj_transpose=True)
         dB = torch.einsum("bpl,bhl->ph", dBu, u.conj())
         if ctx.A_was_1d:
             dA = dA.squeeze(-1)
@@ -85,10 +96,10 @@ class S5InnerFn(torch.autograd.Function):
         P = A.shape[0]
         A_k = _kernel_A(A).contiguous()
         dstate = A_k.shape[1]
-        Bu = torch.einsum("ph,bhl->bpl", B, u)
+        Bu = _proj(B, u)
         ident = torch.ones(P, dstate, dtype=A.dtype, device=A.device)
         scan_out, xs = simplified_scan_cuda.fwd(Bu, delta, A_k, ident, ident, deltaA, discretization)
-        y_complex = torch.einsum("hp,bpl->bhl", C, scan_out)
+        y_complex = _proj(C, scan_out)
         y_real = 2 * y_complex.real if conj_sym else y_complex.real
         u_real = u.real if u.is_complex() else u
         y = y_real + D.unsqueeze(0).unsqueeze(-1) * u_real
@@ -106,7 +117,7 @@ class S5InnerFn(torch.autograd.Function):
         du_skip = D.unsqueeze(0).unsqueeze(-1) * dout
         scale = 2.0 if ctx.conj_sym else 1.0
         dy_complex = torch.complex(scale * dout, torch.zeros_like(dout))
-        dscan = torch.einsum("hp,bhl->bpl", C.conj(), dy_complex)
+        dscan = _proj(C, dy_complex, conj_transpose=True)
         dC = torch.einsum("bhl,bpl->hp", dy_complex, scan_out.conj())
         if dscan.stride(-1) != 1:
             dscan = dscan.contiguous()
@@ -114,7 +125,7 @@ class S5InnerFn(torch.autograd.Function):
                                       need_dB_dC=False, out_=scan_out if scan_out.stride(-1) == 1 else None)
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
-        du_scan = torch.einsum("ph,bpl->bhl", B.conj(), dBu)
+        du_scan = _proj(B, dBu, conj_transpose=True)
         dB = torch.einsum("bpl,bhl->ph", dBu, u.conj())
         if u.is_complex():
             du = du_scan + torch.complex(du_skip, torch.zeros_like(du_skip))

@@ -1,0 +1,258 @@
+"""GPU parity of the Mamba block kernels (causal convolution, its one-token update, residual add
++ RMSNorm), of mamba_inner_fn, and of the LM harness built from them (BASELINE configs 2 and 4).
+
+Reference side: tests/golden/mamba_lm.pt, recorded from lrnnx's own LRNNLMHeadModel on CPU
+(weights, logits, parameter gradients of the shifted cross-entropy, step() logits), and the
+oracle's restatements of the reference's convolution / norm / layer code on seeded CPU inputs.
+Tolerance: fp32 rtol 1e-4 on activations and logits, 1e-3 on parameter gradients (sums over
+batch x L), floors of 2e-5 / 2e-4 of the tensor's largest magnitude; bf16 3e-2.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import assert_close, load_golden
+from oracle import scan_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+LM = load_golden("mamba_lm")
+
+
+# ----------------------------------------------------------------------------- causal convolution
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("L", [8, 50, 1032, 2056])
+@pytest.mark.parametrize("bias,act", [(True, "silu"), (False, None), (True, None)])
+def test_causal_conv1d_fp32(width, L, bias, act):
+    from lrnnx_b200.ops.mamba_block import causal_conv1d_fn
+    g = torch.Generator().manual_seed(L + width)
+    batch, dim = 2, 24
+    x = torch.randn(batch, dim, L, generator=g)
+    w = torch.randn(dim, width, generator=g) * 0.5
+    b = torch.randn(dim, generator=g) if bias else None
+    gout = torch.randn(batch, dim, L, generator=g)
+    cl = [t.clone().requires_grad_(True) for t in (x, w)] + ([b.clone().requires_grad_(True)] if bias else [])
+    y_c = O.causal_conv1d_oracle(cl[0], cl[1], cl[2] if bias else None, act)
+    g_c = torch.autograd.grad(y_c, cl, gout)
+    gl = [t.cuda().requires_grad_(True) for t in (x, w)] + ([b.cuda().requires_grad_(True)] if bias else [])
+    y_g = causal_conv1d_fn(gl[0], gl[1], gl[2] if bias else None, act)
+    assert y_g.shape == y_c.shape and y_g.dtype == y_c.dtype
+    assert_close(y_g.detach().cpu(), y_c.detach(), rtol=1e-4, atol_scale=2e-5, name="out")
+    g_g = torch.autograd.grad(y_g, gl, gout.cuda())
+    for name, a, c in zip(("dx", "dweight", "dbias"), g_g, g_c):
+        assert_close(a.cpu(), c, rtol=3e-4, atol_scale=1e-4, name=name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_causal_conv1d_half_and_strided(dtype):
+    """16-bit activations; x is the first half of a (batch, 2 dim, L) tensor (the xz layout)."""
+    from lrnnx_b200.ops.mamba_block import causal_conv1d_fn
+    g = torch.Generator().manual_seed(3)
+    batch, dim, L, width = 3, 64, 520, 4
+    xz = torch.randn(batch, 2 * dim, L, generator=g).to(dtype)
+    w = (torch.randn(dim, width, generator=g) * 0.5).to(dtype)
+    b = torch.randn(dim, generator=g).to(dtype)
+    y_c = O.causal_conv1d_oracle(xz[:, :dim].float(), w.float(), b.float(), "silu")
+    y_g = causal_conv1d_fn(xz.cuda()[:, :dim], w.cuda(), b.cuda(), "silu")
+    assert_close(y_g.float().cpu(), y_c, rtol=3e-2, atol_scale=1e-2, name="out")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 4])
+def test_causal_conv1d_update_matches_oracle_and_the_sequence_kernel(dtype, width):
+    from lrnnx_b200.ops.mamba_block import causal_conv1d_fn, causal_conv1d_update
+    g = torch.Generator().manual_seed(9)
+    batch, dim, steps = 4, 96, 7
+    w = (torch.randn(dim, width, generator=g) * 0.5).to(dtype)
+    b = torch.randn(dim, generator=g).to(dtype)
+    xs = torch.randn(batch, dim, steps, generator=g).to(dtype)
+    st_c = torch.zeros(batch, dim, width, dtype=dtype)
+    st_g = st_c.cuda()
+    tol = dict(rtol=1e-4, atol_scale=2e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol_scale=1e-2)
+    outs = []
+    for t in range(steps):
+        st_f = st_c.float()
+        o_c = O.causal_conv1d_update_oracle(xs[:, :, t].float(), st_f, w.float(), b.float(), "silu")
+        st_c = st_f.to(dtype)
+        o_g = causal_conv1d_update(xs[:, :, t].cuda(), st_g, w.cuda(), b.cuda(), "silu")
+        assert_close(o_g.float().cpu(), o_c, name=f"out step {t}", **tol)
+        assert_close(st_g.float().cpu(), st_c.float(), name=f"state step {t}", **tol)
+        outs.append(o_g)
+    seq = causal_conv1d_fn(xs.cuda(), w.cuda(), b.cuda(), "silu")
+    assert_close(torch.stack(outs, dim=-1).float().cpu(), seq.float().cpu(), name="steps vs sequence", **tol)
+
+
+# ----------------------------------------------------------------------------- add + RMSNorm
+@pytest.mark.parametrize("cols", [64, 768, 2048, 4096])
+@pytest.mark.parametrize("with_res,prenorm", [(False, False), (True, True), (False, True), (True, False)])
+def test_rms_norm_fp32(cols, with_res, prenorm):
+    from lrnnx_b200.ops.mamba_block import rms_norm_fn
+    g = torch.Generator().manual_seed(cols)
+    x = torch.randn(3, 37, cols, generator=g)
+    w = 1.0 + 0.2 * torch.randn(cols, generator=g)
+    res = torch.randn(3, 37, cols, generator=g) if with_res else None
+    leaves_c = [t.clone().requires_grad_(True) for t in (x, w)] + ([res.clone().requires_grad_(True)] if with_res else [])
+    out_c = O.rms_norm_oracle(leaves_c[0], leaves_c[1], leaves_c[2] if with_res else None, 1e-5, prenorm)
+    leaves_g = [t.cuda().requires_grad_(True) for t in (x, w)] + ([res.cuda().requires_grad_(True)] if with_res else [])
+    out_g = rms_norm_fn(leaves_g[0], leaves_g[1], None, residual=leaves_g[2] if with_res else None, eps=1e-5,
+                        prenorm=prenorm)
+    outs_c = out_c if prenorm else (out_c,)
+    outs_g = out_g if prenorm else (out_g,)
+    gouts = [torch.randn(o.shape, generator=g) for o in outs_c]
+    for a, c in zip(outs_g, outs_c):
+        assert_close(a.detach().cpu(), c.detach(), rtol=1e-4, atol_scale=2e-5, name="output")
+    g_c = torch.autograd.grad(outs_c, leaves_c, gouts)
+    g_g = torch.autograd.grad(outs_g, leaves_g, [t.cuda() for t in gouts])
+    for name, a, c in zip(("dx", "dweight", "dresidual"), g_g, g_c):
+        assert_close(a.cpu(), c, rtol=3e-4, atol_scale=1e-4, name=name)
+
+
+def test_rms_norm_bf16_with_fp32_residual():
+    from lrnnx_b200.ops.mamba_block import rms_norm_fn
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(5, 16, 768, generator=g).bfloat16()
+    w = (1.0 + 0.2 * torch.randn(768, generator=g)).bfloat16()
+    res = torch.randn(5, 16, 768, generator=g)
+    y_g, z_g = rms_norm_fn(x.cuda(), w.cuda(), None, residual=res.cuda(), eps=1e-5, prenorm=True, residual_in_fp32=True)
+    assert z_g.dtype == torch.float32 and y_g.dtype == torch.bfloat16
+    z_c = x.float() + res
+    y_c = O.rms_norm_oracle(z_c, w.float(), None, 1e-5)
+    assert_close(z_g.cpu(), z_c, rtol=1e-6, atol_scale=1e-7, name="residual_out")
+    assert_close(y_g.float().cpu(), y_c, rtol=3e-2, atol_scale=1e-2, name="y")
+
+
+# ----------------------------------------------------------------------------- the LM harness
+def _model(case, dtype=torch.float32):
+    from lrnnx_b200.lm import MambaLMHeadModel
+    cfg = case["config"]
+    m = MambaLMHeadModel(cfg["d_model"], cfg["n_layer"], cfg["vocab_size"], d_state=cfg["d_state"], d_conv=cfg["d_conv"],
+                         expand=cfg["expand"], eps=cfg["eps"])
+    m.load_state_dict(case["state_dict"])
+    return m.cuda().to(dtype)
+
+
+@pytest.mark.parametrize("name", sorted(LM))
+def test_lm_forward_backward_matches_reference_model(name):
+    """The harness with the reference model's weights against the reference's logits and parameter
+    gradients (mamba_inner_fn: convolution, projections, scan in one autograd node)."""
+    case = LM[name]
+    m = _model(case)
+    ids = case["input_ids"].cuda()
+    logits = m(ids)
+    assert_close(logits.detach().cpu(), case["logits"], rtol=1e-4, atol_scale=2e-5, name="logits")
+    V = case["config"]["vocab_size"]
+    loss = F.cross_entropy(logits[:, :-1].reshape(-1, V), ids[:, 1:].reshape(-1))
+    assert_close(loss.detach().cpu(), case["loss"], rtol=1e-5, atol_scale=1e-6, name="loss")
+    loss.backward()
+    for k, p in m.named_parameters():
+        want = case["grads"].get(k)
+        if want is None:
+            continue
+        assert p.grad is not None, k
+        assert_close(p.grad.cpu(), want, rtol=1e-3, atol_scale=2e-4, name=f"grad {k}")
+
+
+@pytest.mark.parametrize("name", sorted(LM))
+def test_lm_step_and_prefill_match_reference_model(name):
+    """step() from zero states reproduces the reference's step() logits; prefill of the first half
+    through the scan kernels followed by steps reproduces forward()'s logits (step == parallel)."""
+    case = LM[name]
+    m = _model(case)
+    ids = case["input_ids"].cuda()
+    batch, L = ids.shape
+    with torch.no_grad():
+        caches = m.allocate_inference_cache(batch)
+        for t in range(L):
+            lg = m.step(ids[:, t], caches)
+            assert_close(lg.cpu(), case["step_logits"][:, t], rtol=3e-4, atol_scale=5e-5, name=f"step {t}")
+        cut = L // 2
+        caches = m.allocate_inference_cache(batch)
+        lg = m(ids[:, :cut], caches, num_last_tokens=1)[:, 0]
+        assert_close(lg.cpu(), case["logits"][:, cut - 1], rtol=3e-4, atol_scale=5e-5, name="prefill")
+        for t in range(cut, L):
+            lg = m.step(ids[:, t], caches)
+            assert_close(lg.cpu(), case["logits"][:, t], rtol=3e-4, atol_scale=5e-5, name=f"continue {t}")
+
+
+def test_lm_generate_cuda_graph_equals_python_loop():
+    """Greedy generation replayed from the captured CUDA graph against the plain Python loop
+    (the check of tests/utils/test_generation.py:167-218 in lrnnx, at the LM level)."""
+    case = LM["small"]
+    m = _model(case)
+    prompt = case["input_ids"][:, :16].cuda()
+    a = m.generate(prompt, 24, use_cuda_graph=True)
+    b = m.generate(prompt, 24, use_cuda_graph=False)
+    assert torch.equal(a, b)
+    # and against the oracle's step-by-step decoding on the CPU
+    sd = dict(case["state_dict"])
+    sd["lm_head.weight"] = sd["backbone.embedding.weight"]
+    cfg = case["config"]
+    lg, states = O.mamba_lm_prefill_oracle(sd, case["input_ids"][:, :16], cfg["n_layer"], cfg["eps"])
+    toks = [lg.argmax(-1)]
+    for _ in range(23):
+        toks.append(O.mamba_lm_step_oracle(sd, toks[-1], states, cfg["n_layer"], cfg["eps"]).argmax(-1))
+    ref = torch.stack(toks, dim=1)
+    agree = (a.cpu() == ref).float().mean().item()
+    assert agree >= 0.9, f"greedy tokens agree with the oracle on {agree:.2f} of the positions"
+
+
+def test_lm_bf16_forward_close_to_fp32():
+    case = LM["wide"]
+    m32, m16 = _model(case), _model(case, torch.bfloat16)
+    ids = case["input_ids"].cuda()
+    with torch.no_grad():
+        a, b = m32(ids), m16(ids)
+    assert b.dtype == torch.bfloat16
+    assert_close(b.float().cpu(), a.cpu(), rtol=5e-2, atol_scale=3e-2, name="bf16 logits")
+
+
+# ----------------------------------------------------------------------------- reference layers on the drop-in modules
+REF = os.environ.get("LRNNX_REF")
+
+
+@pytest.mark.skipif(not REF or not os.path.isdir(REF), reason="the lrnnx source tree is not on this machine (set LRNNX_REF)")
+def test_reference_layers_run_on_the_drop_in_modules():
+    """With lrnnx importable: ``lrnnx_b200.install()`` puts the drop-in extension modules where
+    lrnnx imports its compiled ones, ``selective_state_update`` is rebound in the layer module, and
+    lrnnx's own Mamba.forward / backward / step and capture_graph / generate run on these kernels,
+    compared with the same module on lrnnx's pure-PyTorch reference functions."""
+    import lrnnx_b200
+    from lrnnx_b200.ops import selective_state_update
+    lrnnx_b200.install()
+    sys.path.insert(0, REF)
+    import lrnnx.models.ltv.mamba as M
+    from lrnnx.ops.selective_scan import selective_scan_fn, selective_scan_ref
+    from lrnnx.utils.generation import capture_graph, generate
+    torch.manual_seed(0)
+    layer = M.Mamba(d_model=64, d_state=16, use_fast_path=False).cuda()
+    x = torch.randn(2, 96, 64, device="cuda", requires_grad=True)
+    M.selective_scan_fn = selective_scan_fn
+    M.selective_state_update = selective_state_update
+    y = layer(x)
+    gy = torch.randn_like(y)
+    g_kernel = torch.autograd.grad(y, [x] + list(layer.parameters()), gy, allow_unused=True)
+    M.selective_scan_fn = selective_scan_ref
+    y_ref = layer(x)
+    g_ref = torch.autograd.grad(y_ref, [x] + list(layer.parameters()), gy, allow_unused=True)
+    assert_close(y.detach().cpu(), y_ref.detach().cpu(), rtol=1e-4, atol_scale=2e-5, name="Mamba.forward")
+    for a, b in zip(g_kernel, g_ref):
+        if b is not None:
+            assert_close(a.cpu(), b.cpu(), rtol=1e-3, atol_scale=2e-4, name="Mamba gradient")
+    M.selective_scan_fn = selective_scan_fn
+    with torch.no_grad():
+        cache = layer.allocate_inference_cache(2, 96)
+        ys = []
+        for t in range(96):
+            o, cache = layer.step(x[:, t:t + 1], cache)
+            ys.append(o)
+        assert_close(torch.cat(ys, 1).cpu(), y.detach().cpu(), rtol=3e-4, atol_scale=5e-5, name="Mamba.step vs forward")
+        x0 = torch.randn(4, 64, device="cuda")
+        graph_cache = capture_graph(layer, batch_size=4, H=64)
+        a = generate(layer, x0, 32, graph_cache=graph_cache)
+        b = generate(layer, x0, 32)
+        assert_close(a.cpu(), b.cpu(), rtol=6e-4, atol_scale=2e-3, name="capture_graph / generate vs loop")
