@@ -405,6 +405,19 @@ typedef struct b200_cgemm_args {
 
 int b200_cgemm_wx(const b200_cgemm_args *args, void *stream);
 
+/* Weight gradient of a projection on the tensor cores (same 3xTF32 arithmetic):
+ *     out (M x N) += sum over b, l of g[b, m, l] * conj(u[b, n, l])
+ * g (batch, M, L), u (batch, N, L), out (M, N): complex64, dense, L contiguous.  out must be
+ * zero-filled by the caller (the contraction is cut over several thread blocks which add their
+ * partial results with float32 reductions).  M and N multiples of 128, L of 16. */
+typedef struct b200_cgemm_grad_args {
+  int32_t batch, M, N, L;
+  const void *g, *u;
+  void *out;
+} b200_cgemm_grad_args;
+
+int b200_cgemm_grad(const b200_cgemm_grad_args *args, void *stream);
+
 /* Builds the w_planes operand of b200_cgemm_wx from a complex64 matrix W (M, K) given by element
  * strides (so a transposed view is free), optionally conjugated (conj != 0): planes is float32
  * (4, M, K), written densely. */

@@ -306,6 +306,168 @@ cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) 
   if (tid == 0 && fail_s) atomicExch(&g_cgemm_status, 5);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Weight gradients of the projections:  dW (M x N) = sum over batch and time of G[b] U[b]^H,
+// G (batch, M, L), U (batch, N, L) complex64 with L contiguous: dB~ = sum dBu u^H, dC~ = sum dy x^H
+// (lrnnx/ops/simplified_scan.py:139,168,495,520).  Both operands are K-major here (the contraction
+// runs along their contiguous dimension), and with g', u' the float views interleaved along L
+//     Re dW = g' . u',     Im dW = g' . w',   w'[2l] = -u'[2l+1],  w'[2l+1] = u'[2l]
+// so the imaginary part needs a pair-swapped, sign-flipped copy of the U tile.  The swap stays
+// inside 16-byte chunks, so like the TF32 low parts it is produced in shared memory at the tile's
+// own (swizzled) offsets.  Six tiles per stage: G, U from the TMA; G_lo, U_lo, W, W_lo from the
+// transforming warps.  The long contraction (batch x 2L floats) is cut over grid.z into pieces of 16
+// stages; every CTA adds its 128 x 128 partial result to the zero-filled output with float32
+// vector reductions.
+constexpr uint32_t kIdescKK = kIdesc & ~(1u << 16);      // both operands K-major
+
+struct GradMaps {
+  CUtensorMap g;      // (2 L, batch M) float32, box (32, 128)
+  CUtensorMap u;      // (2 L, batch N) float32, box (32, 128)
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+cgemm_ggh_kernel(const __grid_constant__ GradMaps maps, const b200_cgemm_grad_args p, int stages_per_cta) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full[NSTAGE], empty[NSTAGE], lo_ready[NSTAGE], acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int fail_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * GN, m0 = blockIdx.y * GM;
+  const int per_batch = 2 * p.L / GK;                      // stages per batch entry
+  const int total = p.batch * per_batch;
+  const int s_begin = blockIdx.z * stages_per_cta;
+  const int nk = min(stages_per_cta, total - s_begin);
+  // tile slots of a stage: 0 G, 1 G_lo, 2 U, 3 U_lo, 4 W, 5 W_lo
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&lo_ready[s], 4);
+    }
+    mbar_init(&acc_done, 1);
+    fail_s = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (nk > 0) {
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int ks = 0; ks < nk; ++ks) {
+          const int s = ks % NSTAGE;
+          if (ks >= NSTAGE && !mbar_wait(&empty[s], ((ks / NSTAGE) - 1) & 1, WAIT_LIMIT)) { atomicExch(&fail_s, 1); break; }
+          unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], 2 * TILE);
+          const int sg = s_begin + ks;
+          const int b = sg / per_batch, l0 = (sg % per_batch) * GK;
+          tma_2d(st + 0 * TILE, &maps.g, l0, b * p.M + m0, &full[s]);
+          tma_2d(st + 2 * TILE, &maps.u, l0, b * p.N + n0, &full[s]);
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        const uint32_t dre = tmem_base, dim_ = tmem_base + GN;
+        bool ok = true;
+        for (int ks = 0; ks < nk && ok; ++ks) {
+          const int s = ks % NSTAGE;
+          const uint32_t ph = (ks / NSTAGE) & 1;
+          if (!mbar_wait(&full[s], ph, WAIT_LIMIT)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < GK / 8; ++kk)
+            mma_tf32(dre, a_desc(st + 0 * TILE + kk * 32), a_desc(st + 2 * TILE + kk * 32), (ks > 0 || kk > 0) ? 1u : 0u, kIdescKK);
+          if (!mbar_wait(&lo_ready[s], ph, WAIT_LIMIT)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < GK / 8; ++kk) {
+            const uint64_t g = a_desc(st + 0 * TILE + kk * 32), gl = a_desc(st + 1 * TILE + kk * 32);
+            const uint64_t u = a_desc(st + 2 * TILE + kk * 32), ul = a_desc(st + 3 * TILE + kk * 32);
+            const uint64_t w = a_desc(st + 4 * TILE + kk * 32), wl = a_desc(st + 5 * TILE + kk * 32);
+            mma_tf32(dre, gl, u, 1u, kIdescKK);
+            mma_tf32(dre, g, ul, 1u, kIdescKK);
+            mma_tf32(dim_, g, w, (ks > 0 || kk > 0) ? 1u : 0u, kIdescKK);
+            mma_tf32(dim_, gl, w, 1u, kIdescKK);
+            mma_tf32(dim_, g, wl, 1u, kIdescKK);
+          }
+          mma_commit(&empty[s]);
+        }
+        if (!ok) atomicExch(&fail_s, 1);
+        mma_commit(&acc_done);
+      }
+    } else {
+      const int et = tid - 64;
+      bool ok = true;
+      for (int ks = 0; ks < nk && ok; ++ks) {
+        const int s = ks % NSTAGE;
+        if (!mbar_wait(&full[s], (ks / NSTAGE) & 1, WAIT_LIMIT)) { ok = false; break; }
+        float4 *t = reinterpret_cast<float4 *>(smem + (size_t)s * STAGE_BYTES);
+        constexpr int T4 = TILE / 16;           // float4 per tile
+#pragma unroll
+        for (int i = 0; i < T4 / 128; ++i) {
+          const int o = i * 128 + et;
+          const float4 g = t[o], u = t[2 * T4 + o];
+          t[T4 + o] = make_float4(tf32_low(g.x), tf32_low(g.y), tf32_low(g.z), tf32_low(g.w));
+          const float4 ul = make_float4(tf32_low(u.x), tf32_low(u.y), tf32_low(u.z), tf32_low(u.w));
+          t[3 * T4 + o] = ul;
+          t[4 * T4 + o] = make_float4(-u.y, u.x, -u.w, u.z);
+          t[5 * T4 + o] = make_float4(-ul.y, ul.x, -ul.w, ul.z);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&lo_ready[s]);
+      }
+      if (!ok) atomicExch(&fail_s, 1);
+      if (ok && mbar_wait(&acc_done, 0, WAIT_LIMIT) && fail_s == 0) {
+        tc_fence_after();
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        // A thread holds one output row (its TMEM lane), 32 columns at a time.  The chunk is turned
+        // through shared memory (the stage buffers are free now) so that a warp adds 32 consecutive
+        // complex elements of one row per instruction: coalesced {re, im} vector reductions.
+        float2 *turn = reinterpret_cast<float2 *>(smem) + (size_t)q * 32 * 33;
+        (void)row;
+#pragma unroll 1
+        for (int c = 0; c < GN / 32; ++c) {
+          float vr[32], vi[32];
+          const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + c * 32;
+          tmem_ld32(ta, vr);
+          tmem_ld32(ta + GN, vi);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) turn[lane * 33 + j] = make_float2(vr[j], vi[j]);
+          __syncwarp();
+          float *obase = reinterpret_cast<float *>(p.out) + ((int64_t)(m0 + q * 32) * p.N + n0 + c * 32 + lane) * 2;
+#pragma unroll 8
+          for (int r = 0; r < 32; ++r) {
+            const float2 v = turn[r * 33 + lane];
+            asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(obase + (int64_t)r * p.N * 2), "f"(v.x), "f"(v.y) : "memory");
+          }
+          __syncwarp();
+        }
+      } else {
+        atomicExch(&fail_s, 1);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (tid == 0 && fail_s) atomicExch(&g_cgemm_status, 6);
+}
+
 // Weight planes for cgemm_wx_kernel: (4, M, K) float32 = tf32(Re W), tf32(Re W - that), and the same
 // for Im W, from a complex64 matrix addressed by element strides (a transposed view costs nothing)
 // and optionally conjugated.
@@ -372,6 +534,39 @@ extern "C" int b200_cgemm_debug(float *host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_dbg, n * sizeof(float));
 }
 #endif
+
+extern "C" int b200_cgemm_grad(const b200_cgemm_grad_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "cgemm_grad: null argument block");
+  const b200_cgemm_grad_args &a = *args;
+  B200_REQUIRE(a.g && a.u && a.out, B200_ERR_NULL, "cgemm_grad: g, u, out must be non-null");
+  B200_REQUIRE(a.batch > 0 && a.M > 0 && a.N > 0 && a.L > 0, B200_ERR_SHAPE, "cgemm_grad: sizes must be positive");
+  B200_REQUIRE(a.M % GM == 0 && a.N % GN == 0 && (2 * (int64_t)a.L) % GK == 0, B200_ERR_SHAPE,
+               "cgemm_grad: M and N must be multiples of %d, L of %d (got M=%d N=%d L=%d)", GM, GK / 2, a.M, a.N, a.L);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a.g) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.u) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a.out) & 7) == 0,
+               B200_ERR_ALIGN, "cgemm_grad: operands must be 16-byte aligned");
+  B200_REQUIRE((int64_t)a.batch * a.M < (int64_t(1) << 31) && (int64_t)a.batch * a.N < (int64_t(1) << 31), B200_ERR_SHAPE,
+               "cgemm_grad: batch * rows too large");
+  GradMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  B200_REQUIRE(make_map(&maps.g, a.g, 2ull * a.L, (uint64_t)a.batch * a.M, 8ull * a.L, GM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                   make_map(&maps.u, a.u, 2ull * a.L, (uint64_t)a.batch * a.N, 8ull * a.L, GN, CU_TENSOR_MAP_SWIZZLE_128B),
+               B200_ERR_UNSUPPORTED, "cgemm_grad: tensor-map encoding failed");
+  const int smem = NSTAGE * STAGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(cgemm_ggh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return (int)e; }
+  // Cut the contraction into pieces of at most 16 stages (512 floats of K).  More pieces than SMs
+  // is deliberate: the tensor core adds into its float32 accumulator with truncation, a one-sided
+  // error that grows linearly with the length of one accumulation chain, whereas the pieces are
+  // combined by round-to-nearest float32 reductions.
+  const int64_t total = (int64_t)a.batch * (2 * (int64_t)a.L / GK);
+  const int per = total < 16 ? (int)total : 16;
+  const int64_t splits = (total + per - 1) / per;
+  B200_REQUIRE(splits <= 65535, B200_ERR_SHAPE, "cgemm_grad: batch * L too large (%lld pieces)", (long long)splits);
+  const dim3 grid((unsigned)(a.N / GN), (unsigned)(a.M / GM), (unsigned)splits);
+  cgemm_ggh_kernel<<<grid, NTHREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(maps, a, per);
+  return launch_status();
+}
 
 extern "C" int b200_cgemm_planes(const b200_cgemm_planes_args *args, void *stream) {
   B200_REQUIRE(args && args->w && args->planes, B200_ERR_NULL, "cgemm_planes: w and planes must be non-null");

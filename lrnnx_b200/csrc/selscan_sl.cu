@@ -130,9 +130,7 @@ __device__ __forceinline__ void convert_bc(float *bc, const T *rawB, const T *ra
 template <typename T> struct FwdSmem {
   static constexpr int RAW_ROWS = 5 * SCH;                               // u, delta, z, B, C
   static constexpr int RAW = RAW_ROWS * ST * (int)sizeof(T);             // one raw stage
-  static constexpr int OFF_BC = 2 * RAW;
-  static constexpr int OFF_DD = OFF_BC + ST * BCROW * 4;
-  static constexpr int OFF_PAR = OFF_DD + ST * DDROW * 4;                // bias[16], D[16]
+  static constexpr int OFF_PAR = 2 * RAW;                                // bias[16], D[16]
   static constexpr int TOTAL = ((OFF_PAR + 2 * SCH * 4 + 127) / 128) * 128;
 };
 
@@ -140,9 +138,13 @@ template <typename T, int NW, bool STG>
 __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_selscan_fwd_args p) {
   using SM = FwdSmem<T>;
   extern __shared__ __align__(128) unsigned char smem_all[];
-  // the per-(channel, t) results live in a statically allocated array: a distinct object, so the
-  // compiler may move the operand loads of later steps across the stores into it
+  // Everything the kernel writes AND reads in shared memory lives in statically allocated arrays,
+  // each a distinct object (the dynamic part holds only what the asynchronous copies deliver): the
+  // compiler may then move the loads of later steps or channels across the stores of earlier ones
   __shared__ __align__(16) float ys_all[NW][ST * YSROW];      // [t][channel pair][lane share] {c0, c0 + 1}
+  __shared__ __align__(16) float bc_all[NW][ST * BCROW];      // B | C of the stage, float32, [t][n]
+  __shared__ __align__(16) float dd_all[NW][ST * DDROW];      // {delta0, delta0 u0, delta1, delta1 u1} per (t, channel pair)
+  __shared__ __align__(16) T ot_all[NW][2 * SCH * ST];        // out and gated out tiles of the stage
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sl = lane & 3, cp = lane >> 2;
   const int tiles_per_b = p.dim / SCH;
@@ -185,8 +187,8 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
   issue(0);
   cp_commit();
 
-  float *bc = reinterpret_cast<float *>(smem + SM::OFF_BC);
-  float *dd = reinterpret_cast<float *>(smem + SM::OFF_DD);
+  float *bc = bc_all[warp];
+  float *dd = dd_all[warp];
   float *ys = ys_all[warp];
   float *par = reinterpret_cast<float *>(smem + SM::OFF_PAR);
   if (lane < SCH) {
@@ -336,9 +338,10 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
       *reinterpret_cast<float4 *>(q + (int64_t)n_stages * SN) = make_float4(h[1][0].x, h[1][0].y, h[1][1].x, h[1][1].y);
     }
     __syncwarp();
-    // ---- outputs (lane = timestep): out = y + D u into the delta rows, out * silu(z) into the z rows
+    // ---- outputs (lane = timestep): out = y + D u and out * silu(z) into the output tiles
     {
-      T *ot = raw + SCH * ST, *zt = raw + 2 * SCH * ST;
+      T *ot = ot_all[warp], *zt = ot_all[warp] + SCH * ST;
+      const T *zin = raw + 2 * SCH * ST;
 #pragma unroll 4
       for (int ch = 0; ch < SCH; ++ch) {
         // the four lanes' shares of channel ch at timestep `lane`: {c0, c0+1} pairs of shares 0..3
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
         const float o = fmaf(par[SCH + ch], to_f(raw[ch * ST + lane]), ysum);
         ot[ch * ST + lane] = from_f<T>(o);
         if (has_z) {
-          const float zv = to_f(zt[ch * ST + lane]);
+          const float zv = to_f(zin[ch * ST + lane]);
           zt[ch * ST + lane] = from_f<T>(o * zv * sigmoidf_(zv));
         }
       }
@@ -356,7 +359,7 @@ __global__ void __launch_bounds__(NW * 32) selscan_sl_fwd_kernel(const b200_sels
       store_rows<T, SCH>(Odst, p.out_ds, ot, t0, L, lane);
       if (has_z) store_rows<T, SCH>(OZdst, p.out_z_ds, zt, t0, L, lane);
     }
-    __syncwarp();     // the raw buffer of this stage is refilled by the copies issued two iterations later
+    __syncwarp();     // the output tiles are rewritten in the next iteration
   }
   cp_wait<0>();
 }
@@ -727,13 +730,14 @@ template <typename T> int launch_bwd(const b200_selscan_bwd_args &a, cudaStream_
 
 }  // namespace
 
-// Few rows leave most of the GPU idle under a serial-in-time kernel (a tile of 16 channels is one
-// warp): below this many warps (tiles times sequence segments) the lane-scan kernels are the
-// better fit.  The environment variable LRNNX_B200_SL_MIN_WARPS overrides the threshold (tests
+// A serial-in-time kernel hides its latencies only with several resident warps per scheduler, and a
+// tile of 16 channels is one warp: below 16 warps of work per SM (tiles times sequence segments)
+// the lane-scan kernels, which put 256 threads on 16 channels, are the better fit (measured at
+// the 768-tile Mamba-130M layer shape: 346 us against 301 us forward).  The environment variable LRNNX_B200_SL_MIN_WARPS overrides the threshold (tests
 // use it to run either kernel family on the same small problem).
 static int64_t min_warps() {
   if (const char *e = getenv("LRNNX_B200_SL_MIN_WARPS")) return atoll(e);
-  return 2 * (int64_t)sm_count_current();
+  return 16 * (int64_t)sm_count_current();
 }
 
 bool selscan_fwd_sl_supported(const b200_selscan_fwd_args &a) {
@@ -759,9 +763,9 @@ bool selscan_bwd_sl_supported(const b200_selscan_bwd_args &q) {
 }
 
 int selscan_fwd_sl(const b200_selscan_fwd_args &a, cudaStream_t st) {
-  if (a.dtype == B200_F32) return launch_fwd<float, 3>(a, st);
-  if (a.dtype == B200_BF16) return launch_fwd<__nv_bfloat16, 4>(a, st);
-  return launch_fwd<__half, 4>(a, st);
+  if (a.dtype == B200_F32) return launch_fwd<float, 2>(a, st);
+  if (a.dtype == B200_BF16) return launch_fwd<__nv_bfloat16, 2>(a, st);
+  return launch_fwd<__half, 2>(a, st);
 }
 
 int selscan_bwd_sl(const b200_selscan_bwd_args &a, cudaStream_t st) {

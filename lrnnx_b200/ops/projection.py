@@ -59,3 +59,28 @@ def project(W, x, conj_transpose=False):
         a.out_bs, a.out_ms = out.stride(0), out.stride(1)
         _lib.call("b200_cgemm_wx", a, torch.cuda.current_stream(x.device).cuda_stream)
     return out
+
+
+def grad_supported(g, u) -> bool:
+    if not (g.is_cuda and u.is_cuda and g.dtype == torch.complex64 and u.dtype == torch.complex64):
+        return False
+    if g.dim() != 3 or u.dim() != 3 or g.shape[0] != u.shape[0] or g.shape[2] != u.shape[2]:
+        return False
+    return g.shape[1] % 128 == 0 and u.shape[1] % 128 == 0 and g.shape[2] % 16 == 0
+
+
+def weight_grad(g, u):
+    """einsum("bml,bnl->mn", g, conj(u)) for complex64 g (batch, M, L), u (batch, N, L): the
+    gradient of a projection weight, summed over batch and time on the tensor cores."""
+    if not g.is_contiguous():
+        g = g.contiguous()
+    if not u.is_contiguous():
+        u = u.contiguous()
+    a = _lib.struct("b200_cgemm_grad_args")()
+    a.batch, a.M, a.L = g.shape
+    a.N = u.shape[1]
+    with torch.cuda.device(g.device):
+        out = torch.zeros((g.shape[1], u.shape[1]), dtype=torch.complex64, device=g.device)
+        a.g, a.u, a.out = g.data_ptr(), u.data_ptr(), out.data_ptr()
+        _lib.call("b200_cgemm_grad", a, torch.cuda.current_stream(g.device).cuda_stream)
+    return out

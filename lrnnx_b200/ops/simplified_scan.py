@@ -4,7 +4,7 @@ Mirror SimplifiedScanFn / simplified_scan_fn (lrnnx/ops/simplified_scan.py:14-23
 S5InnerFn / s5_inner_fn (:343-583): the projections Bu = B u and y = C x (and their data
 gradients) run on the tensor-core kernel of ``projection`` where its tiling applies, as complex
 einsums (cuBLAS) otherwise, around the diagonal scan kernel, which is called with identity B / C.
-The two weight gradients (sums over batch and time) are einsums.
+The two weight gradients (sums over batch and time) run on its companion kernel.
 
 One deliberate deviation: with ``return_last_state=True`` the reference's CUDA wrapper
 slices its output tensor instead of the state (simplified_scan.py:106-110) and returns a
@@ -27,6 +27,13 @@ def _proj(W, x, conj_transpose=False):
     if projection.supported(Wm, x if x.is_contiguous() else x.contiguous()):
         return projection.project(W, x, conj_transpose)
     return torch.einsum("mk,bkn->bmn", Wm, x)
+
+
+def _wgrad(g, u):
+    """sum over batch and time of g u^H: the tensor-core kernel where its tiling applies, einsum otherwise."""
+    if projection.grad_supported(g, u):
+        return projection.weight_grad(g, u)
+    return torch.einsum("bml,bnl->mn", g, u.conj())
 
 
 def _kernel_A(A):
@@ -62,7 +69,7 @@ class SimplifiedScanFn(torch.autograd.Function):
     def backward(ctx, dout, *args):
         u, delta, A_k, B, C, Bu, out, xs, ident, deltaA = ctx.saved_tensors
         dx_out = _proj(C, dout, conj_transpose=True)
-        dC = torch.einsum("bhl,bpl->hp", dout, out.conj())
+        dC = _wgrad(dout, out)
         if dx_out.stride(-1) != 1:
             dx_out = dx_out.contiguous()
         res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dx_out, xs, ctx.discretization,
@@ -70,7 +77,7 @@ class SimplifiedScanFn(torch.autograd.Function):
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du = _proj(B, dBu, conj_transpose=True)
-        dB = torch.einsum("bpl,bhl->ph", dBu, u.conj())
+        dB = _wgrad(dBu, u)
         if ctx.A_was_1d:
             dA = dA.squeeze(-1)
         return du, ddelta, dA, dB, dC, ddeltaA, None, None
@@ -118,7 +125,7 @@ class S5InnerFn(torch.autograd.Function):
         scale = 2.0 if ctx.conj_sym else 1.0
         dy_complex = torch.complex(scale * dout, torch.zeros_like(dout))
         dscan = _proj(C, dy_complex, conj_transpose=True)
-        dC = torch.einsum("bhl,bpl->hp", dy_complex, scan_out.conj())
+        dC = _wgrad(dy_complex, scan_out)
         if dscan.stride(-1) != 1:
             dscan = dscan.contiguous()
         res = simplified_scan_cuda.bwd(Bu, delta, A_k, ident, ident, deltaA, dscan, xs, ctx.discretization,
@@ -126,7 +133,7 @@ class S5InnerFn(torch.autograd.Function):
         dBu, ddelta, dA = res[0], res[1], res[2]
         ddeltaA = res[5] if ctx.has_deltaA else None
         du_scan = _proj(B, dBu, conj_transpose=True)
-        dB = torch.einsum("bpl,bhl->ph", dBu, u.conj())
+        dB = _wgrad(dBu, u) if u.is_complex() else torch.einsum("bpl,bhl->ph", dBu, u.conj())
         if u.is_complex():
             du = du_scan + torch.complex(du_skip, torch.zeros_like(du_skip))
         else:

@@ -78,3 +78,27 @@ def test_simplified_scan_uses_the_projection_kernel_and_matches_the_oracle():
         e_ref = float((b32.to(wide) - b64).abs().max())
         e_gpu = float((a.cpu().to(wide) - b64).abs().max())
         assert e_gpu <= 4 * e_ref + 1e-5 * scale, (name, e_gpu, e_ref, scale)
+
+
+@pytest.mark.parametrize("batch,M,N,L", [(1, 128, 128, 16), (2, 128, 256, 208), (3, 256, 128, 2048), (8, 512, 256, 4096)])
+def test_weight_gradient_matches_float64(batch, M, N, L):
+    """sum over batch and time of g u^H (the gradient of a projection weight) on the tensor cores."""
+    from lrnnx_b200 import _lib
+    from lrnnx_b200.ops import projection
+    g = torch.Generator().manual_seed(M + N + L)
+    G, U = _cn(g, batch, M, L), _cn(g, batch, N, L)
+    Gg, Ug = G.cuda(), U.cuda()
+    assert projection.grad_supported(Gg, Ug)
+    out = projection.weight_grad(Gg, Ug)
+    torch.cuda.synchronize()
+    assert _lib.lib().b200_device_status() == 0
+    f32 = torch.einsum("bml,bnl->mn", Gg, Ug.conj())
+    if batch * M * N * L <= 3 * 256 * 128 * 2048:
+        ref = torch.einsum("bml,bnl->mn", G.to(torch.complex128), U.to(torch.complex128).conj())
+    else:       # the float64 product of the large case on the GPU
+        ref = torch.einsum("bml,bnl->mn", Gg.to(torch.complex128), Ug.to(torch.complex128).conj()).cpu()
+    scale = float(ref.abs().max())
+    err = float((out.cpu().to(torch.complex128) - ref).abs().max())
+    err32 = float((f32.cpu().to(torch.complex128) - ref).abs().max())
+    assert out.shape == (M, N) and out.dtype == torch.complex64
+    assert err <= 4 * err32 + 2e-6 * scale, (err, err32, scale)
