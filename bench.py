@@ -764,11 +764,20 @@ class LmTrain:
 
     def _train(self, ids):
         logits = self.model(ids)
-        loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, self.vocab).float(), ids[:, 1:].reshape(-1))
+        # next-token loss: the last position has no target (ignored) instead of slicing the logits, which
+        # would copy them
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, self.vocab).float(), self.labels(ids).view(-1),
+                                                 ignore_index=-100)
         self.opt.zero_grad(set_to_none=True)
         loss.backward()
         self.opt.step()
         return loss
+
+    @staticmethod
+    def labels(ids):
+        lab = torch.full_like(ids, -100)
+        lab[:, :-1] = ids[:, 1:]
+        return lab
 
     def step(self, record=False):
         e = [torch.cuda.Event(enable_timing=True) for _ in range(2)] if record else None

@@ -210,8 +210,10 @@ __global__ void __launch_bounds__(256) conv1d_update_kernel(const b200_conv1d_ar
 }
 
 // ------------------------------------------------------------------ residual add + RMSNorm
-constexpr int NT = 256;           // threads per CTA: a CTA walks rows, a thread owns up to NV columns x 8
-constexpr int NV = 2;             // 16-byte vectors per thread: rows up to 256 * 2 * 8 = 4096 columns
+// A CTA of NT threads walks rows; a thread owns NV 16-byte vectors (8 columns each) of a row.
+// (NT, NV) is picked per call so that most threads have work: (128, 1) up to 1024 columns,
+// (256, 1) up to 2048, (256, 2) up to 4096.
+constexpr int MAXCOLS = 4096;
 
 template <typename T> __device__ __forceinline__ void ldv(const T *p, float (&v)[8]) {
   if constexpr (sizeof(T) == 2) {
@@ -237,7 +239,7 @@ template <typename T> __device__ __forceinline__ void stv(T *p, const float (&v)
   }
 }
 
-__device__ __forceinline__ float block_sum(float v, float *red) {
+template <int NT> __device__ __forceinline__ float block_sum(float v, float *red) {
   v = warp_sum(v);
   const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
   __syncthreads();                 // red may still be read from the previous use
@@ -250,7 +252,7 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 }
 
 // z = x + residual (stored as residual_out when asked for); y = z * rstd * w, rstd = rsqrt(mean z^2 + eps)
-template <typename T, typename R>
+template <typename T, typename R, int NT, int NV>
 __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const b200_rmsnorm_args p) {
   __shared__ float red[NT / 32];
   const int H = p.cols;
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const b200_rmsnorm_args
         for (int i = 0; i < 8; ++i) ss = fmaf(z[j][i], z[j][i], ss);
       }
     }
-    ss = block_sum(ss, red);
+    ss = block_sum<NT>(ss, red);
     const float rstd = rsqrtf(ss / (float)H + p.eps);
     if (threadIdx.x == 0 && p.rstd) reinterpret_cast<float *>(p.rstd)[row] = rstd;
 #pragma unroll
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const b200_rmsnorm_args
 }
 
 // dz = (w dy - zhat mean(zhat w dy)) rstd + dresidual;  dw += dy zhat  (per-thread partial, one atomic per CTA column)
-template <typename T, typename R>
+template <typename T, typename R, int NT, int NV>
 __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const b200_rmsnorm_args p) {
   __shared__ float red[NT / 32];
   const int H = p.cols;
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const b200_rmsnorm_args
         }
       }
     }
-    c1 = block_sum(c1, red) / (float)H;
+    c1 = block_sum<NT>(c1, red) / (float)H;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int c = (j * NT + threadIdx.x) * 8;
@@ -382,8 +384,8 @@ int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
 
 int check_norm(const b200_rmsnorm_args &a, bool bwd) {
   B200_REQUIRE(a.weight && a.rows > 0 && a.cols > 0, B200_ERR_NULL, "rmsnorm: weight must be non-null, sizes positive");
-  B200_REQUIRE(a.cols % 8 == 0 && a.cols <= NT * NV * 8, B200_ERR_SHAPE,
-               "rmsnorm: the row length must be a multiple of 8 and at most %d (got %d)", NT * NV * 8, a.cols);
+  B200_REQUIRE(a.cols % 8 == 0 && a.cols <= MAXCOLS, B200_ERR_SHAPE,
+               "rmsnorm: the row length must be a multiple of 8 and at most %d (got %d)", MAXCOLS, a.cols);
   B200_REQUIRE(a.dtype == B200_F32 || a.dtype == B200_F16 || a.dtype == B200_BF16, B200_ERR_DTYPE, "rmsnorm: unknown dtype");
   B200_REQUIRE(a.residual_dtype == a.dtype || a.residual_dtype == B200_F32, B200_ERR_DTYPE,
                "rmsnorm: the residual is kept in the activation dtype or in float32");
@@ -435,29 +437,38 @@ int b200_conv1d_update(const b200_conv1d_args *args, void *stream) {
   return launch_status();
 }
 
+// The backward adds a per-CTA partial of dweight with one atomic per column: fewer, longer-lived
+// CTAs keep those atomics (all CTAs hit the same `cols` addresses) off the critical path.
+#define NORM_LAUNCH(KERNEL, R_, NT_, NV_)                                                                    \
+  do {                                                                                                       \
+    const int64_t want = (int64_t)sm_count_current() * (is_bwd ? 4 : 2048 / NT_);                            \
+    const unsigned grid = (unsigned)(args->rows < want ? args->rows : want);                                 \
+    DISPATCH_T(args->dtype, (KERNEL<T, R_, NT_, NV_><<<grid, NT_, 0, st>>>(*args)));                          \
+  } while (0)
+#define NORM_SHAPES(KERNEL, R_)                                                \
+  do {                                                                         \
+    if (args->cols <= 1024) NORM_LAUNCH(KERNEL, R_, 128, 1);                   \
+    else if (args->cols <= 2048) NORM_LAUNCH(KERNEL, R_, 256, 1);              \
+    else NORM_LAUNCH(KERNEL, R_, 256, 2);                                      \
+  } while (0)
+
 int b200_rmsnorm_fwd(const b200_rmsnorm_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "rmsnorm_fwd: null argument block");
   if (int e = check_norm(*args, false)) return e;
-  const int64_t grid = args->rows < (int64_t)sm_count_current() * 8 ? args->rows : (int64_t)sm_count_current() * 8;
+  constexpr bool is_bwd = false;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (args->residual_dtype == B200_F32) {
-    DISPATCH_T(args->dtype, (rmsnorm_fwd_kernel<T, float><<<(unsigned)grid, NT, 0, st>>>(*args)));
-  } else {
-    DISPATCH_T(args->dtype, (rmsnorm_fwd_kernel<T, T><<<(unsigned)grid, NT, 0, st>>>(*args)));
-  }
+  if (args->residual_dtype == B200_F32 && args->dtype != B200_F32) NORM_SHAPES(rmsnorm_fwd_kernel, float);
+  else NORM_SHAPES(rmsnorm_fwd_kernel, T);
   return launch_status();
 }
 
 int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "rmsnorm_bwd: null argument block");
   if (int e = check_norm(*args, true)) return e;
-  const int64_t grid = args->rows < (int64_t)sm_count_current() * 4 ? args->rows : (int64_t)sm_count_current() * 4;
+  constexpr bool is_bwd = true;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (args->residual_dtype == B200_F32) {
-    DISPATCH_T(args->dtype, (rmsnorm_bwd_kernel<T, float><<<(unsigned)grid, NT, 0, st>>>(*args)));
-  } else {
-    DISPATCH_T(args->dtype, (rmsnorm_bwd_kernel<T, T><<<(unsigned)grid, NT, 0, st>>>(*args)));
-  }
+  if (args->residual_dtype == B200_F32 && args->dtype != B200_F32) NORM_SHAPES(rmsnorm_bwd_kernel, float);
+  else NORM_SHAPES(rmsnorm_bwd_kernel, T);
   return launch_status();
 }
 

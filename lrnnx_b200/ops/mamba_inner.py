@@ -89,7 +89,8 @@ class MambaInnerFn(torch.autograd.Function):
             dy = dy.to(dt)
             # out_proj
             dout_z = torch.bmm(_wb(out_proj_weight.to(dt).t(), batch), dy.transpose(1, 2))        # (batch, d, L)
-            d_out_w = torch.einsum("blm,bdl->md", dy, out_z)
+            # weight gradients: batched GEMMs on transposed views (no operand is copied), summed over the batch
+            d_out_w = torch.bmm(dy.transpose(1, 2), out_z.transpose(1, 2)).sum(0)
             d_out_b = dy.sum(dim=(0, 1)) if has_out_bias else None
             # recomputed, not stored
             xc = _conv_forward(x, w2, cb)
@@ -104,8 +105,8 @@ class MambaInnerFn(torch.autograd.Function):
             dx_dbl[:, :R].copy_(torch.bmm(_wb(delta_proj_weight.to(dt).t(), batch), ddelta))
             dx_dbl[:, R:R + N].copy_(dB.squeeze(1))
             dx_dbl[:, R + N:].copy_(dC.squeeze(1))
-            d_dt_w = torch.einsum("bdl,brl->dr", ddelta, x_dbl[:, :R])
-            d_xp_w = torch.einsum("brl,bdl->rd", dx_dbl, xc)
+            d_dt_w = torch.bmm(ddelta, x_dbl[:, :R].transpose(1, 2)).sum(0)
+            d_xp_w = torch.bmm(dx_dbl, xc.transpose(1, 2)).sum(0)
             dxc = torch.baddbmm(dxc, _wb(x_proj_weight.to(dt).t(), batch), dx_dbl)
             # convolution
             a = _conv_args(x, w2, cb, True)
