@@ -222,11 +222,45 @@ class S5Scan:
             # as SimplifiedScanFn.backward calls it (identity B and C: dB / dC are not needed, and the
             # forward output, which is the state sequence, is handed back)
             self.res = self.ext.bwd(*args, self.dBu_in, self.x, self.disc, need_dB_dC=False, out_=self.out)
+        self.g_step = None
+        if pg is not None:
+            # Data-parallel step as ONE graph per parity: forward, backward and the copy of dA into
+            # buffer p on the main branch; the all-reduce of the previous step's dA (buffer 1 - p) on a
+            # forked branch, so the collective overlaps this step's kernels and costs no host work per
+            # step (no stream wait, no enqueue: one graph launch).
+            try:
+                self._ar = [torch.zeros(self.P, 1, 2, device=dev) for _ in range(2)]
+                for buf in self._ar:
+                    torch.distributed.all_reduce(buf, group=pg)          # communicator warm-up outside capture
+                torch.cuda.synchronize()
+                graphs = []
+                for par in range(2):
+                    g = torch.cuda.CUDAGraph()
+                    branch = torch.cuda.Stream(device=dev)
+                    with torch.cuda.graph(g):
+                        branch.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(branch):
+                            torch.distributed.all_reduce(self._ar[1 - par], group=pg)
+                        out, x = self.ext.fwd(*args, self.disc)
+                        res = self.ext.bwd(*args, self.dBu_in, x, self.disc, need_dB_dC=False, out_=out)
+                        self._ar[par].copy_(torch.view_as_real(res[2]))
+                        torch.cuda.current_stream().wait_stream(branch)
+                    graphs.append(g)
+                self.g_step, self._parity = graphs, 0
+                self.describe["collective"] = "dA all-reduce (NCCL) captured in the step's CUDA graph on a forked branch"
+            except Exception as exc:      # capture of the collective refused: per-step asynchronous all-reduce instead
+                self.g_step = None
+                self.describe["collective"] = f"dA all-reduce (NCCL) enqueued per step ({type(exc).__name__} during graph capture)"
+                torch.cuda.synchronize()
 
     def step(self, record=False):
         """forward + backward scan kernels through the extension entry points (graph replay)."""
         if self.flush_buf is not None:
             self.flush_buf.zero_()
+        if self.g_step is not None:
+            self.g_step[self._parity].replay()
+            self._parity ^= 1
+            return self.res
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
@@ -250,6 +284,10 @@ class S5Scan:
     launches_per_step = 2
 
     def drain(self):
+        if self.g_step is not None:
+            # the dA of the last step is still to be reduced
+            torch.distributed.all_reduce(self._ar[self._parity ^ 1], group=self.pg)
+            return
         if self._work is not None:
             self._work.wait()
             self._work = None
@@ -295,6 +333,19 @@ class S5Scan:
         return self.h_x.numel() * 4 + self.h_delta.numel() * 4, 4
 
     def kernel_rooflines(self):
+        if not self.ev:      # the step ran as one graph: time the two kernels apart in a short pass of their own
+            for _ in range(8):
+                e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                if self.flush_buf is not None:
+                    self.flush_buf.zero_()
+                e[0].record()
+                self.g_fwd.replay()
+                e[1].record()
+                self.g_bwd.replay()
+                e[2].record()
+                self.ev.append(e)
+            torch.cuda.synchronize()
+            self.ev = self.ev[3:]
         f = [a[0].elapsed_time(a[1]) for a in self.ev]
         b = [a[1].elapsed_time(a[2]) for a in self.ev]
         return {"simpscan_fwd_kernel": (self.fwd_bytes, statistics.mean(f)),
@@ -955,7 +1006,7 @@ def run_reference(args, wl):
                              "sample": wl.cpu_sample},
             "e2e": {"value": tps, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
@@ -1022,7 +1073,8 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
         if note:
             roofs[kname]["note"] = note
     dominant = max(roofs, key=lambda k: roofs[k]["ms_per_launch"])
-    cpu_tps, cpu_sec = time_cpu(wl, 1, 0)
+    # the CPU baseline is taken at N = 1 only (the other ranks would wait for rank 0's host work)
+    cpu_tps, cpu_sec = time_cpu(wl, 1, 0) if world == 1 else (None, None)
     h2d, d2h = wl.e2e_bytes()
     strong = getattr(wl, "scaling", "weak") == "strong"
     total_tokens = wl.tokens * (1 if (strong and getattr(wl, "sp", False)) else world)
@@ -1041,7 +1093,8 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
            "roofline": dict(roofs[dominant], kernel=dominant),
            "kernels": roofs,
            "cpu_baseline": {"value": cpu_tps, "unit": wl.unit, "cores": torch.get_num_threads(),
-                            "kind": "port", "sample": wl.cpu_sample, "seconds": cpu_sec}}
+                            "kind": "port", "sample": wl.cpu_sample if world == 1 else "not timed at N > 1",
+                            "seconds": cpu_sec}}
     if check is not None:
         rec["sp_check"] = check
     return rec
@@ -1083,18 +1136,45 @@ def run_ours(args, wl, with_subs):
             line["workloads"] = subs
     elif rank == 0 and line.get("sp_check") is not None and not line["sp_check"]["ok"]:
         failed = True
-    if rank == 0:
-        print(json.dumps(line))
     if world > 1:
         flag = torch.tensor([1 if failed else 0], device=dev)
         torch.distributed.broadcast(flag, 0)
         failed = bool(flag.item())
-        torch.distributed.destroy_process_group()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+    if rank == 0:
+        emit(json.dumps(line))
     if failed:
-        raise SystemExit("bench.py: the sequence-parallel output differs from the unsplit forward (sp_check)")
+        sys.stderr.write("bench.py: the sequence-parallel output differs from the unsplit forward (sp_check)\n")
+    if world > 1:
+        # Leave without running destructors: tearing down a communicator whose collectives were
+        # captured in CUDA graphs can block for minutes in the communicator's destroy call, after
+        # every number has been produced.  All ranks have passed the barrier above.
+        sys.stderr.flush()
+        os._exit(1 if failed else 0)
+    if failed:
+        raise SystemExit(1)
+
+
+_JSON_FD = None
+
+
+def emit(text):
+    """Write the result line to the process's original stdout."""
+    if _JSON_FD is None:
+        print(text, flush=True)
+    else:
+        os.write(_JSON_FD, (text + "\n").encode())
 
 
 def main():
+    # Libraries (the collective library prints its version banner) write to file descriptor 1;
+    # the result line must be the only thing on stdout, so everything else is sent to stderr.
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

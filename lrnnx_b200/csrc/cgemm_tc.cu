@@ -30,9 +30,6 @@ namespace b200 {
 namespace {
 
 __device__ int g_cgemm_status = 0;
-#ifdef CGEMM_DEBUG
-__device__ float g_dbg[8192];
-#endif
 
 constexpr int GM = 128;               // weight rows per CTA
 constexpr int GN = 128;               // activation floats per CTA (64 complex columns)
@@ -148,28 +145,6 @@ cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-#ifdef CGEMM_DEBUG
-  if (warp >= 2) {      // fill both accumulators with 7.0: tells "the MMA wrote zeros" from "the MMA wrote nothing"
-    const uint32_t seven = __float_as_uint(7.0f);
-    for (int c = 0; c < TMEM_COLS / 32; ++c) {
-      const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + c * 32;
-      asm volatile(
-          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-          "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
-          "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};\n\t"
-          "tcgen05.wait::st.sync.aligned;" ::"r"(ta), "r"(seven) : "memory");
-    }
-  }
-  if (warp == 4) {
-    float rb[32];
-    tmem_ld32(tmem_base + 0, rb);
-    if (lane < 2) for (int i = 0; i < 8; ++i) g_dbg[4100 + lane * 8 + i] = rb[i];
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (tid == 0) g_dbg[4000] = __uint_as_float(tmem_base);
-#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -197,27 +172,6 @@ cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) 
         if (!mbar_wait(&full[s], ph, WAIT_LIMIT)) { ok = false; break; }
         tc_fence_after();
         const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
-#ifdef CGEMM_DEBUG
-        if (ks == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-          const uint64_t da = a_desc(st), db = b_desc(st + 4 * TILE);
-          g_dbg[4200] = __uint_as_float(st);
-          g_dbg[4201] = __uint_as_float((uint32_t)da); g_dbg[4202] = __uint_as_float((uint32_t)(da >> 32));
-          g_dbg[4203] = __uint_as_float((uint32_t)db); g_dbg[4204] = __uint_as_float((uint32_t)(db >> 32));
-          g_dbg[4205] = __uint_as_float(kIdesc);
-          g_dbg[4206] = __uint_as_float(smem_u32(smem_raw));
-        }
-#endif
-#ifdef CGEMM_EXP_KK
-        {                        // experiment: D1 = ReHi * ReHi^T with both operands K-major
-          for (int kk = 0; kk < GK / 8; ++kk) {
-            const uint64_t ad = a_desc(st + kk * 32);
-            mma_tf32(d1, ad, ad, kk > 0 ? 1u : 0u, kIdesc & ~(1u << 16));
-          }
-          if (!mbar_wait(&lo_ready[s], ph, WAIT_LIMIT)) { ok = false; break; }
-          mma_commit(&empty[s]);
-          continue;
-        }
-#endif
         // products with the high part of the activation
 #pragma unroll
         for (int kk = 0; kk < GK / 8; ++kk) {
@@ -261,12 +215,6 @@ cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) 
         r.w = tf32_low(v.w);
         lo[i * 128 + et] = r;
       }
-#ifdef CGEMM_DEBUG
-      if (ks == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        const float *t0 = reinterpret_cast<const float *>(smem + (size_t)s * STAGE_BYTES);
-        for (int i = et; i < 6 * 256; i += 128) g_dbg[i] = t0[(i / 256) * (TILE / 4) + (i % 256)];
-      }
-#endif
       fence_proxy_async();                      // generic-proxy writes -> visible to the tensor core's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(&lo_ready[s]);
@@ -284,10 +232,6 @@ cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) 
         const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + c * 32;
         tmem_ld32(ta, v1);
         tmem_ld32(ta + GN, v2);
-#ifdef CGEMM_DEBUG
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && c == 0 && row < 4)
-          for (int i = 0; i < 32; ++i) { g_dbg[2048 + row * 64 + i] = v1[i]; g_dbg[2048 + row * 64 + 32 + i] = v2[i]; }
-#endif
         float4 *dst = reinterpret_cast<float4 *>(orow + c * 16);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -529,11 +473,6 @@ int cgemm_status_read() {
 
 using namespace b200;
 
-#ifdef CGEMM_DEBUG
-extern "C" int b200_cgemm_debug(float *host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_dbg, n * sizeof(float));
-}
-#endif
 
 extern "C" int b200_cgemm_grad(const b200_cgemm_grad_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "cgemm_grad: null argument block");

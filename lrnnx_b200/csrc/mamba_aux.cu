@@ -10,7 +10,7 @@
 namespace b200 {
 namespace {
 
-constexpr int CVT = 128;          // threads per CTA of the convolution kernels
+constexpr int CVT = 256;          // threads per CTA of the convolution kernels
 constexpr int CVE = 8;            // timesteps per thread
 constexpr int MAXW = 4;           // widest convolution
 
@@ -68,53 +68,66 @@ __device__ __forceinline__ float dsilu_f(float x) {
 }
 
 // out[b, d, t] = act(bias[d] + sum_k w[d, k] x[b, d, t - (W-1) + k])
+// A CTA owns one channel (its taps are read once) and walks that channel's work items, an item
+// being CVT * CVE consecutive steps of one batch row: few, long-lived CTAs instead of one per item
+// (the kernel moves 4 bytes per thread-instruction; the rate at which thread blocks can be
+// started would bound it otherwise).
 template <typename T>
 __global__ void __launch_bounds__(CVT) conv1d_fwd_kernel(const b200_conv1d_args p) {
-  const int row = blockIdx.x;                       // (batch, channel)
-  const int b = row / p.dim, d = row % p.dim;
-  const int t = (blockIdx.y * CVT + threadIdx.x) * CVE;
-  if (t >= p.seqlen) return;
-  const int W = p.width;
-  const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
-  T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+  const int d = blockIdx.x;
+  const int W = p.width, L = p.seqlen;
+  const int nblk = (L + CVT * CVE - 1) / (CVT * CVE), items = p.batch * nblk;
+  // the taps right-aligned in a window of MAXW (zeros in front): every register index below is a
+  // compile-time constant whatever the width
   float w[MAXW];
 #pragma unroll
-  for (int k = 0; k < MAXW; ++k) w[k] = k < W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k]) : 0.f;
+  for (int k = 0; k < MAXW; ++k)
+    w[k] = k >= MAXW - W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k - (MAXW - W)]) : 0.f;
   const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
-  float prev[CVE], cur[CVE], y[CVE];
-  load8<T>(x, t - CVE, p.seqlen, prev);
-  load8<T>(x, t, p.seqlen, cur);
+  for (int item = blockIdx.y; item < items; item += gridDim.y) {
+    const int b = item / nblk;
+    const int t = ((item - b * nblk) * CVT + threadIdx.x) * CVE;
+    if (t >= L) continue;
+    const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
+    T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
+    float prev[CVE], cur[CVE], y[CVE];
+    load8<T>(x, t - CVE, L, prev);
+    load8<T>(x, t, L, cur);
 #pragma unroll
-  for (int i = 0; i < CVE; ++i) {
-    float acc = bias;
+    for (int i = 0; i < CVE; ++i) {
+      float acc = bias;
 #pragma unroll
-    for (int k = 0; k < MAXW; ++k) {
-      if (k < W) {
-        const int j = i - (W - 1) + k;               // offset inside [prev | cur]
+      for (int k = 0; k < MAXW; ++k) {
+        const int j = i - (MAXW - 1) + k;              // offset inside [prev | cur]
         acc = fmaf(w[k], j >= 0 ? cur[j] : prev[CVE + j], acc);
       }
+      y[i] = p.silu ? silu_f(acc) : acc;
     }
-    y[i] = p.silu ? silu_f(acc) : acc;
+    store8<T>(out, t, L, y);
   }
-  store8<T>(out, t, p.seqlen, y);
 }
 
 // dx, and per-thread partial sums of dweight / dbias folded per CTA into float32 accumulators
 template <typename T>
 __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args p) {
-  const int row = blockIdx.x;
-  const int b = row / p.dim, d = row % p.dim;
-  const int t = (blockIdx.y * CVT + threadIdx.x) * CVE;
+  const int d = blockIdx.x;                         // a CTA owns one channel, as in the forward kernel
   const int W = p.width, L = p.seqlen;
-  const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
-  const T *dout = reinterpret_cast<const T *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
-  T *dx = reinterpret_cast<T *>(p.dx) + (int64_t)b * p.dx_bs + (int64_t)d * p.dx_ds;
+  const int nblk = (L + CVT * CVE - 1) / (CVT * CVE), items = p.batch * nblk;
+  // the taps right-aligned in a window of MAXW (zeros in front): every register index below is a
+  // compile-time constant whatever the width
   float w[MAXW];
 #pragma unroll
-  for (int k = 0; k < MAXW; ++k) w[k] = k < W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k]) : 0.f;
+  for (int k = 0; k < MAXW; ++k)
+    w[k] = k >= MAXW - W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k - (MAXW - W)]) : 0.f;
   const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
   float dw[MAXW] = {0.f, 0.f, 0.f, 0.f}, db = 0.f;
-  if (t < L) {
+  for (int item = blockIdx.y; item < items; item += gridDim.y) {
+    const int b = item / nblk;
+    const int t = ((item - b * nblk) * CVT + threadIdx.x) * CVE;
+    if (t >= L) continue;
+    const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
+    const T *dout = reinterpret_cast<const T *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
+    T *dx = reinterpret_cast<T *>(p.dx) + (int64_t)b * p.dx_bs + (int64_t)d * p.dx_ds;
     // x over [t - 8, t + 16), dout over [t, t + 16): the gradient of the pre-activation is needed
     // for this thread's 8 steps and the W - 1 steps after them
     float xs[3 * CVE], g[2 * CVE];
@@ -143,8 +156,7 @@ __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args 
       if (p.silu) {
         float acc = bias;
 #pragma unroll
-        for (int k = 0; k < MAXW; ++k)
-          if (k < W) acc = fmaf(w[k], xs[CVE + i - (W - 1) + k], acc);
+        for (int k = 0; k < MAXW; ++k) acc = fmaf(w[k], xs[CVE + i - (MAXW - 1) + k], acc);
         gi *= dsilu_f(acc);
       }
       dpre[i] = gi;
@@ -154,17 +166,15 @@ __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args 
     for (int i = 0; i < CVE; ++i) {
       float acc = 0.f;
 #pragma unroll
-      for (int k = 0; k < MAXW; ++k)
-        if (k < W) acc = fmaf(w[k], dpre[i + (W - 1) - k], acc);     // x[t+i] feeds out[t+i+(W-1)-k] through w[k]
+      for (int k = 0; k < MAXW; ++k) acc = fmaf(w[k], dpre[i + (MAXW - 1) - k], acc);   // x[t+i] feeds out[t+i+(MAXW-1)-k] through tap k
       dxv[i] = acc;
       db += dpre[i];
 #pragma unroll
-      for (int k = 0; k < MAXW; ++k)
-        if (k < W) dw[k] = fmaf(dpre[i], xs[CVE + i - (W - 1) + k], dw[k]);
+      for (int k = 0; k < MAXW; ++k) dw[k] = fmaf(dpre[i], xs[CVE + i - (MAXW - 1) + k], dw[k]);
     }
     store8<T>(dx, t, L, dxv);
   }
-  // CTA reduction of the parameter gradients, then one atomic per CTA and parameter
+  // CTA reduction of the parameter gradients (summed over the CTA's items), then one atomic per CTA and parameter
   __shared__ float red[CVT / 32][MAXW + 1];
   const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
 #pragma unroll
@@ -180,7 +190,8 @@ __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args 
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < CVT / 32; ++i) s += red[i][threadIdx.x];
-    if (threadIdx.x < W) atomicAdd(reinterpret_cast<float *>(p.dweight) + (int64_t)d * W + threadIdx.x, s);
+    if ((int)threadIdx.x >= MAXW - W && threadIdx.x < MAXW)
+      atomicAdd(reinterpret_cast<float *>(p.dweight) + (int64_t)d * W + threadIdx.x - (MAXW - W), s);
     if (threadIdx.x == MAXW && p.dbias) atomicAdd(reinterpret_cast<float *>(p.dbias) + d, s);
   }
 }
@@ -365,6 +376,78 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const b200_rmsnorm_args
   }
 }
 
+// The same backward for rows of up to 1024 columns: a warp owns a row (lane l holds the 8-column
+// vectors l, l + 32, ...), so a row costs one warp reduction and no block barrier, and the warps of
+// an SM have independent rows in flight.  The weight-gradient partials stay in registers over the
+// warp's rows, are summed per CTA in shared memory and leave as one atomic per CTA and column.
+constexpr int NWT = 256;          // threads per CTA of the warp-per-row kernel
+template <typename T, typename R, int NV>
+__global__ void __launch_bounds__(NWT) rmsnorm_bwd_warp_kernel(const b200_rmsnorm_args p) {
+  __shared__ float sdw[NV * 256];
+  const int H = p.cols;
+  const int lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < NV * 256; c += NWT) sdw[c] = 0.f;
+  __syncthreads();
+  float dwacc[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  const int64_t nwarps = (int64_t)gridDim.x * (NWT / 32);
+  for (int64_t row = (int64_t)blockIdx.x * (NWT / 32) + (threadIdx.x >> 5); row < p.rows; row += nwarps) {
+    const R *z = reinterpret_cast<const R *>(p.residual_out) + row * p.residual_out_rs;
+    const T *dy = reinterpret_cast<const T *>(p.dy) + row * p.dy_rs;
+    const float rstd = reinterpret_cast<const float *>(p.rstd)[row];
+    float zh[NV][8], wdy[NV][8];
+    float c1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < H) {
+        float w[8], g[8];
+        ldv<R>(z + c, zh[j]);
+        ldv<T>(dy + c, g);
+        ldv<T>(reinterpret_cast<const T *>(p.weight) + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          zh[j][i] *= rstd;
+          wdy[j][i] = g[i] * w[i];
+          c1 = fmaf(zh[j][i], wdy[j][i], c1);
+          dwacc[j][i] = fmaf(g[i], zh[j][i], dwacc[j][i]);
+        }
+      }
+    }
+    c1 = warp_sum(c1) / (float)H;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * 32 + lane) * 8;
+      if (c < H) {
+        float dz[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dz[i] = (wdy[j][i] - zh[j][i] * c1) * rstd;
+        if (p.dresidual) {
+          float r[8];
+          ldv<R>(reinterpret_cast<const R *>(p.dresidual) + row * p.dresidual_rs + c, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dz[i] += r[i];
+        }
+        stv<T>(reinterpret_cast<T *>(p.dx) + row * p.dx_rs + c, dz);
+        if (p.dresidual_in) stv<R>(reinterpret_cast<R *>(p.dresidual_in) + row * p.dresidual_in_rs + c, dz);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = (j * 32 + lane) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&sdw[c + i], dwacc[j][i]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += NWT) atomicAdd(reinterpret_cast<float *>(p.dweight) + c, sdw[c]);
+}
+
 int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
   B200_REQUIRE(a.x && a.weight && (bwd || a.out), B200_ERR_NULL, "conv1d: x, weight, out must be non-null");
   B200_REQUIRE(a.batch > 0 && a.dim > 0 && (update || a.seqlen > 0), B200_ERR_SHAPE, "conv1d: sizes must be positive");
@@ -378,8 +461,20 @@ int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
     B200_REQUIRE(a.dout && a.dx && a.dweight, B200_ERR_NULL, "conv1d_bwd: dout, dx, dweight must be non-null");
     B200_REQUIRE(!a.bias || a.dbias, B200_ERR_NULL, "conv1d_bwd: dbias is required when bias is given");
   }
-  B200_REQUIRE((int64_t)a.batch * a.dim < (int64_t(1) << 31), B200_ERR_SHAPE, "conv1d: too many rows");
+  B200_REQUIRE((int64_t)a.batch * ((a.seqlen + CVT * CVE - 1) / (CVT * CVE)) < (int64_t(1) << 31), B200_ERR_SHAPE,
+               "conv1d: too many (batch, block) items per channel");
   return 0;
+}
+
+// grid of the convolution kernels: a column of CTAs per channel, as many per channel as it takes
+// to put about two CTAs on every resident slot (8 per SM), and never more than the channel has items
+dim3 conv_grid(const b200_conv1d_args &a) {
+  const int64_t nblk = (a.seqlen + CVT * CVE - 1) / (CVT * CVE), items = (int64_t)a.batch * nblk;
+  const int64_t slots = (int64_t)sm_count_current() * 8;
+  int64_t gy = (2 * slots + a.dim - 1) / a.dim;
+  gy = gy < 1 ? 1 : (gy > items ? items : gy);
+  if (gy > 65535) gy = 65535;
+  return dim3((unsigned)a.dim, (unsigned)gy);
 }
 
 int check_norm(const b200_rmsnorm_args &a, bool bwd) {
@@ -413,7 +508,7 @@ extern "C" {
 int b200_conv1d_fwd(const b200_conv1d_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "conv1d_fwd: null argument block");
   if (int e = check_conv(*args, false, false)) return e;
-  const dim3 grid((unsigned)(args->batch * args->dim), (unsigned)((args->seqlen + CVT * CVE - 1) / (CVT * CVE)));
+  const dim3 grid = conv_grid(*args);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   DISPATCH_T(args->dtype, (conv1d_fwd_kernel<T><<<grid, CVT, 0, st>>>(*args)));
   return launch_status();
@@ -422,7 +517,7 @@ int b200_conv1d_fwd(const b200_conv1d_args *args, void *stream) {
 int b200_conv1d_bwd(const b200_conv1d_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "conv1d_bwd: null argument block");
   if (int e = check_conv(*args, true, false)) return e;
-  const dim3 grid((unsigned)(args->batch * args->dim), (unsigned)((args->seqlen + CVT * CVE - 1) / (CVT * CVE)));
+  const dim3 grid = conv_grid(*args);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   DISPATCH_T(args->dtype, (conv1d_bwd_kernel<T><<<grid, CVT, 0, st>>>(*args)));
   return launch_status();
@@ -462,11 +557,31 @@ int b200_rmsnorm_fwd(const b200_rmsnorm_args *args, void *stream) {
   return launch_status();
 }
 
+#define NORM_WARP_LAUNCH(R_, NV_)                                                                        \
+  do {                                                                                                  \
+    DISPATCH_T(args->dtype, (rmsnorm_bwd_warp_kernel<T, R_, NV_><<<grid, NWT, 0, st>>>(*args)));         \
+  } while (0)
+#define NORM_WARP_SHAPES(R_)                              \
+  do {                                                    \
+    if (args->cols <= 256) NORM_WARP_LAUNCH(R_, 1);       \
+    else if (args->cols <= 512) NORM_WARP_LAUNCH(R_, 2);  \
+    else if (args->cols <= 768) NORM_WARP_LAUNCH(R_, 3);  \
+    else NORM_WARP_LAUNCH(R_, 4);                         \
+  } while (0)
+
 int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream) {
   B200_REQUIRE(args, B200_ERR_NULL, "rmsnorm_bwd: null argument block");
   if (int e = check_norm(*args, true)) return e;
   constexpr bool is_bwd = true;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (args->cols <= 1024) {
+    // warp per row: two CTAs of 8 warps per SM, fewer when there are fewer rows than warps
+    const int64_t want = (int64_t)sm_count_current() * 2, need = (args->rows + NWT / 32 - 1) / (NWT / 32);
+    const unsigned grid = (unsigned)(need < want ? need : want);
+    if (args->residual_dtype == B200_F32 && args->dtype != B200_F32) NORM_WARP_SHAPES(float);
+    else NORM_WARP_SHAPES(T);
+    return launch_status();
+  }
   if (args->residual_dtype == B200_F32 && args->dtype != B200_F32) NORM_SHAPES(rmsnorm_bwd_kernel, float);
   else NORM_SHAPES(rmsnorm_bwd_kernel, T);
   return launch_status();

@@ -166,6 +166,7 @@ class MambaLMHeadModel(nn.Module):
                 nn.init.kaiming_uniform_(layer.mixer.out_proj.weight, a=math.sqrt(5))
                 layer.mixer.out_proj.weight /= math.sqrt(n_layer)
         self.lm_head.weight = self.backbone.embedding.weight
+        self._decode_graphs = {}
 
     def load_state_dict(self, state_dict, strict=True):
         sd = {k: v for k, v in state_dict.items() if "dtA_proj" not in k}
@@ -185,42 +186,58 @@ class MambaLMHeadModel(nn.Module):
     def allocate_inference_cache(self, batch_size, dtype=None, state_dtype=None):
         return [layer.mixer.allocate_inference_cache(batch_size, dtype, state_dtype) for layer in self.backbone.layers]
 
+    def _decode_graph(self, batch, state_dtype):
+        """The captured decoding step for this batch size: static state buffers, a static token
+        buffer and the graph that advances them by one token.  Built once and kept (the counterpart
+        of lrnnx's CUDAGraphStepCache, lrnnx/utils/generation.py:165-290); ``clear_decode_graphs``
+        drops it, which is needed after the parameters change because the caches hold float32
+        copies of A, D and the step-size bias."""
+        dev = self.lm_head.weight.device
+        key = (batch, state_dtype, dev)
+        entry = self._decode_graphs.get(key)
+        if entry is not None:
+            return entry
+        caches = self.allocate_inference_cache(batch, state_dtype=state_dtype)
+        tok_buf = torch.zeros(batch, dtype=torch.long, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                  # warm-up outside capture; the states it leaves are overwritten by the prefill
+            for _ in range(3):
+                self.step(tok_buf, caches).argmax(dim=-1)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            nxt = self.step(tok_buf, caches).argmax(dim=-1)
+            tok_buf.copy_(nxt)
+        entry = {"caches": caches, "tok": tok_buf, "graph": graph}
+        self._decode_graphs[key] = entry
+        return entry
+
+    def clear_decode_graphs(self):
+        self._decode_graphs.clear()
+
     @torch.no_grad()
     def generate(self, prompt_ids, n_new, use_cuda_graph=True, state_dtype=torch.float32, timings=None):
         """Greedy decoding: prefill ``prompt_ids`` (batch, L) through the scan kernels keeping the
         last states, then ``n_new`` tokens with one decoding step per token, replayed from a
-        captured CUDA graph over static buffers.  Returns the (batch, n_new) generated ids."""
+        captured CUDA graph over static buffers (captured at the first call for a batch size and
+        reused afterwards).  Returns the (batch, n_new) generated ids."""
         batch = prompt_ids.shape[0]
         dev = prompt_ids.device
-        caches = self.allocate_inference_cache(batch, state_dtype=state_dtype)
+        if use_cuda_graph:
+            entry = self._decode_graph(batch, state_dtype)
+            caches = entry["caches"]
+        else:
+            caches = self.allocate_inference_cache(batch, state_dtype=state_dtype)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         ev[0].record()
-        logits = self.forward(prompt_ids, caches, num_last_tokens=1)[:, 0]
+        logits = self.forward(prompt_ids, caches, num_last_tokens=1)[:, 0]      # writes every state of the caches
         token = logits.argmax(dim=-1)
         out = torch.empty(batch, n_new, dtype=torch.long, device=dev)
         out[:, 0] = token
         ev[1].record()
         if use_cuda_graph:
-            # the states of the prefill are the graph's static state buffers; the warm-up steps must
-            # not advance them, so they run on copies that are restored afterwards
-            saved = [{k: v.clone() for k, v in c.items()} for c in caches]
-            tok_buf = token.clone()
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    self.step(tok_buf, caches).argmax(dim=-1)
-            torch.cuda.current_stream().wait_stream(side)
-            for c, s in zip(caches, saved):
-                for k in ("conv_state", "lrnn_state"):
-                    c[k].copy_(s[k])
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                nxt = self.step(tok_buf, caches).argmax(dim=-1)
-                tok_buf.copy_(nxt)
-            for c, s in zip(caches, saved):          # the capture does not run the kernels, but keep the states exact
-                for k in ("conv_state", "lrnn_state"):
-                    c[k].copy_(s[k])
+            tok_buf, graph = entry["tok"], entry["graph"]
             tok_buf.copy_(token)
             for t in range(1, n_new):
                 graph.replay()

@@ -188,6 +188,14 @@ def test_lm_generate_cuda_graph_equals_python_loop():
     a = m.generate(prompt, 24, use_cuda_graph=True)
     b = m.generate(prompt, 24, use_cuda_graph=False)
     assert torch.equal(a, b)
+    # the captured step is kept and reused: a second prompt of another length goes through the same
+    # graph and static state buffers, and a repeat of the first prompt reproduces its tokens
+    assert len(m._decode_graphs) == 1
+    prompt2 = case["input_ids"][:, 3:14].cuda()
+    a2 = m.generate(prompt2, 12, use_cuda_graph=True)
+    assert len(m._decode_graphs) == 1
+    assert torch.equal(a2, m.generate(prompt2, 12, use_cuda_graph=False))
+    assert torch.equal(a, m.generate(prompt, 24, use_cuda_graph=True))
     # and against the oracle's step-by-step decoding on the CPU
     sd = dict(case["state_dict"])
     sd["lm_head.weight"] = sd["backbone.embedding.weight"]
