@@ -255,8 +255,6 @@ class S5Scan:
 
     def step(self, record=False):
         """forward + backward scan kernels through the extension entry points (graph replay)."""
-        if self.flush_buf is not None:
-            self.flush_buf.zero_()
         if self.g_step is not None:
             self.g_step[self._parity].replay()
             self._parity ^= 1
@@ -467,8 +465,6 @@ class S6Scan:
 
     def step(self, record=False):
         t = self.t
-        if self.flush_buf is not None:
-            self.flush_buf.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
@@ -726,7 +722,6 @@ class CauchyKernel:
 
     def step(self, record=False):
         t = self.t
-        self.flush_buf.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
@@ -1018,20 +1013,39 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, n, w, record=False):
+    def timed(fn, n, w, record=False, flush=None):
+        """n steps between two barriers.  Workloads whose operands fit in the L2 get a 256 MB write
+        before every step; the time of a step is then taken between events that bracket the step
+        alone (the flush writes are not part of the workload), and the steps' times are summed."""
         for _ in range(w):
+            if flush is not None:
+                flush.zero_()
             fn()
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn(record=True) if record else fn()
         drain = getattr(wl, "drain", None)
-        if drain is not None:
-            drain()          # the current stream waits for collectives still in flight on NCCL's stream
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
+        if flush is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn(record=True) if record else fn()
+            if drain is not None:
+                drain()          # the current stream waits for collectives still in flight on NCCL's stream
+            e1.record()
+            barrier()
+            ms = e0.elapsed_time(e1)
+        else:
+            pairs = []
+            for i in range(n):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn(record=True) if record else fn()
+                if drain is not None and i == n - 1:
+                    drain()
+                b.record()
+                pairs.append((a, b))
+            barrier()
+            ms = sum(a.elapsed_time(b) for a, b in pairs)
         if world > 1:
             t = torch.tensor([ms], device=dev)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -1041,7 +1055,7 @@ def measure(wl, steps, warmup, world, rank, local, dev, pg, sample_clocks=True):
     sampler = ClockSampler(local) if (rank == 0 and sample_clocks) else None
     if sampler:
         sampler.start()
-    ms_step = timed(wl.step, steps, warmup, record=True)
+    ms_step = timed(wl.step, steps, warmup, record=True, flush=getattr(wl, "flush_buf", None))
     clocks = sampler.stop() if sampler else None
     e2e_steps = max(3, min(steps, 10))
     ms_e2e = timed(wl.e2e_step, e2e_steps, 3)
