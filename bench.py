@@ -123,10 +123,11 @@ class ClockSampler:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
 # profiles/ (same workload, same kernel); None where no capture exists.
 NCU_TRAFFIC = {
-    ("s5_scan_cfg1", "simpscan_fwd_kernel"): 128.8e6,
-    ("s5_scan_cfg1", "simpscan_bwd_kernel"): 304.9e6,
-    ("s6_layer_cfg2", "selscan_fwd"): 222.1e6,
-    ("s6_layer_cfg2", "selscan_bwd"): 382.4e6,
+    ("s5_scan_cfg1", "simpscan_fwd_kernel"): 127.6e6,
+    ("s5_scan_cfg1", "simpscan_bwd_kernel"): 301.5e6,
+    ("s6_layer_cfg2", "selscan_fwd"): 223.4e6,
+    ("s6_layer_cfg2", "selscan_bwd"): 382.2e6,
+    ("cauchy_s4", "cauchy_fwd"): 76.1e6,
 }
 
 

@@ -39,6 +39,26 @@ class RMSNorm(nn.Module):
                            residual_in_fp32=residual_in_fp32)
 
 
+class _InProjFn(torch.autograd.Function):
+    """xz = W hidden^T per batch row, produced directly in the (batch, channel, L) layout the scan
+    kernels read.  A plain bmm would do the forward; its autograd hands the input gradient back as
+    a transposed view, which the norm backward in front of it then has to copy.  Here the input
+    gradient is computed as dxz^T W, i.e. directly in the (batch, L, d_model) layout of ``hidden``."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight):
+        ctx.save_for_backward(hidden, weight)
+        return torch.bmm(weight.unsqueeze(0).expand(hidden.shape[0], -1, -1), hidden.transpose(1, 2))
+
+    @staticmethod
+    def backward(ctx, dxz):
+        hidden, weight = ctx.saved_tensors
+        batch = hidden.shape[0]
+        d_hidden = torch.bmm(dxz.transpose(1, 2), weight.unsqueeze(0).expand(batch, -1, -1))
+        d_weight = torch.bmm(dxz, hidden).sum(0)
+        return d_hidden, d_weight.to(weight.dtype)
+
+
 class Mamba(nn.Module):
     """The S6 mixer with lrnnx's parameter layout (lrnnx/models/ltv/mamba.py:66-177)."""
 
@@ -66,6 +86,8 @@ class Mamba(nn.Module):
 
     def _xz(self, hidden):
         """in_proj straight into the (batch, channel, L) layout: W (2d, d_model) @ hidden^T."""
+        if torch.is_grad_enabled() and (hidden.requires_grad or self.in_proj.weight.requires_grad):
+            return _InProjFn.apply(hidden, self.in_proj.weight)
         batch = hidden.shape[0]
         return torch.bmm(self.in_proj.weight.unsqueeze(0).expand(batch, -1, -1), hidden.transpose(1, 2))
 
