@@ -807,14 +807,14 @@ class LmTrain:
         self.h_ids = torch.randint(0, self.vocab, (self.local_batch, self.L), generator=g).pin_memory()
         self.ids = self.h_ids.to(dev)
         self.ev = []
-        self.launches_per_step = self.n_layer * 8          # conv, scan, norm forward and backward per layer (this package's kernels)
+        self.launches_per_step = self.n_layer * 8 + 2      # conv, scan, norm forward and backward per layer; the loss (this package's kernels)
 
     def _train(self, ids):
+        from lrnnx_b200.ops.cross_entropy import cross_entropy
         logits = self.model(ids)
         # next-token loss: the last position has no target (ignored) instead of slicing the logits, which
         # would copy them
-        loss = torch.nn.functional.cross_entropy(logits.view(-1, self.vocab).float(), self.labels(ids).view(-1),
-                                                 ignore_index=-100)
+        loss = cross_entropy(logits.view(-1, self.vocab), self.labels(ids).view(-1), ignore_index=-100)
         self.opt.zero_grad(set_to_none=True)
         loss.backward()
         self.opt.step()

@@ -430,6 +430,31 @@ typedef struct b200_cgemm_planes_args {
 
 int b200_cgemm_planes(const b200_cgemm_planes_args *args, void *stream);
 
+/* ------------------------------------------------------------------------
+ * Next-token cross-entropy over a wide vocabulary, read straight from the logits in their own
+ * dtype (no float32 copy of the (rows, cols) logits).  lrnnx has no counterpart: its LM returns
+ * logits (lrnnx/architectures/language_model.py:615-727) and its training benchmark sums them
+ * (benchmarks/benchmark_training.py:33-34); this is the loss the LM harness trains with.
+ *   forward : lse[r] = log sum_j exp(logits[r, j]);  loss[r] = lse[r] - logits[r, labels[r]],
+ *             0 for rows whose label equals ignore_index
+ *   backward: dlogits[r, j] = (exp(logits[r, j] - lse[r]) - [j == labels[r]]) * scale[0],
+ *             0 for ignored rows;  scale is a float32 scalar in device memory
+ *             (upstream gradient / number of counted rows)
+ *   logits, dlogits (rows, cols) float32 / float16 / bfloat16, cols contiguous;
+ *   labels int64 (rows); lse, loss float32 (rows).
+ * ------------------------------------------------------------------------ */
+typedef struct b200_xent_args {
+  int64_t rows;
+  int32_t cols, dtype;
+  int64_t ignore_index;
+  const void *logits, *labels, *scale;
+  void *lse, *loss, *dlogits;
+  int64_t logits_rs, dlogits_rs;
+} b200_xent_args;
+
+int b200_xent_fwd(const b200_xent_args *args, void *stream);
+int b200_xent_bwd(const b200_xent_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,7 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_cgemm_args")) return (int)sizeof(b200_cgemm_args);
   if (!strcmp(name, "b200_cgemm_planes_args")) return (int)sizeof(b200_cgemm_planes_args);
   if (!strcmp(name, "b200_cgemm_grad_args")) return (int)sizeof(b200_cgemm_grad_args);
+  if (!strcmp(name, "b200_xent_args")) return (int)sizeof(b200_xent_args);
   return -1;
 }
 

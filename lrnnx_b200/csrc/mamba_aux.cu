@@ -448,6 +448,116 @@ __global__ void __launch_bounds__(NWT) rmsnorm_bwd_warp_kernel(const b200_rmsnor
   for (int c = threadIdx.x; c < H; c += NWT) atomicAdd(reinterpret_cast<float *>(p.dweight) + c, sdw[c]);
 }
 
+// ------------------------------------------------------------------ cross-entropy over a wide row
+// A CTA owns a row.  Forward: one pass, each thread keeps a running (max, sum of exp) over its
+// 8-element vectors, merged across the CTA.  Backward: one pass, exp(x - lse) written back in
+// the logits' dtype.  Rows that are not 16-byte aligned take element accesses.
+constexpr int XT = 512;           // threads per CTA of the cross-entropy kernels
+constexpr float kLog2eF = 1.4426950408889634f, kLn2F = 0.6931471805599453f;
+
+template <typename T>
+__global__ void __launch_bounds__(XT) xent_fwd_kernel(const b200_xent_args p) {
+  __shared__ float red_m[XT / 32], red_s[XT / 32];
+  const int64_t row = blockIdx.x;
+  const T *x = reinterpret_cast<const T *>(p.logits) + row * p.logits_rs;
+  const int V = p.cols;
+  const bool vec = al16(x) && (V % 8 == 0);
+  float m = -INFINITY, sum = 0.f;      // in units of log2: m = max x log2e, sum = sum 2^(x log2e - m)
+  auto take = [&](float v) {
+    const float y = v * kLog2eF;
+    if (y > m) {
+      sum = sum * exp2f(m - y) + 1.f;
+      m = y;
+    } else {
+      sum += exp2f(y - m);
+    }
+  };
+  if (vec) {
+    for (int c = threadIdx.x * 8; c < V; c += XT * 8) {
+      float v[8];
+      ldv<T>(x + c, v);
+      float vm = v[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) vm = fmaxf(vm, v[i]);
+      const float y = vm * kLog2eF;
+      if (y > m) {
+        sum *= exp2f(m - y);
+        m = y;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += exp2f(fmaf(v[i], kLog2eF, -m));
+    }
+  } else {
+    for (int c = threadIdx.x; c < V; c += XT) take(tof(x[c]));
+  }
+  // merge (m, sum) over the warp, then over the CTA
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
+    const float nm = fmaxf(m, om);
+    sum = (m == -INFINITY ? 0.f : sum * exp2f(m - nm)) + (om == -INFINITY ? 0.f : os * exp2f(om - nm));
+    m = nm;
+  }
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  if (lane == 0) { red_m[wp] = m; red_s[wp] = sum; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float M = -INFINITY;
+    for (int i = 0; i < XT / 32; ++i) M = fmaxf(M, red_m[i]);
+    float S = 0.f;
+    for (int i = 0; i < XT / 32; ++i)
+      if (red_m[i] != -INFINITY) S += red_s[i] * exp2f(red_m[i] - M);
+    const float lse = (M + log2f(S)) * kLn2F;
+    const int64_t label = reinterpret_cast<const int64_t *>(p.labels)[row];
+    reinterpret_cast<float *>(p.lse)[row] = lse;
+    float loss = 0.f;
+    if (label != p.ignore_index && label >= 0 && label < V) loss = lse - tof(x[label]);
+    reinterpret_cast<float *>(p.loss)[row] = loss;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(XT) xent_bwd_kernel(const b200_xent_args p) {
+  const int64_t row = blockIdx.x;
+  const T *x = reinterpret_cast<const T *>(p.logits) + row * p.logits_rs;
+  T *dx = reinterpret_cast<T *>(p.dlogits) + row * p.dlogits_rs;
+  const int V = p.cols;
+  const int64_t label = reinterpret_cast<const int64_t *>(p.labels)[row];
+  const bool counted = label != p.ignore_index && label >= 0 && label < V;
+  const float scale = counted ? reinterpret_cast<const float *>(p.scale)[0] : 0.f;
+  const float off = reinterpret_cast<const float *>(p.lse)[row] * kLog2eF;
+  const bool vec = al16(x) && al16(dx) && (V % 8 == 0);
+  if (vec) {
+    for (int c = threadIdx.x * 8; c < V; c += XT * 8) {
+      float v[8];
+      if (counted) {
+        ldv<T>(x + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (exp2f(fmaf(v[i], kLog2eF, -off)) - ((int64_t)(c + i) == label ? 1.f : 0.f)) * scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      stv<T>(dx + c, v);
+    }
+  } else {
+    for (int c = threadIdx.x; c < V; c += XT) {
+      float v = 0.f;
+      if (counted) v = (exp2f(fmaf(tof(x[c]), kLog2eF, -off)) - ((int64_t)c == label ? 1.f : 0.f)) * scale;
+      dx[c] = fromf<T>(v);
+    }
+  }
+}
+
+int check_xent(const b200_xent_args &a, bool bwd) {
+  B200_REQUIRE(a.logits && a.labels && a.lse, B200_ERR_NULL, "xent: logits, labels and lse must be non-null");
+  B200_REQUIRE(a.rows > 0 && a.cols > 0 && a.rows < (int64_t(1) << 31), B200_ERR_SHAPE, "xent: sizes must be positive");
+  B200_REQUIRE(a.dtype == B200_F32 || a.dtype == B200_F16 || a.dtype == B200_BF16, B200_ERR_DTYPE, "xent: unknown dtype");
+  if (!bwd) B200_REQUIRE(a.loss, B200_ERR_NULL, "xent_fwd: loss must be non-null");
+  else B200_REQUIRE(a.dlogits && a.scale, B200_ERR_NULL, "xent_bwd: dlogits and scale must be non-null");
+  return 0;
+}
+
 int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
   B200_REQUIRE(a.x && a.weight && (bwd || a.out), B200_ERR_NULL, "conv1d: x, weight, out must be non-null");
   B200_REQUIRE(a.batch > 0 && a.dim > 0 && (update || a.seqlen > 0), B200_ERR_SHAPE, "conv1d: sizes must be positive");
@@ -584,6 +694,22 @@ int b200_rmsnorm_bwd(const b200_rmsnorm_args *args, void *stream) {
   }
   if (args->residual_dtype == B200_F32 && args->dtype != B200_F32) NORM_SHAPES(rmsnorm_bwd_kernel, float);
   else NORM_SHAPES(rmsnorm_bwd_kernel, T);
+  return launch_status();
+}
+
+int b200_xent_fwd(const b200_xent_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "xent_fwd: null argument block");
+  if (int e = check_xent(*args, false)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DISPATCH_T(args->dtype, (xent_fwd_kernel<T><<<(unsigned)args->rows, XT, 0, st>>>(*args)));
+  return launch_status();
+}
+
+int b200_xent_bwd(const b200_xent_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "xent_bwd: null argument block");
+  if (int e = check_xent(*args, true)) return e;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DISPATCH_T(args->dtype, (xent_bwd_kernel<T><<<(unsigned)args->rows, XT, 0, st>>>(*args)));
   return launch_status();
 }
 

@@ -38,11 +38,15 @@ __device__ int g_simpscan_status = 0;   // set to non-zero when a bounded barrie
 
 namespace {
 
-template <int DM>
-__device__ __forceinline__ void s5_coef(cf A, float d, float dA, cf &a, cf &k) {
+// Coefficients of one step: a (state transition) and k (input gain).  SAME: the transition uses
+// the input's step size (no separate deltaA), so zero-order hold needs one complex exponential
+// per step, not two.  invA = 1 / A is formed once per (row, state).
+template <int DM, bool SAME>
+__device__ __forceinline__ void s5_coef(cf A, cf invA, float d, float dA, cf &a, cf &k) {
   if constexpr (DM == B200_DISC_ZOH) {
     a = cexp(A * dA);
-    k = (cexp(A * d) - cf(1.f, 0.f)) / A;
+    const cf E = SAME ? a : cexp(A * d);
+    k = (E - cf(1.f, 0.f)) * invA;
   } else if constexpr (DM == B200_DISC_BILINEAR) {
     const cf vA = A * (0.5f * dA);
     a = (cf(1.f, 0.f) + vA) / (cf(1.f, 0.f) - vA);
@@ -243,11 +247,12 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
     same_step = __all_sync(0xffffffffu, same_step);
     for (int si = 0; si < S; ++si) {
       const cf An = S1 ? A0 : Ap[(int64_t)si * p.A_ns];
+      const cf invAn = cf(1.f, 0.f) / An;
       const cf BC = S1 ? BC0 : Bp[(int64_t)si * p.B_ns] * Cp[(int64_t)si * p.C_ns];
       cf a[FI], h[FI];
       if (same_step) {
         cf a0, k0;
-        s5_coef<DM>(An, dl[0], dAv[0], a0, k0);
+        s5_coef<DM, !HAS_DA>(An, invAn, dl[0], dAv[0], a0, k0);
 #pragma unroll
         for (int i = 0; i < FI; ++i) {
           a[i] = a0;
@@ -261,7 +266,7 @@ __global__ void __launch_bounds__(FWARPS * 32, 7) simpscan_fwd_kernel(const b200
             h[i] = u[i];
           } else {
             cf kk;
-            s5_coef<DM>(An, dl[i], dAv[i], a[i], kk);
+            s5_coef<DM, !HAS_DA>(An, invAn, dl[i], dAv[i], a[i], kk);
             h[i] = kk * u[i];
           }
         }
@@ -589,6 +594,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
       const int par = iter & 1;
       ++iter;
       const cf An = S1 ? A0 : Ap[(int64_t)si * p.A_ns];
+      const cf invAn = cf(1.f, 0.f) / An;
       const cf Cc = conj(S1 ? C0 : Cp[(int64_t)si * p.C_ns]);
       // checkpoint of the previous chunk: issued early so the load overlaps the local scans
       cf hpre = cf(0.f, 0.f);
@@ -597,7 +603,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
       cf a[BI], kk[kUnitK ? 1 : BI], h[BI];
       if (same_step) {   // time-invariant step size: one coefficient evaluation for the thread
         cf a0, k0;
-        s5_coef<DM>(An, dl[0], dAv[0], a0, k0);
+        s5_coef<DM, !HAS_DA>(An, invAn, dl[0], dAv[0], a0, k0);
 #pragma unroll
         for (int i = 0; i < BI; ++i) {
           a[i] = a0;
@@ -607,7 +613,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
 #pragma unroll
         for (int i = 0; i < BI; ++i) {
           if constexpr (kUnitK) a[i] = cexp(An * dAv[i]);
-          else s5_coef<DM>(An, dl[i], dAv[i], a[i], kk[i]);
+          else s5_coef<DM, !HAS_DA>(An, invAn, dl[i], dAv[i], a[i], kk[i]);
         }
       }
       auto beta = [&](int i) { return kUnitK ? u[i] : kk[kUnitK ? 0 : i] * u[i]; };
@@ -676,10 +682,10 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
         if (NEED_BC) dC_l = dC_l + dy[i] * conj(h[i]);
         float d_dl = 0.f, d_dA = 0.f;
         if constexpr (DM == B200_DISC_ZOH) {
-          const cf E = cexp(An * dv);
+          const cf E = HAS_DA ? kk[kUnitK ? 0 : i] * An + cf(1.f, 0.f) : a[i];   // exp(A dv) = 1 + k A
           d_dA = (t * conj(An)).re;
           d_dl = (G * conj(E * u[i])).re;
-          dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / An));
+          dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) * invAn));
         } else if constexpr (DM == B200_DISC_BILINEAR) {
           const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dv));
           const cf rA = cf(1.f, 0.f) / (cf(1.f, 0.f) - An * (0.5f * dav));
@@ -935,7 +941,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
   bool stores_pending = false;
   RowPtrs rp = row_ptrs(blockIdx.x);
   int64_t row = blockIdx.x;
-  cf A0, Cc, inv_bc;
+  cf A0, invA0, Cc, inv_bc;
   bool c_one = false, bc_one = false;
   cf dA_acc, dB_acc, dC_acc;
   int j = -1;
@@ -947,6 +953,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
       rp = row_ptrs(row);
       const int d = (int)(row % p.dim);
       A0 = reinterpret_cast<const cf *>(p.A)[(int64_t)d * p.A_ds];
+      invA0 = cf(1.f, 0.f) / A0;
       const cf B0 = reinterpret_cast<const cf *>(p.B)[(int64_t)d * p.B_ds];
       const cf C0 = reinterpret_cast<const cf *>(p.C)[(int64_t)d * p.C_ds];
       const cf bc = B0 * C0;
@@ -1046,7 +1053,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
     cf a[BI], kk[kUnitK ? 1 : BI];
     if (same_step) {
       cf a0, k0;
-      s5_coef<DM>(A0, dl[0], dAv[0], a0, k0);
+      s5_coef<DM, !HAS_DA>(A0, invA0, dl[0], dAv[0], a0, k0);
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
         a[i] = a0;
@@ -1056,7 +1063,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
         if constexpr (kUnitK) a[i] = cexp(A0 * dAv[i]);
-        else s5_coef<DM>(A0, dl[i], dAv[i], a[i], kk[i]);
+        else s5_coef<DM, !HAS_DA>(A0, invA0, dl[i], dAv[i], a[i], kk[i]);
       }
     }
     auto beta = [&](int i) { return kUnitK ? u[i] : kk[kUnitK ? 0 : i] * u[i]; };
@@ -1104,10 +1111,10 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
       if (NEED_BC) dC_l = dC_l + dy[i] * conj(h[i]);
       float d_dl = 0.f, d_dA = 0.f;
       if constexpr (DM == B200_DISC_ZOH) {
-        const cf E = cexp(A0 * dv);
+        const cf E = HAS_DA ? kk[kUnitK ? 0 : i] * A0 + cf(1.f, 0.f) : a[i];   // exp(A dv) = 1 + k A
         d_dA = (t * conj(A0)).re;
         d_dl = (G * conj(E * u[i])).re;
-        dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) / A0));
+        dA_l = dA_l + t * dav + G * conj(u[i] * ((E * dv - kk[kUnitK ? 0 : i]) * invA0));
       } else if constexpr (DM == B200_DISC_BILINEAR) {
         const cf hprev = (i == 0) ? hprev0 : h[i == 0 ? 0 : i - 1];
         const cf r = cf(1.f, 0.f) / (cf(1.f, 0.f) - A0 * (0.5f * dv));

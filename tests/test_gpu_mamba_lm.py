@@ -264,3 +264,43 @@ def test_reference_layers_run_on_the_drop_in_modules():
         a = generate(layer, x0, 32, graph_cache=graph_cache)
         b = generate(layer, x0, 32)
         assert_close(a.cpu(), b.cpu(), rtol=6e-4, atol_scale=2e-3, name="capture_graph / generate vs loop")
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(37, 50280), (64, 1000), (5, 131), (3, 8)])
+def test_cross_entropy_matches_torch(dtype, rows, cols):
+    """The fused loss against F.cross_entropy on a float32 copy of the same logits: value and
+    gradient, with ignored rows, aligned and unaligned row lengths."""
+    from lrnnx_b200.ops.cross_entropy import cross_entropy
+    g = torch.Generator().manual_seed(rows * 1000 + cols)
+    logits = (torch.randn(rows, cols, generator=g) * 3).to(dtype).cuda().requires_grad_(True)
+    labels = torch.randint(0, cols, (rows,), generator=g)
+    labels[::4] = -100
+    labels = labels.cuda()
+    loss = cross_entropy(logits, labels, ignore_index=-100)
+    (loss * 1.7).backward()
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-100)
+    (ref * 1.7).backward()
+    assert abs(loss.item() - ref.item()) <= 2e-5 * max(1.0, abs(ref.item()))
+    tol = 1e-6 if dtype == torch.float32 else 4e-3
+    err = (logits.grad.float() - ref_in.grad).abs().max().item()
+    assert err <= tol * ref_in.grad.abs().max().item() + 1e-9, (err, ref_in.grad.abs().max().item())
+    assert logits.grad.dtype == dtype
+    assert torch.count_nonzero(logits.grad[::4]).item() == 0
+
+
+def test_cross_entropy_strided_rows_and_all_ignored():
+    from lrnnx_b200.ops.cross_entropy import cross_entropy
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(12, 520, generator=g).cuda()
+    logits = big[:, 3:515].detach().requires_grad_(True)          # rows start 12 bytes off a 16-byte boundary
+    labels = torch.randint(0, 512, (12,), generator=g).cuda()
+    loss = cross_entropy(logits, labels)
+    loss.backward()
+    ref_in = logits.detach().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) <= 2e-5 * abs(ref.item())
+    assert (logits.grad - ref_in.grad).abs().max().item() <= 1e-6 * ref_in.grad.abs().max().item() + 1e-9
+    none = cross_entropy(logits.detach(), torch.full((12,), -100).cuda())
+    assert none.item() == 0.0
