@@ -144,6 +144,12 @@ typedef struct b200_selscan_bwd_args {
   int64_t dA_ds, dA_ns;
   int64_t dB_bs, dB_gs, dB_ns;
   int64_t dC_bs, dC_gs, dC_ns;
+  /* Sequence-parallel backward (both optional, float32 (batch, dim, dstate), real A only; no
+   * counterpart in lrnnx).  h_in: the state entering the first step (instead of zero), with f.x
+   * holding the checkpoints corrected for it (b200_selscan_fixup does that).  q_in: the gradient
+   * of the loss with respect to the state after the last step, i.e. what later slices of the
+   * sequence send back (b200_selscan_adjoint_summary, folded from the right). */
+  const void *h_in, *q_in;
 } b200_selscan_bwd_args;
 
 int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream);
@@ -176,6 +182,24 @@ int b200_selscan_fixup(const b200_selscan_fixup_args *args, void *stream);
  * Writes h_in and p_in (same layout as above; the pointers are outputs here); uses f.x, f.batch,
  * f.dim, f.dstate, f.seqlen, n_segments and seg_len only. */
 int b200_selscan_fold(const b200_selscan_fixup_args *args, void *stream);
+
+/* Adjoint summary of a slice for the sequence-parallel backward: what the slice hands to the
+ * slice before it when nothing arrives from the slices after it,
+ *   G[b,d,n] = sum_t (prod_{k<=t} a_k[n]) * C[t,n] * dy[b,d,t],   dy = dout (* silu(z) when z is given),
+ * a_k = exp(delta'_k A_n) with delta' = delta after bias and softplus (the transposed map of
+ * b200_selscan_fixup; same restrictions: real A, variable C, "mamba" / "zoh" / "dirac" without
+ * deltaA).  With P = the product of a over the whole slice (the forward's last checkpoint entry
+ * before the fix-up) the gradient arriving at the end of slice r-1 is q[r-1] = G[r] + P[r] q[r].
+ * Uses f.delta, f.delta_bias, f.delta_softplus, f.A, f.C, f.z and their strides; dout
+ * (batch, dim, seqlen) activations dtype with the strides given; G float32 (batch, dim, dstate). */
+typedef struct b200_selscan_adjsum_args {
+  b200_selscan_fwd_args f;
+  const void *dout;
+  void *G;
+  int64_t dout_bs, dout_ds;
+} b200_selscan_adjsum_args;
+
+int b200_selscan_adjoint_summary(const b200_selscan_adjsum_args *args, void *stream);
 
 /* ------------------------------------------------------------------------
  * Simplified (diagonal, complex-input) scan used by LTV-S5.

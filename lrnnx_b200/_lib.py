@@ -22,6 +22,7 @@ ENTRY_POINTS = (
     "b200_last_error", "b200_abi_version", "b200_sizeof", "b200_device_status", "b200_s4_bwd_scratch_bytes",
     "b200_selscan_stage_states",
     "b200_selscan_fwd", "b200_selscan_bwd", "b200_selscan_fixup", "b200_selscan_fold",
+    "b200_selscan_adjoint_summary",
     "b200_simpscan_fwd", "b200_simpscan_bwd",
     "b200_ssu_step", "b200_s5_step",
     "b200_cauchy_fwd", "b200_cauchy_bwd", "b200_cauchy_bwd_static", "b200_vand_fwd", "b200_vand_bwd",

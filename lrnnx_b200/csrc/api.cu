@@ -42,7 +42,7 @@ using namespace b200;
 extern "C" {
 
 const char *b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 4; }
+int b200_abi_version(void) { return 5; }
 
 // size of an argument block as this library was compiled; lets a binding
 // verify its own struct layout before the first call
@@ -51,6 +51,7 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_selscan_fwd_args")) return (int)sizeof(b200_selscan_fwd_args);
   if (!strcmp(name, "b200_selscan_bwd_args")) return (int)sizeof(b200_selscan_bwd_args);
   if (!strcmp(name, "b200_selscan_fixup_args")) return (int)sizeof(b200_selscan_fixup_args);
+  if (!strcmp(name, "b200_selscan_adjsum_args")) return (int)sizeof(b200_selscan_adjsum_args);
   if (!strcmp(name, "b200_simpscan_args")) return (int)sizeof(b200_simpscan_args);
   if (!strcmp(name, "b200_ssu_args")) return (int)sizeof(b200_ssu_args);
   if (!strcmp(name, "b200_s4_args")) return (int)sizeof(b200_s4_args);
@@ -109,6 +110,10 @@ int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream) {
   B200_REQUIRE(!f.delta_bias || args->ddelta_bias, B200_ERR_NULL,
                "selscan_bwd: ddelta_bias is required when delta_bias is given");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (args->h_in || args->q_in) {      // a slice of a sequence-parallel backward: the coverage kernel takes both
+    B200_REQUIRE(!f.is_complex, B200_ERR_UNSUPPORTED, "selscan_bwd: h_in / q_in need a real A");
+    return selscan_bwd_generic(*args, st);
+  }
   if (selscan_bwd_sl_supported(*args)) return selscan_bwd_sl(*args, st);
   if (selscan_bwd_fast_supported(*args)) {
     b200_selscan_bwd_args a = *args;

@@ -318,7 +318,13 @@ __global__ void __launch_bounds__(GWARPS * 32) selscan_bwd_generic_kernel(const 
   const bool constB = !p.var_B;
   const bool has_dA_in = p.deltaA != nullptr;
 
-  for (int n = lane; n < N; n += 32) { accA[n] = V(0.f); accBC[n] = V(0.f); gcar[n] = V(0.f); anext[n] = V(1.f); }
+  // gcar = adjoint arriving from beyond the last step (zero, or q_in of a sequence-parallel slice)
+  for (int n = lane; n < N; n += 32) {
+    accA[n] = V(0.f);
+    accBC[n] = V(0.f);
+    gcar[n] = q.q_in ? V(reinterpret_cast<const float *>(q.q_in)[row * N + n]) : V(0.f);
+    anext[n] = V(1.f);
+  }
   __syncwarp();
   float dD_acc = 0.f, dbias_acc = 0.f;
 
@@ -327,7 +333,9 @@ __global__ void __launch_bounds__(GWARPS * 32) selscan_bwd_generic_kernel(const 
     const int clen = min(kChunk, L - cbase);
     const int nst = (clen + GSTAGE - 1) / GSTAGE;
     // ---- sweep 1: states at the stage boundaries of this chunk
-    for (int n = lane; n < N; n += 32) hb[n * STAGES_PER_CHUNK] = (c > 0) ? xrow[(int64_t)(c - 1) * 2 * N + 2 * n + 1] : V(0.f);
+    for (int n = lane; n < N; n += 32)
+      hb[n * STAGES_PER_CHUNK] = (c > 0) ? xrow[(int64_t)(c - 1) * 2 * N + 2 * n + 1]
+                                         : (q.h_in ? V(reinterpret_cast<const float *>(q.h_in)[row * N + n]) : V(0.f));
     __syncwarp();
     for (int s = 0; s + 1 < nst; ++s) {
       const int t0 = cbase + s * GSTAGE;
@@ -496,7 +504,9 @@ __global__ void __launch_bounds__(GWARPS * 32) selscan_bwd_generic_kernel(const 
         V dBv[GI], dCv[GI];
 #pragma unroll
         for (int i = 0; i < GI; ++i) {
-          const V G = gl[i];
+          // past the end of the row the adjoint only passes through (it is q_in there, not zero, for a
+          // sequence-parallel slice): those positions contribute to no gradient
+          const V G = (t0 + lane * GI + i < L) ? gl[i] : V(0.f);
           const V hprev = (i == 0) ? hin : h[i - 1];
           const V beta = vmul(kk[i], u[i]) * Bv[i];
           const float dv = dl[i], dav = dAv[i], uv = u[i];

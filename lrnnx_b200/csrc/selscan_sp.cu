@@ -342,6 +342,75 @@ bool fixup_vec_ok(const b200_selscan_fixup_args &q) {
   return true;
 }
 
+// Adjoint summary of a slice (the transposed map of the fix-up): G[n] = sum_t exp(A_n cum_t) C[t, n] dy_t
+// with dy = dout * silu(z).  One warp per (batch, channel) row, one timestep per lane; per 32-step
+// block the running sum of delta is a warp scan plus the carried total, every state's terms are
+// summed over the lanes, and the row stops once its slowest-decaying state has fallen below 2^-40
+// of its entry value (delta' >= 0 and A < 0 make the weights non-increasing; rows where that does
+// not hold run to the end).
+__global__ void __launch_bounds__(SPW * 32) selscan_adjsum_kernel(const b200_selscan_adjsum_args q) {
+  const b200_selscan_fwd_args &p = q.f;
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * SPW + warp;
+  if (row >= (int64_t)p.batch * p.dim) return;
+  const int b = (int)(row / p.dim), d = (int)(row % p.dim);
+  const int g = d / (p.dim / p.n_groups);
+  const int N = p.dstate, dt = p.dtype, L = p.seqlen;
+  float *A2 = sm + warp * 2 * N;
+  float *acc = A2 + N;
+  const float *A = reinterpret_cast<const float *>(p.A) + (int64_t)d * p.A_ds;
+  float amax = -INFINITY;
+  for (int n = lane; n < N; n += 32) {
+    const float a = A[(int64_t)n * p.A_ns] * kLog2e;
+    A2[n] = a;
+    acc[n] = 0.f;
+    amax = fmaxf(amax, a);
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  __syncwarp();
+  const bool may_stop = p.delta_softplus && amax < 0.f;      // weights cannot grow again
+  const int64_t dl_off = (int64_t)b * p.delta_bs + (int64_t)d * p.delta_ds;
+  const int64_t z_off = (int64_t)b * p.z_bs + (int64_t)d * p.z_ds;
+  const int64_t do_off = (int64_t)b * q.dout_bs + (int64_t)d * q.dout_ds;
+  const int64_t c_off = (int64_t)b * p.C_bs + (int64_t)g * p.C_gs;
+  const float bias = p.delta_bias ? reinterpret_cast<const float *>(p.delta_bias)[d] : 0.f;
+  float carry = 0.f;
+  for (int t0 = 0; t0 < L; t0 += 32) {
+    if (may_stop && amax * carry < -40.f) break;
+    const int t = t0 + lane;
+    float dv = 0.f, dy = 0.f;
+    if (t < L) {
+      dv = ld_act(p.delta, dt, dl_off + t) + bias;
+      if (p.delta_softplus) dv = softplus20(dv);
+      dy = ld_act(q.dout, dt, do_off + t);
+      if (p.z) {
+        const float zv = ld_act(p.z, dt, z_off + t);
+        dy *= zv * sigmoidf_(zv);
+      }
+    }
+    float cum = dv;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, cum, off);
+      if (lane >= off) cum += v;
+    }
+    cum += carry;
+    carry = __shfl_sync(0xffffffffu, cum, 31);
+    for (int n = 0; n < N; ++n) {
+      const float cv = t < L ? ld_act(p.C, dt, c_off + (int64_t)n * p.C_ns + t) : 0.f;
+      float term = cv * exp2f(A2[n] * cum) * dy;
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) term += __shfl_xor_sync(0xffffffffu, term, m);
+      if (lane == 0) acc[n] += term;
+    }
+  }
+  __syncwarp();
+  float *G = reinterpret_cast<float *>(q.G) + row * N;
+  for (int n = lane; n < N; n += 32) G[n] = acc[n];
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -391,5 +460,24 @@ extern "C" int b200_selscan_fold(const b200_selscan_fixup_args *args, void *stre
       reinterpret_cast<const float *>(a.x), reinterpret_cast<float *>(const_cast<void *>(args->h_in)),
       reinterpret_cast<float *>(const_cast<void *>(args->p_in)), rows, a.dstate, n_chunks, args->seg_len / kChunk,
       args->n_segments);
+  return launch_status();
+}
+
+extern "C" int b200_selscan_adjoint_summary(const b200_selscan_adjsum_args *args, void *stream) {
+  B200_REQUIRE(args, B200_ERR_NULL, "selscan_adjoint_summary: null argument block");
+  const b200_selscan_fwd_args &a = args->f;
+  B200_REQUIRE(a.delta && a.A && a.C && args->dout && args->G, B200_ERR_NULL,
+               "selscan_adjoint_summary: delta, A, C, dout, G must be non-null");
+  B200_REQUIRE(a.batch > 0 && a.dim > 0 && a.seqlen > 0 && a.dstate > 0 && a.dstate <= kMaxDState && a.n_groups >= 1 &&
+                   a.dim % a.n_groups == 0,
+               B200_ERR_SHAPE, "selscan_adjoint_summary: bad sizes");
+  B200_REQUIRE(!a.is_complex && a.var_C && !a.deltaA &&
+                   (a.method == B200_DISC_MAMBA || a.method == B200_DISC_ZOH || a.method == B200_DISC_DIRAC),
+               B200_ERR_UNSUPPORTED,
+               "selscan_adjoint_summary supports real A, variable C, no deltaA and the mamba / zoh / dirac transitions");
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const size_t smem = (size_t)SPW * 2 * a.dstate * sizeof(float);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  selscan_adjsum_kernel<<<(unsigned)((rows + SPW - 1) / SPW), SPW * 32, smem, st>>>(*args);
   return launch_status();
 }

@@ -255,9 +255,13 @@ def fwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, delta_softplus, discret
 
 
 def bwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, dout, x_, out_, dz_, delta_softplus, recompute_out_z,
-        discretization_method_str):
+        discretization_method_str, h_in=None, q_in=None):
     """Returns ``[du, ddelta, dA, dB, dC, dD, ddelta_bias, (ddeltaA), (dz), (out_z)]``
-    (selective_scan_cpu.cpp:627-631); dD / ddelta_bias are None when D / delta_bias are."""
+    (selective_scan_cpu.cpp:627-631); dD / ddelta_bias are None when D / delta_bias are.
+    Two additions to the reference signature, for a slice of a sequence-parallel scan (real A):
+    ``h_in`` (batch, dim, dstate) float32, the state entering the first step, with ``x_`` holding
+    the checkpoints corrected for it; ``q_in``, same shape, the gradient with respect to the state
+    after the last step."""
     f, (batch, dim, seqlen, dstate, n_groups, is_complex, var_B, var_C) = _common(
         u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, discretization_method_str)
     _check(dout.dtype == u.dtype, "dout must have the dtype of u")
@@ -312,6 +316,19 @@ def bwd(u, delta, A, B, C, D_, z_, delta_bias_, deltaA_, dout, x_, out_, dz_, de
         q.ddeltaA, q.dz = _ptr(ddeltaA), _ptr(dz)
         q.dA, q.dB, q.dC = dA.data_ptr(), dB.data_ptr(), dC.data_ptr()
         q.dD, q.ddelta_bias = _ptr(dD), _ptr(ddelta_bias)
+        if h_in is not None or q_in is not None:
+            _check(not is_complex, "h_in / q_in need a real A")
+            keep = []
+            for name, t in (("h_in", h_in), ("q_in", q_in)):
+                if t is None:
+                    continue
+                _check(t.is_cuda and tuple(t.shape) == (batch, dim, dstate), f"{name} must be a CUDA tensor (batch, dim, dstate)")
+                t = t.to(torch.float32).contiguous()
+                keep.append(t)
+                setattr(q, name, t.data_ptr())
+            if h_in is not None:
+                f.stage_h, f.stage_len = None, 0      # stage states of a zero-start forward do not apply
+                q.f = f
         q.dout_bs, q.dout_ds = dout.stride(0), dout.stride(1)
         q.du_bs, q.du_ds = du.stride(0), du.stride(1)
         q.ddelta_bs, q.ddelta_ds = ddelta.stride(0), ddelta.stride(1)

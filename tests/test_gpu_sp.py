@@ -1,7 +1,9 @@
 """Sequence-parallel fix-up kernel on one GPU: the sequence is cut into R slices that are scanned
 one after the other as R emulated ranks (zero-start forward, summary fold on the device,
 b200_selscan_fixup), and the stitched output, gated output, checkpoints and last state must
-equal the unsplit forward of the same library and the CPU oracle."""
+equal the unsplit forward of the same library and the CPU oracle.  The backward is emulated the
+same way from the right (adjoint summaries, fold_suffix, b200_selscan_bwd with h_in / q_in) and
+must reproduce the gradients of the unsplit backward."""
 from __future__ import annotations
 
 import pytest
@@ -50,3 +52,79 @@ def test_sp_slices_match_unsplit(R, L, dtype, rtol, atol):
                  name="last state vs unsplit")
     ref = O.selective_scan_oracle(**t, delta_softplus=True)
     assert_close(outz_sp.float().cpu(), ref.float(), rtol=rtol, atol_scale=atol, name="out_z vs oracle")
+
+
+@pytest.mark.parametrize("dtype,rtol,atol", [(torch.float32, 3e-4, 1e-4), (torch.bfloat16, 3e-2, 1e-2)])
+@pytest.mark.parametrize("R,L", [(2, 512), (4, 8192), (3, 4104)])
+def test_sp_backward_slices_match_unsplit(R, L, dtype, rtol, atol):
+    from lrnnx_b200 import selective_scan_cuda
+    from lrnnx_b200.sp import adjoint_summary, apply_fixup, fold_prefix, fold_suffix
+    g = torch.Generator().manual_seed(L + 7 * R)
+    b, d, n = 2, 32, 16
+    t = dict(u=torch.randn(b, d, L, generator=g).to(dtype), delta=(torch.randn(b, d, L, generator=g) - 2.0).to(dtype),
+             A=-torch.rand(d, n, generator=g) * 0.5 - 0.01, B=torch.randn(b, 1, n, L, generator=g).to(dtype),
+             C=torch.randn(b, 1, n, L, generator=g).to(dtype), D=torch.randn(d, generator=g),
+             z=torch.randn(b, d, L, generator=g).to(dtype), delta_bias=torch.rand(d, generator=g) - 3.0)
+    cu = {k: v.cuda() for k, v in t.items()}
+    gout = torch.randn(b, d, L, generator=g).to(dtype).cuda()
+    out, x, _ = selective_scan_cuda.fwd(cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], cu["z"],
+                                        cu["delta_bias"], None, True, "mamba")
+    ref = selective_scan_cuda.bwd(cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], cu["z"], cu["delta_bias"],
+                                  None, gout, x, out, None, True, False, "mamba")
+    bounds = [(r * L // R) // 8 * 8 for r in range(R)] + [L]
+    slices, ctxs, Ps, hs = [], [], [], []
+    for r in range(R):                                   # forward, left to right
+        lo, hi = bounds[r], bounds[r + 1]
+        sl = {k: (v[..., lo:hi].contiguous() if v.dim() >= 3 else v) for k, v in cu.items()}
+        o, xs, oz = selective_scan_cuda.fwd(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"],
+                                            sl["delta_bias"], None, True, "mamba")
+        Ps.append(xs[:, :, -1, 0::2].clone())
+        hs.append(xs[:, :, -1, 1::2].clone())
+        h_in = None
+        if r > 0:
+            p_in, h_in = fold_prefix(torch.stack(Ps), torch.stack(hs), r)
+            apply_fixup(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"], sl["delta_bias"], True,
+                        o, xs, oz, p_in, h_in)
+        slices.append(sl)
+        ctxs.append((o, xs, h_in))
+    Gs = [adjoint_summary(sl["delta"], sl["A"], sl["C"], sl["z"], sl["delta_bias"], True,
+                          gout[..., bounds[r]:bounds[r + 1]].contiguous()) for r, sl in enumerate(slices)]
+    P_all, G_all = torch.stack(Ps).float(), torch.stack(Gs)
+    parts = []
+    for r in range(R):                                   # every slice's backward is independent of the others now
+        sl, (o, xs, h_in) = slices[r], ctxs[r]
+        q_in = fold_suffix(P_all, G_all, r) if r < R - 1 else None
+        parts.append(selective_scan_cuda.bwd(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"],
+                                             sl["delta_bias"], None, gout[..., bounds[r]:bounds[r + 1]].contiguous(), xs, o,
+                                             None, True, False, "mamba", h_in=h_in, q_in=q_in))
+    names = ["du", "ddelta", "dA", "dB", "dC", "dD", "ddelta_bias", "dz"]
+    for i, name in enumerate(names):
+        if name in ("dA", "dD", "ddelta_bias"):
+            got = sum(p[i].float() for p in parts)
+            tol_r, tol_a = (3e-4, 1e-4) if dtype == torch.float32 else (3e-2, 2e-2)
+        else:
+            got = torch.cat([p[i].float() for p in parts], dim=-1)
+            tol_r, tol_a = rtol, atol
+        assert_close(got.cpu(), ref[i].float().cpu(), rtol=tol_r, atol_scale=tol_a, name=f"{name} vs unsplit backward")
+
+
+def test_adjoint_summary_is_the_transpose_of_the_fixup():
+    """<fixup(h), dy> = <h, adjoint_summary(dy)> for random h and dy (both maps are linear)."""
+    from lrnnx_b200 import selective_scan_cuda
+    from lrnnx_b200.sp import adjoint_summary, apply_fixup
+    g = torch.Generator().manual_seed(91)
+    b, d, n, L = 2, 16, 16, 777
+    mk = lambda *s: torch.randn(*s, generator=g).cuda()
+    u, delta = mk(b, d, L), mk(b, d, L) - 2.0
+    A = (-torch.rand(d, n, generator=g) * 0.5 - 0.01).cuda()
+    B, C = mk(b, 1, n, L), mk(b, 1, n, L)
+    bias = (torch.rand(d, generator=g) - 3.0).cuda()
+    out, x = selective_scan_cuda.fwd(u, delta, A, B, C, None, None, bias, None, True, "mamba")
+    h = mk(b, d, n)
+    dy = mk(b, d, L)
+    out2, x2 = out.clone(), x.clone()
+    apply_fixup(u, delta, A, B, C, None, None, bias, True, out2, x2, None, torch.ones_like(h), h)
+    lhs = ((out2 - out).double() * dy.double()).sum().item()
+    G = adjoint_summary(delta, A, C, None, bias, True, dy)
+    rhs = (h.double() * G.double()).sum().item()
+    assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0), (lhs, rhs)

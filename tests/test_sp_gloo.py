@@ -1,7 +1,10 @@
 """Sequence-parallel exchange logic on CPU ranks (gloo, world size 2 and 3): every rank scans
 its slice from a zero state with the CPU oracle, the ranks all-gather their (product, state)
 summaries through lrnnx_b200.sp.exchange_summaries, fold them with fold_prefix, apply the
-fix-up formula, and the stitched result must equal the unsplit oracle scan."""
+fix-up formula, and the stitched result must equal the unsplit oracle scan.  The backward runs the
+mirrored exchange: adjoint summaries all-gathered, folded from the right with fold_suffix, the
+slice's gradients taken with the folded gradient applied to its final state; the stitched input
+gradients and the all-reduced parameter gradients must equal autograd through the unsplit scan."""
 from __future__ import annotations
 
 import os
@@ -85,3 +88,89 @@ def test_fold_prefix_identity_for_rank0():
     p2, h2 = fold_prefix(P, h, 2)
     torch.testing.assert_close(p2, P[0] * P[1])
     torch.testing.assert_close(h2, P[1] * h[0] + h[1])
+
+
+def _slice_scan(u, delta, A, B, C, D, z, bias, h0):
+    """Differentiable scan of a slice from the state h0 (plain loop; "mamba" discretization)."""
+    import torch.nn.functional as F
+    dl = F.softplus(delta + bias[:, None])
+    h = h0
+    ys = []
+    for t in range(u.shape[-1]):
+        a = torch.exp(dl[:, :, t, None] * A)
+        h = a * h + dl[:, :, t, None] * B[:, 0, :, t][:, None, :] * u[:, :, t, None]
+        ys.append((h * C[:, 0, :, t][:, None, :]).sum(-1) + D * u[:, :, t])
+    return torch.stack(ys, dim=-1) * F.silu(z), h, torch.exp(dl.sum(-1, keepdim=True) * A)
+
+
+def _bwd_worker(rank, world, port, L, q):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lrnnx_b200.sp import exchange_summaries, fold_prefix, fold_suffix
+        t = _inputs(L)
+        gout = torch.randn(t["u"].shape, generator=torch.Generator().manual_seed(17))
+        lo, hi = rank * L // world, (rank + 1) * L // world
+        names = ("u", "delta", "B", "C", "z")
+        sl = {k: t[k][..., lo:hi].clone().requires_grad_(True) for k in names}
+        par = {k: t[k].clone().requires_grad_(True) for k in ("A", "D", "delta_bias")}
+        zero = torch.zeros(t["u"].shape[0], t["u"].shape[1], t["A"].shape[1])
+        # forward exchange: zero-start summary of the slice, folded from the left
+        with torch.no_grad():
+            _, h_loc, P_loc = _slice_scan(sl["u"], sl["delta"], par["A"], sl["B"], sl["C"], par["D"], sl["z"],
+                                          par["delta_bias"], zero)
+        P_all, h_all = exchange_summaries(P_loc.contiguous(), h_loc.contiguous())
+        _, h_in = fold_prefix(P_all, h_all, rank)
+        # backward exchange: the slice's own adjoint summary is the gradient at its entering state
+        h0 = h_in.clone().requires_grad_(True)
+        y, h_last, _ = _slice_scan(sl["u"], sl["delta"], par["A"], sl["B"], sl["C"], par["D"], sl["z"],
+                                   par["delta_bias"], h0)
+        (G,) = torch.autograd.grad((y * gout[..., lo:hi]).sum(), h0, retain_graph=True)
+        P_all, G_all = exchange_summaries(P_loc.contiguous(), G.contiguous())
+        q_in = fold_suffix(P_all, G_all, rank)
+        ((y * gout[..., lo:hi]).sum() + (h_last * q_in).sum()).backward()
+        pg = torch.cat([par[k].grad.reshape(-1) for k in ("A", "D", "delta_bias")])
+        dist.all_reduce(pg)
+        q.put((rank, {k: sl[k].grad for k in names}, pg))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,L", [(2, 48), (3, 75)])
+def test_sp_backward_fold_matches_unsplit_autograd(world, L):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29100 + (os.getpid() % 500) + world
+    procs = [ctx.Process(target=_bwd_worker, args=(r, world, port, L, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict()
+    for _ in range(world):
+        r, grads, pg = q.get(timeout=180)
+        results[r] = (grads, pg)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    t = _inputs(L)
+    gout = torch.randn(t["u"].shape, generator=torch.Generator().manual_seed(17))
+    leaves = {k: v.clone().requires_grad_(True) for k, v in t.items()}
+    zero = torch.zeros(t["u"].shape[0], t["u"].shape[1], t["A"].shape[1])
+    y, _, _ = _slice_scan(leaves["u"], leaves["delta"], leaves["A"], leaves["B"], leaves["C"], leaves["D"], leaves["z"],
+                          leaves["delta_bias"], zero)
+    (y * gout).sum().backward()
+    for k in ("u", "delta", "B", "C", "z"):
+        got = torch.cat([results[r][0][k] for r in range(world)], dim=-1)
+        torch.testing.assert_close(got, leaves[k].grad, rtol=2e-5, atol=2e-5, msg=lambda m: f"d{k}: {m}")
+    ref_pg = torch.cat([leaves[k].grad.reshape(-1) for k in ("A", "D", "delta_bias")])
+    for r in range(world):
+        torch.testing.assert_close(results[r][1], ref_pg, rtol=2e-5, atol=2e-5)
+
+
+def test_fold_suffix_identity_for_last_rank():
+    from lrnnx_b200.sp import fold_suffix
+    P = torch.rand(3, 2, 4, 5)
+    G = torch.randn(3, 2, 4, 5)
+    assert torch.equal(fold_suffix(P, G, 2), torch.zeros(2, 4, 5))
+    torch.testing.assert_close(fold_suffix(P, G, 1), G[2])
+    torch.testing.assert_close(fold_suffix(P, G, 0), G[1] + P[1] * G[2])
