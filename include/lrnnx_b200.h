@@ -455,6 +455,24 @@ typedef struct b200_cgemm_planes_args {
 int b200_cgemm_planes(const b200_cgemm_planes_args *args, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Linear layer for the few tokens of one decoding step: out (M, N) = x (M, K) W^T (+ bias), with
+ * W (N, K) the row-major weight of an nn.Linear, 16-bit operands, float32 accumulation.  Takes the
+ * place of the library GEMMs behind F.linear in Mamba.step (lrnnx/models/ltv/mamba.py:355-487:
+ * in_proj, x_proj, dt_proj, out_proj) and the LM head at decoding time, where each weight is
+ * streamed once per generated token.  1 <= M <= 64; K a multiple of 64; rows of x and W start on
+ * 16-byte boundaries (strides multiples of 8 elements); out rows may have any stride.
+ * Deterministic (no atomics).
+ * ------------------------------------------------------------------------ */
+typedef struct b200_skinny_linear_args {
+  int32_t M, N, K, dtype;          /* dtype: B200_BF16 or B200_F16 (x, weight, bias, out) */
+  const void *x, *weight, *bias;   /* bias (N) nullable */
+  void *out;
+  int64_t x_rs, w_rs, out_rs;      /* row strides in elements */
+} b200_skinny_linear_args;
+
+int b200_skinny_linear(const b200_skinny_linear_args *args, void *stream);
+
+/* ------------------------------------------------------------------------
  * Next-token cross-entropy over a wide vocabulary, read straight from the logits in their own
  * dtype (no float32 copy of the (rows, cols) logits).  lrnnx has no counterpart: its LM returns
  * logits (lrnnx/architectures/language_model.py:615-727) and its training benchmark sums them

@@ -28,7 +28,7 @@ ENTRY_POINTS = (
     "b200_cauchy_fwd", "b200_cauchy_bwd", "b200_cauchy_bwd_static", "b200_vand_fwd", "b200_vand_bwd",
     "b200_conv1d_fwd", "b200_conv1d_bwd", "b200_conv1d_update", "b200_rmsnorm_fwd", "b200_rmsnorm_bwd",
     "b200_cgemm_wx", "b200_cgemm_planes", "b200_cgemm_grad",
-    "b200_xent_fwd", "b200_xent_bwd",
+    "b200_xent_fwd", "b200_xent_bwd", "b200_skinny_linear",
 )
 
 _SCALARS = {"int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "uint32_t": ctypes.c_uint32,

@@ -62,6 +62,7 @@ int b200_sizeof(const char *name) {
   if (!strcmp(name, "b200_cgemm_planes_args")) return (int)sizeof(b200_cgemm_planes_args);
   if (!strcmp(name, "b200_cgemm_grad_args")) return (int)sizeof(b200_cgemm_grad_args);
   if (!strcmp(name, "b200_xent_args")) return (int)sizeof(b200_xent_args);
+  if (!strcmp(name, "b200_skinny_linear_args")) return (int)sizeof(b200_skinny_linear_args);
   return -1;
 }
 

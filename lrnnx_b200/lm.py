@@ -22,6 +22,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .ops.linear_step import linear_step
 from .ops.mamba_block import causal_conv1d_fn, causal_conv1d_update, rms_norm_fn
 from .ops.mamba_inner import mamba_inner_fn
 from .ops.selective_scan import selective_scan_fn
@@ -117,14 +118,14 @@ class Mamba(nn.Module):
         """One token: hidden (batch, d_model) -> (batch, d_model); both states advance in place
         (lrnnx/models/ltv/mamba.py:355-487)."""
         d, N, R = self.d_inner, self.d_state, self.dt_rank
-        xz = F.linear(hidden, self.in_proj.weight)
+        xz = linear_step(hidden, self.in_proj.weight)
         x, z = xz[:, :d], xz[:, d:]
         x = causal_conv1d_update(x, cache["conv_state"], self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
-        x_db = F.linear(x, self.x_proj.weight)
-        dt = F.linear(x_db[:, :R], self.dt_proj.weight)
+        x_db = linear_step(x, self.x_proj.weight)
+        dt = linear_step(x_db[:, :R], self.dt_proj.weight)
         y = selective_state_update(cache["lrnn_state"], x, dt, cache["A"], x_db[:, R:R + N], x_db[:, R + N:], cache["D"],
                                    z=z, dt_bias=cache["dt_bias"], dt_softplus=True)
-        return F.linear(y, self.out_proj.weight)
+        return linear_step(y, self.out_proj.weight)
 
     def allocate_inference_cache(self, batch_size, dtype=None, state_dtype=None):
         dev = self.out_proj.weight.device
@@ -203,7 +204,7 @@ class MambaLMHeadModel(nn.Module):
 
     def step(self, token_ids, caches):
         """token_ids (batch,) -> logits (batch, vocab); caches advance in place."""
-        return self.lm_head(self.backbone.step(token_ids, caches))
+        return linear_step(self.backbone.step(token_ids, caches), self.lm_head.weight)
 
     def allocate_inference_cache(self, batch_size, dtype=None, state_dtype=None):
         return [layer.mixer.allocate_inference_cache(batch_size, dtype, state_dtype) for layer in self.backbone.layers]

@@ -304,3 +304,52 @@ def test_cross_entropy_strided_rows_and_all_ignored():
     assert (logits.grad - ref_in.grad).abs().max().item() <= 1e-6 * ref_in.grad.abs().max().item() + 1e-9
     none = cross_entropy(logits.detach(), torch.full((12,), -100).cuda())
     assert none.item() == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N", [(64, 2048, 8192), (64, 4096, 160), (64, 128, 4096), (64, 4096, 2048), (7, 768, 3072),
+                                   (1, 64, 50), (33, 1536, 80), (64, 2048, 50280), (16, 512, 128)])
+def test_linear_step_matches_float64(M, K, N, dtype, monkeypatch):
+    """The weight-streaming linear layer of the decoding step against a float64 product of the same
+    16-bit operands (every K-slice count and feature-tile width the launcher picks), twice for
+    reproducibility."""
+    from lrnnx_b200.ops import linear_step as mod
+    from lrnnx_b200.ops.linear_step import linear_step, supported
+    monkeypatch.setattr(mod, "MAX_FEATURES", 1 << 30)      # every width goes through the kernel here
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    b = torch.randn(N, generator=g).to(dtype).cuda()
+    assert supported(x, w, b)
+    with torch.no_grad():
+        y = linear_step(x, w)
+        yb = linear_step(x, w, b)
+        y2 = linear_step(x, w)
+    ref = x.double() @ w.double().t()
+    tol = (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11)
+    scale = ref.abs().max().item()
+    assert (y.double() - ref).abs().max().item() <= tol * scale + 1e-6
+    assert (yb.double() - (ref + b.double())).abs().max().item() <= tol * (ref + b.double()).abs().max().item() + 1e-6
+    assert torch.equal(y, y2)
+
+
+def test_linear_step_strided_input_and_fallbacks():
+    from lrnnx_b200.ops.linear_step import linear_step, supported
+    g = torch.Generator().manual_seed(2)
+    xdb = torch.randn(64, 160, generator=g).bfloat16().cuda()
+    w = (torch.randn(384, 128, generator=g) / 11).bfloat16().cuda()
+    x = xdb[:, :128]                       # the low-rank step-size input of dt_proj: a strided view
+    assert supported(x, w)
+    with torch.no_grad():
+        y = linear_step(x, w)
+    ref = x.double() @ w.double().t()
+    assert (y.double() - ref).abs().max().item() <= 2.0 ** -8 * ref.abs().max().item()
+    # float32, more than 64 tokens, K not a multiple of 64, misaligned rows: the library path
+    assert not supported(x.float(), w.float())
+    assert not supported(torch.zeros(65, 128, dtype=torch.bfloat16, device="cuda"), w)
+    assert not supported(xdb[:, :96], w[:, :96])
+    assert not supported(xdb[:, 4:132], w)
+    assert not supported(x, torch.zeros(4096, 128, dtype=torch.bfloat16, device="cuda"))   # wide outputs: library GEMM
+    wg = w.clone().requires_grad_(True)
+    assert not supported(x, wg)            # gradients go through F.linear
+    torch.testing.assert_close(linear_step(x.float(), w.float()), x.float() @ w.float().t())
