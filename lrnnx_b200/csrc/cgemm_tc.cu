@@ -23,11 +23,13 @@
 // bounded; an expired wait sets the status word, skips the stores and still frees the TMEM.
 #include "common.cuh"
 #include "dispatch.h"
-#include <cuda.h>   // CUtensorMap and its enums (types only: the encoder is looked up at run time)
+#include "tc_common.cuh"
 #include <cstring>
 
 namespace b200 {
 namespace {
+
+using namespace tc;
 
 __device__ int g_cgemm_status = 0;
 
@@ -47,20 +49,6 @@ struct GemmMaps {
   CUtensorMap x;      // (2 N, batch K) float32, box (32, 32)
 };
 
-__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                   smem_u32(dst)),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-               : "memory");
-}
-
-// shared-memory matrix descriptor (descriptor version 1).  layout 2: 128-byte swizzle of 16-byte
-// chunks (the K-major weight tiles); layout 1: 128-byte swizzle of 32-byte chunks, the only
-// layout the tensor core accepts for an MN-major operand of 32-bit elements (the activation tile).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout) {
-  return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (layout << 61);
-}
 // weight-plane tile, K-major: rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t a_desc(uint32_t addr) { return smem_desc(addr, 16, 1024, 2); }
 // activation tile, MN-major: 32-float column groups 4096 bytes apart, 4-row K groups 512 bytes apart
@@ -84,32 +72,6 @@ __device__ __forceinline__ float tf32_low(float v) {
   const float r = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
   return __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xffffe000u);
 }
-__device__ __forceinline__ void mma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 32 consecutive columns of this thread's TMEM lane.  The load is asynchronous: the registers
-// are valid only after tcgen05.wait::ld, so load and wait sit in ONE asm statement; as separate
-// statements the compiler would be free to schedule uses of the outputs before the wait.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 __global__ void __launch_bounds__(NTHREADS, 1)
 cgemm_wx_kernel(const __grid_constant__ GemmMaps maps, const b200_cgemm_args p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -429,23 +391,6 @@ __global__ void cgemm_planes_kernel(const float2 *w, int M, int K, int64_t rs, i
   planes[MK + i] = __uint_as_float((__float_as_uint(rl) + 0x1000u) & 0xffffe000u);
   planes[2 * MK + i] = ih;
   planes[3 * MK + i] = __uint_as_float((__float_as_uint(il) + 0x1000u) & 0xffffe000u);
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encoder() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    void *ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    tried = true;
-  }
-  return fn;
 }
 
 bool make_map(CUtensorMap *m, const void *base, uint64_t inner, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,

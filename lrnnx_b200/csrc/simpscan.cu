@@ -1385,7 +1385,9 @@ int b200_device_status(void) {
   if (w < 0) return -1;
   const int g = cgemm_status_read();
   if (g < 0) return -1;
-  return v ? v : (w ? w : g);
+  const int l = linear_status_read();
+  if (l < 0) return -1;
+  return v ? v : (w ? w : (g ? g : l));
 }
 
 }  // extern "C"

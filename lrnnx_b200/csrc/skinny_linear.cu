@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "dispatch.h"
 
 namespace cg = cooperative_groups;
 
@@ -243,6 +244,7 @@ extern "C" int b200_skinny_linear(const b200_skinny_linear_args *args, void *str
                    (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0,
                B200_ERR_ALIGN, "skinny_linear: rows of x and weight must start on 16-byte boundaries");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (linear_tc_supported(a)) return linear_tc(a, st);     // wide outputs: the tcgen05 weight stream
   // K slices per feature tile: at most 8 (the portable cluster size), each at least two pipeline stages long;
   // feature tile: the widest of 128 / 64 / 32 that still gives every SM a CTA
   const int sms = sm_count_current();

@@ -11,8 +11,6 @@ loses where the output is wide (in_proj 13.1 against 8.2 us, out_proj 10.2 again
 the limiter before HBM is.  ``linear_step`` therefore takes the kernel for narrow outputs only and
 ``F.linear`` for everything else.
 """
-
-MAX_FEATURES = 512     # widest output the kernel is used for
 from __future__ import annotations
 
 import torch
@@ -21,11 +19,18 @@ import torch.nn.functional as F
 from .. import _lib
 from .mamba_block import _DT, _stream
 
+MAX_FEATURES = 512        # widest output the mma.sync kernel is used for
+MIN_TC_FEATURES = 1024    # narrowest output the tcgen05 kernel is used for (with K >= 512)
+
+
+def _width_ok(n, k):
+    return n <= MAX_FEATURES or (n >= MIN_TC_FEATURES and k >= 512)
+
 
 def supported(x, weight, bias=None):
     return (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
             and (bias is None or bias.dtype == x.dtype)
-            and 1 <= x.shape[0] <= 64 and weight.shape[0] <= MAX_FEATURES and weight.shape[1] % 64 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+            and 1 <= x.shape[0] <= 64 and _width_ok(weight.shape[0], weight.shape[1]) and weight.shape[1] % 64 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
             and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and weight.data_ptr() % 16 == 0 and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)))
 

@@ -107,3 +107,15 @@ def test_install_registers_extension_modules():
                 sys.modules.pop(k, None)
             else:
                 sys.modules[k] = v
+
+
+def test_every_python_module_of_the_package_imports():
+    """Import errors in modules that only the GPU tests use must show up without a GPU."""
+    import importlib
+    import pkgutil
+
+    import lrnnx_b200
+    for mod in pkgutil.walk_packages(lrnnx_b200.__path__, "lrnnx_b200."):
+        if mod.name.endswith(".build"):
+            continue
+        importlib.import_module(mod.name)
