@@ -26,10 +26,6 @@ int selscan_bwd_sl(const b200_selscan_bwd_args &a, cudaStream_t st);
 
 // status word of the tensor-core projection kernel (cgemm_tc.cu)
 int cgemm_status_read();
-int linear_status_read();
-// decoding-step linear layer on the tensor cores (wide outputs)
-bool linear_tc_supported(const b200_skinny_linear_args &a);
-int linear_tc(const b200_skinny_linear_args &a, cudaStream_t st);
 
 // status word of the decode-step pipeline (ssu.cu): non-zero after an expired bounded wait
 int ssu_status_read();

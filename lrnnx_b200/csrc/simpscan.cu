@@ -1385,9 +1385,7 @@ int b200_device_status(void) {
   if (w < 0) return -1;
   const int g = cgemm_status_read();
   if (g < 0) return -1;
-  const int l = linear_status_read();
-  if (l < 0) return -1;
-  return v ? v : (w ? w : (g ? g : l));
+  return v ? v : (w ? w : g);
 }
 
 }  // extern "C"

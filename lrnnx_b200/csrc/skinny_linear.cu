@@ -11,19 +11,20 @@
 //   * Weight and activation tiles (BN x 64 and 64 x 64 elements) arrive by 16-byte cp.async into a
 //     4-stage ring of 128-byte-row, XOR-swizzled shared-memory tiles; eight warps (16 tokens x half
 //     of the features each) consume them with ldmatrix + mma.sync.m16n8k16.  Measured at 64 tokens:
-//     faster than the library GEMM for narrow outputs (160 features over K = 4096: 5.1 against 7.0 us),
-//     slower for wide ones (8192 features: 13.1 against 8.2 us), where the legacy tensor path of
-//     mma.sync limits it before HBM does; the Python wrapper uses the kernel for narrow outputs only.
-//   * The partial sums of the cluster's CTAs meet in distributed shared memory: every CTA parks
-//     its (64 x BN) float32 partial in its own shared memory, and after a cluster barrier CTA r adds
-//     up rows [r 64/S, (r+1) 64/S) over the S partials in rank order.  No atomics: the result does
-//     not depend on arrival order, so decoding is reproducible.
+//     faster than the library GEMM for narrow outputs (160 features over K = 4096: 4.7 against 7.0 us),
+//     slower for wide ones (8192 features: 13 to 17 against 8.2 us; a tcgen05 variant with the weight as
+//     the 128-row operand, TMA tiles and a TMEM accumulator was correct but no faster, 12.3 us: at one
+//     CTA per SM both are held near 45 GB/s per SM by the activation tile every CTA re-reads from
+//     L2 next to its weight stream); the Python wrapper uses the kernel for narrow outputs only.
+//   * The partial sums of the cluster's CTAs meet in distributed shared memory: CTA r owns token rows
+//     [r 64/S, (r+1) 64/S); every CTA posts its partial values for those rows into r's receive buffer
+//     (plain remote stores), and after one cluster barrier r adds up the S contributions in rank
+//     order.  No atomics: the result does not depend on arrival order, so decoding is reproducible.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
-#include "dispatch.h"
 
 namespace cg = cooperative_groups;
 
@@ -79,8 +80,8 @@ template <int BN> struct SkSmem {
   static constexpr int PIPE = SK_STAGES * STAGE;
   static constexpr int PROW = BN + 8;                        // floats per row of the partial tile (8 rows of a
                                                              // fragment store land in distinct 32-byte segments)
-  static constexpr int PART = SK_M * PROW * 4;               // float32 partial of the tile (reuses the ring)
-  static constexpr int TOTAL = PIPE > PART ? PIPE : PART;
+  static constexpr int PART = SK_M * PROW * 4;               // receive buffer: S slots of 64 / S token rows, float32
+  static constexpr int TOTAL = PIPE + PART;
 };
 
 template <typename T, int BN>
@@ -154,33 +155,39 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_linear_kernel(const b200_sk
     }
   }
   cp_async_wait<0>();
-  __syncthreads();                                    // the ring is free: it becomes the partial tile
 
-  // park the partial (64 x BN float32)
-  float *part = reinterpret_cast<float *>(smem);
+  // Token rows are dealt out to the cluster's CTAs: rank r owns rows [r 64 / S, (r + 1) 64 / S).  Every
+  // warp posts its fragment values straight into the owner's receive buffer, slot [sender rank][row],
+  // with plain stores into distributed shared memory (nothing waits on a remote round trip); after one
+  // cluster barrier every CTA adds up its S slots from its own shared memory, in rank order.
+  float *recv = reinterpret_cast<float *>(smem + SM::PIPE);
+  const int log2s = 31 - __clz(S);
+  const int rows_per = SK_M >> log2s;
   {
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int j = 0; j < HN / 8; ++j) {
-      const int col = wn * HN + j * 8 + t4 * 2;
-      *reinterpret_cast<float2 *>(part + (wm * 16 + g) * SM::PROW + col) = make_float2(acc[j][0], acc[j][1]);
-      *reinterpret_cast<float2 *>(part + (wm * 16 + g + 8) * SM::PROW + col) = make_float2(acc[j][2], acc[j][3]);
+    for (int half = 0; half < 2; ++half) {
+      const int row = wm * 16 + g + half * 8;
+      const int owner = row >> (6 - log2s);
+      float *dst = (S > 1 ? cluster.map_shared_rank(recv, owner) : recv) + (ks * rows_per + (row & (rows_per - 1))) * SM::PROW;
+#pragma unroll
+      for (int j = 0; j < HN / 8; ++j) {
+        const int col = wn * HN + j * 8 + t4 * 2;
+        *reinterpret_cast<float2 *>(dst + col) = make_float2(acc[j][2 * half], acc[j][2 * half + 1]);
+      }
     }
   }
   if (S > 1) cluster.sync();
   else __syncthreads();
 
-  // CTA ks adds up rows [ks * 64 / S, (ks + 1) * 64 / S) over the cluster's partials, in rank order
-  const int rows_per = SK_M / S;
-  const int r_begin = ks * rows_per;
   T *out = reinterpret_cast<T *>(p.out);
   const T *bias = reinterpret_cast<const T *>(p.bias);
   for (int i = tid; i < rows_per * (BN / 4); i += SK_THREADS) {
-    const int r = r_begin + i / (BN / 4), c4 = (i % (BN / 4)) * 4;
+    const int rl = i / (BN / 4), c4 = (i % (BN / 4)) * 4;
+    const int r = ks * rows_per + rl;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < S; ++q) {
-      const float *src = S > 1 ? cluster.map_shared_rank(part, q) : part;
-      const float4 v = *reinterpret_cast<const float4 *>(src + r * SM::PROW + c4);
+      const float4 v = *reinterpret_cast<const float4 *>(recv + (q * rows_per + rl) * SM::PROW + c4);
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
     if (r < p.M) {
@@ -196,7 +203,6 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_linear_kernel(const b200_sk
       }
     }
   }
-  if (S > 1) cluster.sync();                          // nobody leaves while its partial is still being read
 }
 
 template <typename T, int BN>
@@ -244,7 +250,6 @@ extern "C" int b200_skinny_linear(const b200_skinny_linear_args *args, void *str
                    (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0,
                B200_ERR_ALIGN, "skinny_linear: rows of x and weight must start on 16-byte boundaries");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (linear_tc_supported(a)) return linear_tc(a, st);     // wide outputs: the tcgen05 weight stream
   // K slices per feature tile: at most 8 (the portable cluster size), each at least two pipeline stages long;
   // feature tile: the widest of 128 / 64 / 32 that still gives every SM a CTA
   const int sms = sm_count_current();

@@ -5,9 +5,9 @@ Mamba.step (lrnnx/models/ltv/mamba.py:355-487) applies in_proj, x_proj, dt_proj 
 do almost no arithmetic, so they are bound by how fast the weight streams from HBM.
 ``b200_skinny_linear`` is built for that case (up to 64 tokens, 16-bit operands).  Measured on B200
 at 64 tokens it beats the library GEMM only where the output is narrow — x_proj, 160 features over
-K = 4096: 5.1 us against 7.0 us, because the library launches too few thread blocks there — and
-loses where the output is wide (in_proj 13.1 against 8.2 us, out_proj 10.2 against 8.2 us, LM head
-57 against 37 us): its ``mma.sync`` tiles run on the legacy tensor path, which at 64 tokens is
+K = 4096: 4.7 us against 7.0 us, because the library launches too few thread blocks there — and
+loses where the output is wide (in_proj 13 to 17 against 8.2 us, out_proj 9.8 against 8.2 us, LM head
+57 to 66 against 37 us): its ``mma.sync`` tiles run on the legacy tensor path, which at 64 tokens is
 the limiter before HBM is.  ``linear_step`` therefore takes the kernel for narrow outputs only and
 ``F.linear`` for everything else.
 """
@@ -19,12 +19,11 @@ import torch.nn.functional as F
 from .. import _lib
 from .mamba_block import _DT, _stream
 
-MAX_FEATURES = 512        # widest output the mma.sync kernel is used for
-MIN_TC_FEATURES = 1024    # narrowest output the tcgen05 kernel is used for (with K >= 512)
+MAX_FEATURES = 512        # widest output the kernel is used for
 
 
 def _width_ok(n, k):
-    return n <= MAX_FEATURES or (n >= MIN_TC_FEATURES and k >= 512)
+    return n <= MAX_FEATURES
 
 
 def supported(x, weight, bias=None):
