@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Default workload (BASELINE.json configs[1]): the diagonal complex simplified scan used by
+Default workload (benchmark configuration 1): the diagonal complex simplified scan used by
 S5, complex64, B=8, P=256 states, H=512 channels, L=4096, forward + backward, recurrence
 x_k = Lambda x_{k-1} + (B u)_k  (A = log Lambda, delta = 1, "dirac").
 
@@ -166,7 +166,7 @@ def build_step_graphs(dev, copy_stream, issue_copies, compute):
 
 # --------------------------------------------------------------------------- workloads
 class S5Scan:
-    """BASELINE config 1 (and its variants: time-varying step size, batch split over the ranks)."""
+    """benchmark configuration 1 (and its variants: time-varying step size, batch split over the ranks)."""
     dtype = "c64"
     metric, unit = "scan tokens/s (simplified scan fwd+bwd)", "tokens/s"
 
@@ -430,7 +430,7 @@ class S5Scan:
 
 
 class S6Scan:
-    """Selective scan (S6/Mamba) forward(+backward); shapes of BASELINE configs 0, 2 (one layer) and 3."""
+    """Selective scan (S6/Mamba) forward(+backward); shapes of benchmark configurations 0, 2 (one layer) and 3."""
     roofline_note = ("with dstate 16 the scan needs one ex2 and ~7 fp32 operations per (timestep, state, channel) "
                      "for 4-10 bytes: it is bound by fp32 / SFU instruction issue, not by HBM (ncu: 62 % of the issue "
                      "slots busy in the forward, DRAM below 10 %)")
@@ -690,7 +690,7 @@ class S6Scan:
 
 
 class SsuStep:
-    """Decode step kernel at the BASELINE config 4 shape: 48 layers x selective_state_update with
+    """Decode step kernel at the benchmark configuration 4 shape: 48 layers x selective_state_update with
     batch 64, d_inner 4096, dstate 16, bf16 activations, fp32 state (one step = 48 launches; the
     projections, conv and norms of the model are outside the path)."""
     name = "ssu_step_cfg4"
@@ -858,7 +858,7 @@ class CauchyKernel:
 
 
 class LmTrain:
-    """BASELINE configs[2]: Mamba LM, 24 layers, d_model 768 (d_inner 1536, dstate 16, dt_rank 48,
+    """benchmark configuration 2: Mamba LM, 24 layers, d_model 768 (d_inner 1536, dstate 16, dt_rank 48,
     conv 4), vocabulary 50280, random-init bf16 weights, token ids uniform in [0, 50280), batch 8 x
     2048 tokens, forward + backward of the shifted cross-entropy + a fused AdamW step.  The batch
     is split over the ranks (fixed total work); gradients are all-reduced in buckets overlapped
@@ -952,7 +952,7 @@ class LmTrain:
 
 
 class LmDecode:
-    """BASELINE configs[4]: Mamba LM at the 1.4B shape (48 layers, d_model 2048, d_inner 4096,
+    """benchmark configuration 4: Mamba LM at the 1.4B shape (48 layers, d_model 2048, d_inner 4096,
     dstate 16, dt_rank 128), random-init bf16 weights, batch 64 (split over the ranks), random
     prompts of 512 tokens prefilled through the scan kernels, then 256 greedy tokens replayed from
     one captured CUDA graph of the decoding step.  A step of this workload is one whole generation."""

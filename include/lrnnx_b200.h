@@ -157,7 +157,7 @@ int b200_selscan_bwd(const b200_selscan_bwd_args *args, void *stream);
 /* ------------------------------------------------------------------------
  * Sequence-parallel helpers for the selective scan (no counterpart in lrnnx,
  * which is single-GPU; they implement the chunk-summary exchange that
- * BASELINE's long-sequence configuration asks for).
+ * the long-sequence benchmark configuration asks for).
  * b200_selscan_fixup adds the contribution of an incoming state h_in
  * (batch, dim, dstate) float32 to an already computed zero-state output:
  *   out[b,d,t] += sum_n C[t,n] * (prod_{k<=t} a_k[n]) * h_in[b,d,n]

@@ -487,8 +487,8 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
   if (lane == 0) { issue(); issue(); }
 
   // A bounded wait that expires marks the thread as failed; a failed thread skips every later
-  // wait (results are then garbage and the status word says so) but keeps taking part in the
-  // block barriers, so the CTA always terminates.
+  // wait and its warp stores no further du / ddelta (the status word says that the outputs are
+  // incomplete) but keeps taking part in the block barriers, so the CTA always terminates.
   bool failed = false;
   auto wait = [&](uint64_t *bar, uint32_t parity) {
     if (!failed && !mbar_wait(bar, parity, 1u << 21)) failed = true;
@@ -748,7 +748,8 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
+      const bool warp_failed = __any_sync(0xffffffffu, failed);   // a warp that gave up on a wait stores nothing more
+      if (lane == 0 && !warp_failed) {
         const int w0 = warp * SL;
         if (SWZ) {
           const int64_t e0 = row * L + t0 + w0;
@@ -767,7 +768,7 @@ simpscan_bwd_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMaps 
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
         const int t = t0 + tid * BI + i;
-        if (t < L) {
+        if (t < L && !failed) {
           rp.du[t] = du[i];
           rp.dd[t] = ddl[i];
           if (HAS_DA) rp.ddA[t] = ddA[i];
@@ -1152,7 +1153,8 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
+      const bool warp_failed = __any_sync(0xffffffffu, failed);   // a warp that gave up on a wait stores nothing more
+      if (lane == 0 && !warp_failed) {
         if (SWZ) {
           const int64_t e0 = row * L + tw;
           tensor_s2g(&maps.du, (int)(e0 >> 4), su);
@@ -1170,7 +1172,7 @@ simpscan_bwd_h_kernel(const b200_simpscan_args p, const __grid_constant__ TmaMap
 #pragma unroll
       for (int i = 0; i < BI; ++i) {
         const int t = tw + lane * BI + i;
-        if (t < L) {
+        if (t < L && !failed) {
           rp.du[t] = du[i];
           rp.dd[t] = ddl[i];
           if (HAS_DA) rp.ddA[t] = ddA[i];

@@ -1,4 +1,4 @@
-"""Mamba language-model harness for BASELINE configs 2 (training step) and 4 (decoding).
+"""Mamba language-model harness for benchmark configurations 2 (training step) and 4 (decoding).
 
 A host-side mirror of lrnnx's ``LRNNLMHeadModel`` restricted to what those two configurations
 use: Mamba mixers, RMSNorm, tied embeddings, no MLP (lrnnx/architectures/language_model.py:

@@ -1,4 +1,4 @@
-"""Sequence-parallel selective scan (BASELINE config 3): forward, and the backward that mirrors it.
+"""Sequence-parallel selective scan (benchmark configuration 3): forward, and the backward that mirrors it.
 
 lrnnx is single-GPU; this is the multi-GPU split its long-sequence case needs.  Rank r owns
 the timesteps [r*L/R, (r+1)*L/R).  Because the recurrence h_t = a_t h_{t-1} + b_t is linear,

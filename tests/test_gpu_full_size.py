@@ -1,4 +1,4 @@
-"""Checks at the full BASELINE sizes, where the CPU oracle is too slow, through properties that do
+"""Checks at the full benchmark sizes, where the CPU oracle is too slow, through properties that do
 not depend on the size:
   * linearity of the scan in its input (the recurrence is linear in u for fixed delta, A),
   * time-shift consistency: scanning a suffix from a zero state after an all-zero prefix equals

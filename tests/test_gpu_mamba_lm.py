@@ -1,5 +1,5 @@
 """GPU parity of the Mamba block kernels (causal convolution, its one-token update, residual add
-+ RMSNorm), of mamba_inner_fn, and of the LM harness built from them (BASELINE configs 2 and 4).
++ RMSNorm), of mamba_inner_fn, and of the LM harness built from them (benchmark configurations 2 and 4).
 
 Reference side: tests/golden/mamba_lm.pt, recorded from lrnnx's own LRNNLMHeadModel on CPU
 (weights, logits, parameter gradients of the shifted cross-entropy, step() logits), and the

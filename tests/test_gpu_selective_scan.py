@@ -3,7 +3,7 @@
 Reference side: the golden fixtures recorded from lrnnx's selective_scan_ref /
 rglru_scan_ref / s7_scan_ref, and the CPU oracle on seeded CPU-generated inputs.
 Tolerance: rtol 1e-4 for fp32 activations, 3e-2 for bf16/fp16 activations
-(BASELINE north_star), with an absolute floor of 1e-5 (fp32) / 1e-2 (16-bit)
+(the acceptance tolerance of the benchmark specification), with an absolute floor of 1e-5 (fp32) / 1e-2 (16-bit)
 times the largest reference magnitude of the tensor being compared.
 """
 from __future__ import annotations
@@ -125,7 +125,7 @@ def test_half_precision_inputs(dtype):
 
 
 def test_config0_shape():
-    """BASELINE config 0: B=2, D=256, L=512, N=16, A = -[1..N], D = 1, dt-style bias."""
+    """benchmark configuration 0: B=2, D=256, L=512, N=16, A = -[1..N], D = 1, dt-style bias."""
     import math
     g = torch.Generator().manual_seed(0)
     batch, dim, L, N = 2, 256, 512, 16

@@ -154,7 +154,7 @@ def test_multi_state_kernel():
 
 
 def test_config1_recurrence_shape_slice():
-    """BASELINE config 1 recurrence x_k = Lambda x_{k-1} + (B u)_k through simplified_scan_fn with
+    """benchmark configuration 1 recurrence x_k = Lambda x_{k-1} + (B u)_k through simplified_scan_fn with
     A = log Lambda, delta = 1, "dirac"; a (2, 64, 4096) slice of the (8, 256/512, 4096) shape.
 
     |Lambda| reaches 0.999, i.e. a memory of ~1000 steps through which every rounding of the
