@@ -857,6 +857,137 @@ class CauchyKernel:
         return 64 * self.L
 
 
+class BlockKernels:
+    """The HBM-bound kernels around the scan in a Mamba block and LM step, at the config-2 shapes:
+    causal convolution + SiLU forward / backward on (8, 1536, 2048) bf16, residual add + RMSNorm
+    forward / backward on (16384, 768) bf16, next-token cross-entropy forward / backward on
+    (16384, 50280) bf16 logits, and the narrow projection of a decoding step (64 x 4096 -> 160).
+    A step runs each REPEAT times (one CUDA graph per kernel); a token is one (batch, position) of the
+    config-2 batch, counted once per repeat."""
+    name = "block_kernels_cfg2"
+    dtype = "bf16"
+    metric, unit = "tokens/s through the block kernels (conv, norm, loss; fwd+bwd)", "tokens/s"
+    launches_per_step = 7 * 4
+    roofline_note = ("conv and norm operands (25-50 MB per tensor) partly stay in the 126 MB L2 between the forward and "
+                     "backward launch, as they do inside the LM step; the fraction is algorithmic bytes over time")
+
+    def __init__(self, batch=8, d_inner=1536, L=2048, d_model=768, vocab=50280):
+        self.batch, self.d_inner, self.L, self.d_model, self.vocab = batch, d_inner, L, d_model, vocab
+        self.tokens = batch * L * self.REPEAT
+        self.describe = {"workload": f"{self.name}: conv (8,{d_inner},{L}), norm ({batch * L},{d_model}), "
+                                     f"loss ({batch * L},{vocab}), x_proj 64x4096->160; bf16",
+                         "global_batch": batch, "seq_len": L,
+                         "l2": "the loss kernels stream 1.65 GB of logits; a 256 MB write flushes the L2 before every step"}
+
+    def setup(self, dev, pg):
+        from lrnnx_b200.ops.cross_entropy import cross_entropy
+        from lrnnx_b200.ops.linear_step import linear_step
+        from lrnnx_b200.ops.mamba_block import causal_conv1d_fn, rms_norm_fn
+        self.dev, self.pg = dev, pg
+        self.fn = dict(conv=causal_conv1d_fn, norm=rms_norm_fn, xent=cross_entropy, lin=linear_step)
+        g = torch.Generator().manual_seed(0)
+        bf = torch.bfloat16
+        rows = self.batch * self.L
+        mk = lambda *s: torch.randn(*s, generator=g).to(bf)
+        self.h_x = mk(self.batch, self.d_inner, self.L).pin_memory()
+        self.t = dict(x=self.h_x.to(dev).requires_grad_(True), w=mk(self.d_inner, 4).to(dev).requires_grad_(True),
+                      b=torch.zeros(self.d_inner, dtype=bf, device=dev, requires_grad=True),
+                      gconv=mk(self.batch, self.d_inner, self.L).to(dev),
+                      h=mk(rows, self.d_model).to(dev).requires_grad_(True), r=mk(rows, self.d_model).to(dev).requires_grad_(True),
+                      g=torch.ones(self.d_model, dtype=bf, device=dev, requires_grad=True), gnorm=mk(rows, self.d_model).to(dev),
+                      logits=mk(rows, self.vocab).to(dev).requires_grad_(True),
+                      labels=torch.randint(0, self.vocab, (rows,), generator=g).to(dev),
+                      xs=mk(64, 4096).to(dev), wx=(mk(160, 4096) / 64).to(dev))
+        self.ev = []
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        s2 = 2
+        BDL, RC, RV = self.batch * self.d_inner * self.L, rows * self.d_model, rows * self.vocab
+        self.bytes = {"conv1d_fwd": 2 * BDL * s2, "conv1d_bwd": 3 * BDL * s2, "rmsnorm_fwd": 4 * RC * s2,
+                      "rmsnorm_bwd": 4 * RC * s2, "xent_fwd": RV * s2, "xent_bwd": 2 * RV * s2,
+                      "skinny_linear": 160 * 4096 * s2 + 64 * 4096 * s2}
+
+    REPEAT = 4      # launches of a kernel per graph: the time of one is the replay's time / REPEAT
+
+    def _build_graphs(self):
+        """One CUDA graph per kernel, REPEAT launches each, so that the timed region holds kernels and
+        not the host work of an autograd call (which is 2-5x the kernels' own time at these sizes)."""
+        t, fn = self.t, self.fn
+        grad = torch.autograd.grad
+        yc = fn["conv"](t["x"], t["w"], t["b"], "silu")
+        o, z = fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True)
+        loss = fn["xent"](t["logits"], t["labels"])
+        bodies = [
+            lambda: fn["conv"](t["x"], t["w"], t["b"], "silu"),
+            lambda: grad(yc, [t["x"], t["w"], t["b"]], t["gconv"], retain_graph=True),
+            lambda: fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True),
+            lambda: grad([o, z], [t["h"], t["r"], t["g"]], [t["gnorm"], t["gnorm"]], retain_graph=True),
+            lambda: fn["xent"](t["logits"], t["labels"]),
+            lambda: grad(loss, [t["logits"]], retain_graph=True),
+            lambda: fn["lin"](t["xs"], t["wx"]),
+        ]
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for body in bodies:
+                body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graphs = []
+        for k, body in enumerate(bodies):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                if k == 6:
+                    with torch.no_grad():
+                        for _ in range(self.REPEAT):
+                            body()
+                else:
+                    for _ in range(self.REPEAT):
+                        body()
+            self.graphs.append(g)
+        self._loss = loss.detach()
+
+    def step(self, record=False):
+        if getattr(self, "graphs", None) is None:
+            self._build_graphs()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(8)] if record else None
+        for k, g in enumerate(self.graphs):
+            if record:
+                ev[k].record()
+            g.replay()
+        if record:
+            ev[7].record()
+            self.ev.append(ev)
+        return self._loss
+
+    def e2e_step(self):
+        with torch.no_grad():
+            self.t["x"].copy_(self.h_x, non_blocking=True)
+        return float(self.step().item())
+
+    def e2e_bytes(self):
+        return self.h_x.numel() * 2, 4
+
+    def kernel_rooflines(self):
+        names = ("conv1d_fwd", "conv1d_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "xent_fwd", "xent_bwd", "skinny_linear")
+        out = {}
+        for i, n in enumerate(names):
+            out[n] = (self.bytes[n], statistics.mean(e[i].elapsed_time(e[i + 1]) for e in self.ev) / self.REPEAT)
+        return out
+
+    cpu_sample = "convolution + norm forward on 1 of 8 sequences (float32, PyTorch ops of the oracle)"
+
+    def cpu_step(self):
+        from oracle import scan_oracle as O
+        if not hasattr(self, "_cpu"):
+            g = torch.Generator().manual_seed(0)
+            self._cpu = (torch.randn(1, self.d_inner, self.L, generator=g), torch.randn(self.d_inner, 4, generator=g),
+                         torch.randn(self.L, self.d_model, generator=g), torch.ones(self.d_model))
+        x, w, h, gw = self._cpu
+        O.causal_conv1d_oracle(x, w, None, "silu")
+        O.rms_norm_oracle(h, gw, None, 1e-5)
+        return self.L
+
+
 class LmTrain:
     """benchmark configuration 2: Mamba LM, 24 layers, d_model 768 (d_inner 1536, dstate 16, dt_rank 48,
     conv 4), vocabulary 50280, random-init bf16 weights, token ids uniform in [0, 50280), batch 8 x
@@ -1049,6 +1180,8 @@ def make_workload(name, sub=False):
         return SsuStep()
     if name in ("cauchy", "cauchy_s4"):
         return CauchyKernel()
+    if name in ("block_kernels", "block_kernels_cfg2"):
+        return BlockKernels()
     if name == "lm_cfg2":
         return LmTrain()
     if name == "decode_cfg4":
@@ -1056,8 +1189,8 @@ def make_workload(name, sub=False):
     raise SystemExit(f"unknown workload {name}")
 
 
-SUB_WORKLOADS = ("s6_cfg0", "s6_layer", "s6_layer_f32", "s6_long", "ssu_step", "cauchy", "s5_scan_zoh", "lm_cfg2",
-                 "decode_cfg4")
+SUB_WORKLOADS = ("s6_cfg0", "s6_layer", "s6_layer_f32", "s6_long", "ssu_step", "cauchy", "s5_scan_zoh", "block_kernels",
+                 "lm_cfg2", "decode_cfg4")
 
 # nominal fp32 rate of one B200: 148 SMs x 128 FMA lanes x 2 x 1.965 GHz (no measured figure exists)
 FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12

@@ -105,7 +105,10 @@ class Mamba(nn.Module):
         batch, _, L = xz.shape
         d, N, R = self.d_inner, self.d_state, self.dt_rank
         x, z = xz[:, :d], xz[:, d:]
-        cache["conv_state"].copy_(F.pad(x, (self.d_conv - L, 0)))
+        if L >= self.d_conv:                               # the last d_conv inputs (a padded copy of x would move all of it)
+            cache["conv_state"].copy_(x[..., L - self.d_conv:])
+        else:
+            cache["conv_state"].copy_(F.pad(x, (self.d_conv - L, 0)))
         xc = causal_conv1d_fn(x, self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
         x_dbl = torch.bmm(self.x_proj.weight.unsqueeze(0).expand(batch, -1, -1), xc)
         delta = torch.bmm(self.dt_proj.weight.unsqueeze(0).expand(batch, -1, -1), x_dbl[:, :R])
