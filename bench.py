@@ -913,29 +913,31 @@ class BlockKernels:
         not the host work of an autograd call (which is 2-5x the kernels' own time at these sizes)."""
         t, fn = self.t, self.fn
         grad = torch.autograd.grad
-        yc = fn["conv"](t["x"], t["w"], t["b"], "silu")
-        o, z = fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True)
-        loss = fn["xent"](t["logits"], t["labels"])
-        bodies = [
-            lambda: fn["conv"](t["x"], t["w"], t["b"], "silu"),
-            lambda: grad(yc, [t["x"], t["w"], t["b"]], t["gconv"], retain_graph=True),
-            lambda: fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True),
-            lambda: grad([o, z], [t["h"], t["r"], t["g"]], [t["gnorm"], t["gnorm"]], retain_graph=True),
-            lambda: fn["xent"](t["logits"], t["labels"]),
-            lambda: grad(loss, [t["logits"]], retain_graph=True),
-            lambda: fn["lin"](t["xs"], t["wx"]),
-        ]
-        side = torch.cuda.Stream(device=self.dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for body in bodies:
+        # autograd runs a backward node on the stream its forward ran on, so the forward passes whose
+        # backward is captured run on the capture stream too
+        cap = torch.cuda.Stream(device=self.dev)
+        cap.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(cap):
+            yc = fn["conv"](t["x"], t["w"], t["b"], "silu")
+            o, z = fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True)
+            loss = fn["xent"](t["logits"], t["labels"])
+            bodies = [
+                lambda: fn["conv"](t["x"], t["w"], t["b"], "silu"),
+                lambda: grad(yc, [t["x"], t["w"], t["b"]], t["gconv"], retain_graph=True),
+                lambda: fn["norm"](t["h"], t["g"], None, residual=t["r"], prenorm=True),
+                lambda: grad([o, z], [t["h"], t["r"], t["g"]], [t["gnorm"], t["gnorm"]], retain_graph=True),
+                lambda: fn["xent"](t["logits"], t["labels"]),
+                lambda: grad(loss, [t["logits"]], retain_graph=True),
+                lambda: fn["lin"](t["xs"], t["wx"]),
+            ]
+            for body in bodies:                       # warm-up outside capture
                 body()
-        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.current_stream().wait_stream(cap)
         torch.cuda.synchronize()
         self.graphs = []
         for k, body in enumerate(bodies):
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, stream=cap):
                 if k == 6:
                     with torch.no_grad():
                         for _ in range(self.REPEAT):

@@ -16,20 +16,20 @@ class SelectiveScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, u, delta, A, B, C, D=None, z=None, delta_bias=None, deltaA=None, delta_softplus=False,
                 return_last_state=False, discretization=None):
-        if not u.is_contiguous():
-            u = u.contiguous()
-        if not delta.is_contiguous():
-            delta = delta.contiguous()
+        # The extension takes batch / channel strides as they are (a slice of a wider tensor, such
+        # as the x and z halves of a Mamba block's in-projection, is scanned in place); only the
+        # sequence dimension has to be dense.  lrnnx's wrapper copies every non-contiguous operand
+        # (lrnnx/ops/selective_scan.py:48-62) because its extension assumes more.
+        def dense_last(t):
+            return t if t is None or t.stride(-1) == 1 or t.size(-1) == 1 else t.contiguous()
+
+        u, delta, z, deltaA = dense_last(u), dense_last(delta), dense_last(z), dense_last(deltaA)
         if D is not None:
             D = D.contiguous()
-        if not B.is_contiguous():
-            B = B.contiguous()
-        if not C.is_contiguous():
-            C = C.contiguous()
-        if z is not None and not z.is_contiguous():
-            z = z.contiguous()
-        if deltaA is not None and not deltaA.is_contiguous():
-            deltaA = deltaA.contiguous()
+        if B.dim() >= 3:
+            B = dense_last(B)
+        if C.dim() >= 3:
+            C = dense_last(C)
         ctx.squeeze_B = ctx.squeeze_C = False
         if B.dim() == 3:
             B = B.unsqueeze(1)
