@@ -68,15 +68,26 @@ __device__ __forceinline__ float dsilu_f(float x) {
 }
 
 // out[b, d, t] = act(bias[d] + sum_k w[d, k] x[b, d, t - (W-1) + k])
+// Threads per row of an item: 256 for rows of 2048 steps or more, the next power of two above L / 8
+// for shorter rows, so that a CTA of 256 threads covers 256 / tpr batch rows at once and no thread
+// idles past the end of a short row.
+__host__ __device__ __forceinline__ int conv_tpr(int L) {
+  int t = 1;
+  while (t < CVT && t * CVE < L) t <<= 1;
+  return t;
+}
+
 // A CTA owns one channel (its taps are read once) and walks that channel's work items, an item
-// being CVT * CVE consecutive steps of one batch row: few, long-lived CTAs instead of one per item
+// being up to CVT * CVE consecutive steps of one batch row (or of several short rows): few, long-lived CTAs instead of one per item
 // (the kernel moves 4 bytes per thread-instruction; the rate at which thread blocks can be
 // started would bound it otherwise).
 template <typename T>
 __global__ void __launch_bounds__(CVT) conv1d_fwd_kernel(const b200_conv1d_args p) {
   const int d = blockIdx.x;
   const int W = p.width, L = p.seqlen;
-  const int nblk = (L + CVT * CVE - 1) / (CVT * CVE), items = p.batch * nblk;
+  const int tpr = conv_tpr(L), rpi = CVT / tpr;          // threads per row, batch rows per item
+  const int nblk = (L + tpr * CVE - 1) / (tpr * CVE), items = ((p.batch + rpi - 1) / rpi) * nblk;
+  const int sub = threadIdx.x / tpr, tt = threadIdx.x - sub * tpr;
   // the taps right-aligned in a window of MAXW (zeros in front): every register index below is a
   // compile-time constant whatever the width
   float w[MAXW];
@@ -85,9 +96,10 @@ __global__ void __launch_bounds__(CVT) conv1d_fwd_kernel(const b200_conv1d_args 
     w[k] = k >= MAXW - W ? tof(reinterpret_cast<const T *>(p.weight)[(int64_t)d * W + k - (MAXW - W)]) : 0.f;
   const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
   for (int item = blockIdx.y; item < items; item += gridDim.y) {
-    const int b = item / nblk;
-    const int t = ((item - b * nblk) * CVT + threadIdx.x) * CVE;
-    if (t >= L) continue;
+    const int bg = item / nblk;
+    const int b = bg * rpi + sub;
+    const int t = ((item - bg * nblk) * tpr + tt) * CVE;
+    if (t >= L || b >= p.batch) continue;
     const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
     T *out = reinterpret_cast<T *>(p.out) + (int64_t)b * p.out_bs + (int64_t)d * p.out_ds;
     float prev[CVE], cur[CVE], y[CVE];
@@ -112,7 +124,9 @@ template <typename T>
 __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args p) {
   const int d = blockIdx.x;                         // a CTA owns one channel, as in the forward kernel
   const int W = p.width, L = p.seqlen;
-  const int nblk = (L + CVT * CVE - 1) / (CVT * CVE), items = p.batch * nblk;
+  const int tpr = conv_tpr(L), rpi = CVT / tpr;          // threads per row, batch rows per item
+  const int nblk = (L + tpr * CVE - 1) / (tpr * CVE), items = ((p.batch + rpi - 1) / rpi) * nblk;
+  const int sub = threadIdx.x / tpr, tt = threadIdx.x - sub * tpr;
   // the taps right-aligned in a window of MAXW (zeros in front): every register index below is a
   // compile-time constant whatever the width
   float w[MAXW];
@@ -122,9 +136,10 @@ __global__ void __launch_bounds__(CVT) conv1d_bwd_kernel(const b200_conv1d_args 
   const float bias = p.bias ? tof(reinterpret_cast<const T *>(p.bias)[d]) : 0.f;
   float dw[MAXW] = {0.f, 0.f, 0.f, 0.f}, db = 0.f;
   for (int item = blockIdx.y; item < items; item += gridDim.y) {
-    const int b = item / nblk;
-    const int t = ((item - b * nblk) * CVT + threadIdx.x) * CVE;
-    if (t >= L) continue;
+    const int bg = item / nblk;
+    const int b = bg * rpi + sub;
+    const int t = ((item - bg * nblk) * tpr + tt) * CVE;
+    if (t >= L || b >= p.batch) continue;
     const T *x = reinterpret_cast<const T *>(p.x) + (int64_t)b * p.x_bs + (int64_t)d * p.x_ds;
     const T *dout = reinterpret_cast<const T *>(p.dout) + (int64_t)b * p.dout_bs + (int64_t)d * p.dout_ds;
     T *dx = reinterpret_cast<T *>(p.dx) + (int64_t)b * p.dx_bs + (int64_t)d * p.dx_ds;
@@ -579,7 +594,8 @@ int check_conv(const b200_conv1d_args &a, bool bwd, bool update) {
 // grid of the convolution kernels: a column of CTAs per channel, as many per channel as it takes
 // to put about two CTAs on every resident slot (8 per SM), and never more than the channel has items
 dim3 conv_grid(const b200_conv1d_args &a) {
-  const int64_t nblk = (a.seqlen + CVT * CVE - 1) / (CVT * CVE), items = (int64_t)a.batch * nblk;
+  const int tpr = conv_tpr(a.seqlen), rpi = CVT / tpr;
+  const int64_t nblk = (a.seqlen + tpr * CVE - 1) / (tpr * CVE), items = (int64_t)((a.batch + rpi - 1) / rpi) * nblk;
   const int64_t slots = (int64_t)sm_count_current() * 8;
   int64_t gy = (2 * slots + a.dim - 1) / a.dim;
   gy = gy < 1 ? 1 : (gy > items ? items : gy);
