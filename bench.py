@@ -994,8 +994,8 @@ class LmTrain:
     """benchmark configuration 2: Mamba LM, 24 layers, d_model 768 (d_inner 1536, dstate 16, dt_rank 48,
     conv 4), vocabulary 50280, random-init bf16 weights, token ids uniform in [0, 50280), batch 8 x
     2048 tokens, forward + backward of the shifted cross-entropy + a fused AdamW step.  The batch
-    is split over the ranks (fixed total work); gradients are all-reduced in buckets overlapped
-    with the backward pass (DistributedDataParallel over NCCL)."""
+    is split over the ranks (fixed total work); the gradients are averaged with one flat NCCL
+    all-reduce inside the captured step graph (DistributedDataParallel if the capture is refused)."""
     name = "lm_cfg2"
     dtype = "bf16 weights and activations, f32 scan state"
     metric, unit = "training tokens/s (LM forward + backward + optimizer step)", "tokens/s"
@@ -1021,16 +1021,67 @@ class LmTrain:
         torch.manual_seed(0)
         model = MambaLMHeadModel(self.d_model, self.n_layer, self.vocab, device=dev, dtype=torch.bfloat16)
         self.n_params = sum(p.numel() for p in model.parameters())
-        self.model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index]) if pg is not None else model
-        self.opt = torch.optim.AdamW(self.model.parameters(), lr=1e-4, fused=True)
         g = torch.Generator().manual_seed(r)
         self.h_ids = torch.randint(0, self.vocab, (self.local_batch, self.L), generator=g).pin_memory()
         self.ids = self.h_ids.to(dev)
         self.ev = []
+        self.graph = None
+        if pg is not None:
+            # With a few sequences per rank the step is bound by the host enqueueing ~2000 kernels, not
+            # by the GPU: the whole step (forward, loss, backward, one flat gradient all-reduce over
+            # NCCL, AdamW) is captured once and replayed.  If the capture is refused the step falls
+            # back to DistributedDataParallel enqueued from the host.
+            try:
+                self.model = model
+                self.opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True, capturable=True)
+                self._capture_step(w)
+                self.describe["parallelism"] += "; whole step replayed from a CUDA graph, one flat gradient all-reduce (NCCL) inside it"
+            except Exception as exc:
+                torch.cuda.synchronize()
+                self.graph = None
+                self.describe["parallelism"] += f"; DistributedDataParallel from the host ({type(exc).__name__} during graph capture)"
+                self.model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index])
+                self.opt = torch.optim.AdamW(self.model.parameters(), lr=1e-4, fused=True)
+        else:
+            self.model = model
+            self.opt = torch.optim.AdamW(self.model.parameters(), lr=1e-4, fused=True)
         self.launches_per_step = self.n_layer * 8 + 2      # conv, scan, norm forward and backward per layer; the loss (this package's kernels)
+
+    def _fwd_bwd_reduce(self, world):
+        from lrnnx_b200.ops.cross_entropy import cross_entropy
+        logits = self.model(self.ids)
+        loss = cross_entropy(logits.view(-1, self.vocab), self.labels(self.ids).view(-1), ignore_index=-100)
+        loss.backward()
+        grads = [p.grad for p in self.model.parameters() if p.grad is not None]
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        torch.distributed.all_reduce(flat, group=self.pg)
+        flat.div_(world)
+        torch._foreach_copy_(grads, [t.view_as(g) for t, g in zip(flat.split([g.numel() for g in grads]), grads)])
+        return loss
+
+    def _capture_step(self, world):
+        dev = self.dev
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                     # warm-up: optimizer state, communicator, allocator
+            for _ in range(3):
+                self.opt.zero_grad(set_to_none=True)
+                self._fwd_bwd_reduce(world)
+                self.opt.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        self.opt.zero_grad(set_to_none=True)
+        with torch.cuda.graph(graph):
+            self._loss = self._fwd_bwd_reduce(world)
+            self.opt.step()
+        self.graph = graph
 
     def _train(self, ids):
         from lrnnx_b200.ops.cross_entropy import cross_entropy
+        if self.graph is not None:                        # ids is the graph's static input buffer
+            self.graph.replay()
+            return self._loss
         logits = self.model(ids)
         # next-token loss: the last position has no target (ignored) instead of slicing the logits, which
         # would copy them
