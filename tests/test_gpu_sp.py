@@ -128,3 +128,76 @@ def test_adjoint_summary_is_the_transpose_of_the_fixup():
     G = adjoint_summary(delta, A, C, None, bias, True, dy)
     rhs = (h.double() * G.double()).sum().item()
     assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0), (lhs, rhs)
+
+
+def _nccl_worker(rank, world, port, L, q):
+    import os
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lrnnx_b200.sp import sp_selective_scan_fn
+        g = torch.Generator().manual_seed(123)
+        b, d, n = 2, 32, 16
+        t = dict(u=torch.randn(b, d, L, generator=g), delta=torch.randn(b, d, L, generator=g) - 2.0,
+                 A=-torch.rand(d, n, generator=g) * 0.5 - 0.01, B=torch.randn(b, 1, n, L, generator=g),
+                 C=torch.randn(b, 1, n, L, generator=g), D=torch.randn(d, generator=g),
+                 z=torch.randn(b, d, L, generator=g), delta_bias=torch.rand(d, generator=g) - 3.0)
+        gout = torch.randn(b, d, L, generator=g)
+        lo, hi = rank * L // world, (rank + 1) * L // world
+        dev = torch.device("cuda", rank)
+        sl = {k: (v[..., lo:hi].contiguous() if v.dim() >= 3 else v).to(dev).requires_grad_(True) for k, v in t.items()}
+        y = sp_selective_scan_fn(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"], sl["delta_bias"], True)
+        y.backward(gout[..., lo:hi].to(dev))
+        torch.cuda.synchronize()
+        q.put((rank, y.detach().cpu(), {k: v.grad.cpu() for k, v in sl.items()}))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("L", [4096, 6144])
+def test_sp_scan_fn_over_nccl_matches_unsplit(L):
+    """sp_selective_scan_fn on two ranks over NCCL (one GPU each): the slices' outputs and input
+    gradients, stitched, and the all-reduced parameter gradients equal the unsplit op."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import torch.multiprocessing as mp
+    from lrnnx_b200.ops import selective_scan_fn
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29300 + (os.getpid() % 400)
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, L, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        r, y, grads = q.get(timeout=300)
+        res[r] = (y, grads)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    g = torch.Generator().manual_seed(123)
+    b, d, n = 2, 32, 16
+    t = dict(u=torch.randn(b, d, L, generator=g), delta=torch.randn(b, d, L, generator=g) - 2.0,
+             A=-torch.rand(d, n, generator=g) * 0.5 - 0.01, B=torch.randn(b, 1, n, L, generator=g),
+             C=torch.randn(b, 1, n, L, generator=g), D=torch.randn(d, generator=g),
+             z=torch.randn(b, d, L, generator=g), delta_bias=torch.rand(d, generator=g) - 3.0)
+    gout = torch.randn(b, d, L, generator=g)
+    cu = {k: v.cuda().requires_grad_(True) for k, v in t.items()}
+    y = selective_scan_fn(cu["u"], cu["delta"], cu["A"], cu["B"], cu["C"], cu["D"], z=cu["z"], delta_bias=cu["delta_bias"],
+                          delta_softplus=True)
+    y.backward(gout.cuda())
+    assert_close(torch.cat([res[r][0] for r in range(world)], -1), y.detach().cpu(), rtol=1e-4, atol_scale=2e-5, name="out")
+    for k in ("u", "delta", "B", "C", "z"):
+        got = torch.cat([res[r][1][k] for r in range(world)], -1)
+        assert_close(got, cu[k].grad.cpu(), rtol=3e-4, atol_scale=1e-4, name=f"d{k}")
+    for k in ("A", "D", "delta_bias"):
+        for r in range(world):
+            assert_close(res[r][1][k], cu[k].grad.cpu(), rtol=3e-4, atol_scale=1e-4, name=f"d{k} on rank {r}")
